@@ -1,0 +1,481 @@
+// Causal attention over the paged cache on the CUDA cores, for any head size
+// that is a multiple of 16 (up to 256), any number of heads and groups, any
+// page size that divides the key tile, float32 or bfloat16 storage, with an
+// optional window.
+//
+// Keys are cut into splits of LS_SPLIT tokens at fixed absolute positions.  A
+// split is reduced by an online softmax over ascending key tiles; the splits of
+// a row are folded in ascending order by ls_fold().  A split's bounds and the
+// fold order depend only on the row's own position, so a row's result does not
+// depend on the portion or batch it came in.  Two ways of running the splits
+// give the same arithmetic:
+//   serial:   one block walks all splits of its rows and folds as it goes
+//             (portions of prompts: many rows, no scratch memory);
+//   parallel: one block per split writes a partial (acc, m, l) to scratch and
+//             ls_attention_combine folds them (decoded tokens: few rows).
+//
+// pages: [num_pages, 2, nkv, page_size, d]; q, out: [tokens, nq, d].
+// work item (8 ints): request row in the block table, first token (packed
+// index), number of tokens, position of the first token, first split, end
+// split, first scratch slot (-1: serial, write `out`), unused.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+#define LS_SPLIT 256
+
+namespace {
+
+constexpr int TILE_M = 16;   // query tokens of a tile kernel block
+constexpr int TILE_N = 32;   // keys per tile of the tile kernel
+constexpr int MAX_D = 256;
+
+struct Fold {
+  float m, l;
+};
+
+// acc_run, m_run, l_run <- fold of (acc_s, m_s, l_s), written with explicit
+// roundings so that every caller produces the same bits.
+__device__ __forceinline__ void ls_fold_scales(float m_run, float m_s, float& alpha, float& beta,
+                                               float& m_new) {
+  m_new = fmaxf(m_run, m_s);
+  alpha = (m_run == -CUDART_INF_F) ? 0.f : expf(m_run - m_new);
+  beta = (m_s == -CUDART_INF_F) ? 0.f : expf(m_s - m_new);
+}
+
+__device__ __forceinline__ float ls_fold_value(float run, float alpha, float part, float beta) {
+  return __fmaf_rn(part, beta, __fmul_rn(run, alpha));
+}
+
+template <typename T>
+__device__ __forceinline__ const T* page_ptr(const T* pages, const int* table_row, int key,
+                                             int which, int kvh, int nkv, int page_size, int d,
+                                             int num_pages, int* err) {
+  const int page = table_row[key / page_size];
+  if (page < 0 || page >= num_pages) {
+    ls_record_fault(err, LS_DEV_PAGE_RANGE, key);
+    return nullptr;
+  }
+  return pages + ((((int64_t)page * 2 + which) * nkv + kvh) * page_size + (key % page_size)) * d;
+}
+
+// --------------------------------------------------------------------------
+// tile kernel: up to 16 query tokens of one request, one query head
+// --------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* __restrict__ out,
+                      float* __restrict__ part_acc, float* __restrict__ part_ml,
+                      const int* __restrict__ work, const int* __restrict__ block_table,
+                      int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
+                      int window, float scale, int* err) {
+  extern __shared__ float smem[];
+  const int dp = d + 1;
+  float* Qs = smem;                    // [TILE_M][d+1]
+  float* Ks = Qs + TILE_M * dp;        // [TILE_N][d+1]
+  float* Vs = Ks + TILE_N * dp;        // [TILE_N][d]
+  float* Ps = Vs + TILE_N * d;         // [TILE_M][TILE_N+1]
+
+  const int* w = work + (int64_t)blockIdx.x * 8;
+  const int req_row = w[0], tok0 = w[1], ntok = w[2], pos0 = w[3];
+  const int split_begin = w[4], split_end = w[5], slot_base = w[6];
+  const int h = blockIdx.y;
+  const int kvh = h / (nq / nkv);
+  const int tid = threadIdx.x;
+  const int m = tid >> 3, sub = tid & 7;
+  const int nchunk = d >> 3;           // outputs per thread: dd = sub + 8*j
+  const int* table_row = block_table + (int64_t)req_row * table_stride;
+
+  const int pos_last = pos0 + ntok - 1;
+  const int key_lo_tile = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int qpos = pos0 + m;
+  const bool row_valid = m < ntok;
+  const int row_lo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+
+  for (int i = tid; i < TILE_M * d; i += 128) {
+    const int r = i / d, c = i - r * d;
+    Qs[r * dp + c] = r < ntok ? ls_to_float<T>(q[((int64_t)(tok0 + r) * nq + h) * d + c]) : 0.f;
+  }
+
+  float acc_run[MAX_D / 8], acc_s[MAX_D / 8];
+#pragma unroll
+  for (int j = 0; j < MAX_D / 8; ++j) acc_run[j] = 0.f;
+  float m_run = -CUDART_INF_F, l_run = 0.f;
+
+  for (int split = split_begin; split < split_end; ++split) {
+    const int s_lo = split * LS_SPLIT;
+    int s_hi = s_lo + LS_SPLIT;                 // exclusive
+    if (s_hi > pos_last + 1) s_hi = pos_last + 1;
+#pragma unroll
+    for (int j = 0; j < MAX_D / 8; ++j) acc_s[j] = 0.f;
+    float m_s = -CUDART_INF_F, l_s = 0.f;
+
+    // tiles lie at fixed offsets from the split's start; those wholly before
+    // the first row's window change nothing and are skipped
+    int t_first = s_lo;
+    if (key_lo_tile > s_lo) t_first = s_lo + ((key_lo_tile - s_lo) / TILE_N) * TILE_N;
+    for (int n0 = t_first; n0 < s_hi; n0 += TILE_N) {
+      __syncthreads();
+      for (int i = tid; i < TILE_N * d; i += 128) {
+        const int n = i / d, c = i - n * d;
+        const int key = n0 + n;
+        float kv = 0.f, vv = 0.f;
+        if (key < s_hi && key >= key_lo_tile) {
+          const T* kp = page_ptr<T>(pages, table_row, key, 0, kvh, nkv, page_size, d, num_pages, err);
+          if (kp != nullptr) {
+            kv = ls_to_float<T>(kp[c]);
+            vv = ls_to_float<T>(kp[(int64_t)nkv * page_size * d + c]);
+          }
+        }
+        Ks[n * dp + c] = kv;
+        Vs[n * d + c] = vv;
+      }
+      __syncthreads();
+
+      float s[4];
+      float tile_max = -CUDART_INF_F;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = sub * 4 + j;
+        const int key = n0 + n;
+        float dot = 0.f;
+        const float* qr = Qs + m * dp;
+        const float* kr = Ks + n * dp;
+        for (int c = 0; c < d; ++c) dot = fmaf(qr[c], kr[c], dot);
+        const bool keep = row_valid && key < s_hi && key <= qpos && key >= row_lo;
+        s[j] = keep ? dot * scale : -CUDART_INF_F;
+        tile_max = fmaxf(tile_max, s[j]);
+      }
+      tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+      tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+      tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
+      const float m_new = fmaxf(m_s, tile_max);
+      float alpha = 1.f;
+      float psum = 0.f;
+      float p[4] = {0.f, 0.f, 0.f, 0.f};
+      if (m_new != -CUDART_INF_F) {
+        alpha = (m_s == -CUDART_INF_F) ? 0.f : expf(m_s - m_new);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          p[j] = (s[j] == -CUDART_INF_F) ? 0.f : expf(s[j] - m_new);
+          psum += p[j];
+        }
+      }
+      psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 4);
+      l_s = __fmaf_rn(l_s, alpha, psum);
+      m_s = m_new;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) Ps[m * (TILE_N + 1) + sub * 4 + j] = p[j];
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < MAX_D / 8; ++j) {
+        if (j < nchunk) {
+          float a = __fmul_rn(acc_s[j], alpha);
+          const float* pr = Ps + m * (TILE_N + 1);
+          const float* vc = Vs + sub + 8 * j;
+          for (int n = 0; n < TILE_N; ++n) a = fmaf(pr[n], vc[n * d], a);
+          acc_s[j] = a;
+        }
+      }
+      __syncwarp();
+    }
+
+    if (slot_base >= 0) {
+      // parallel mode: this block covers one split; write the partial
+      if (row_valid) {
+        const int64_t slot = (int64_t)slot_base + m;
+#pragma unroll
+        for (int j = 0; j < MAX_D / 8; ++j)
+          if (j < nchunk) part_acc[(slot * nq + h) * d + sub + 8 * j] = acc_s[j];
+        if (sub == 0) {
+          part_ml[(slot * nq + h) * 2 + 0] = m_s;
+          part_ml[(slot * nq + h) * 2 + 1] = l_s;
+        }
+      }
+    } else {
+      float alpha, beta, m_new;
+      ls_fold_scales(m_run, m_s, alpha, beta, m_new);
+      if (m_s != -CUDART_INF_F) {
+#pragma unroll
+        for (int j = 0; j < MAX_D / 8; ++j)
+          if (j < nchunk) acc_run[j] = ls_fold_value(acc_run[j], alpha, acc_s[j], beta);
+        l_run = ls_fold_value(l_run, alpha, l_s, beta);
+        m_run = m_new;
+      }
+    }
+  }
+
+  if (slot_base < 0 && row_valid) {
+    T* o = out + ((int64_t)(tok0 + m) * nq + h) * d;
+#pragma unroll
+    for (int j = 0; j < MAX_D / 8; ++j)
+      if (j < nchunk) o[sub + 8 * j] = ls_from_float<T>(l_run > 0.f ? __fdiv_rn(acc_run[j], l_run) : 0.f);
+  }
+}
+
+// --------------------------------------------------------------------------
+// decode kernel: one query token, one split, one kv head with its whole group
+// of query heads (they share the loaded keys and values).  Writes a partial.
+// --------------------------------------------------------------------------
+constexpr int DEC_TILE = 64;
+constexpr int DEC_ACC = 8;     // outputs per thread: group * d <= 128 * DEC_ACC
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
+                        float* __restrict__ part_acc, float* __restrict__ part_ml,
+                        const int* __restrict__ work, const int* __restrict__ block_table,
+                        int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
+                        int window, float scale, int* err) {
+  extern __shared__ __align__(16) unsigned char dsm[];
+  constexpr int VEC = 16 / sizeof(T);        // elements per 16-byte chunk
+  const int group = nq / nkv;
+  const int kstride = d + VEC;               // padded row of K in elements
+  T* Ks = reinterpret_cast<T*>(dsm);                       // [DEC_TILE][d+VEC]
+  T* Vs = Ks + DEC_TILE * kstride;                         // [DEC_TILE][d]
+  float* Qs = reinterpret_cast<float*>(Vs + DEC_TILE * d); // [group][d]
+  float* Ss = Qs + group * d;                              // [group][DEC_TILE]
+  float* St = Ss + group * DEC_TILE;                       // [group][3]: m, l, alpha
+
+  const int* w = work + (int64_t)blockIdx.x * 8;
+  const int req_row = w[0], tok = w[1], pos = w[3], split = w[4], slot = w[6];
+  const int kvh = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int* table_row = block_table + (int64_t)req_row * table_stride;
+
+  const int row_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int s_lo = split * LS_SPLIT;
+  int s_hi = s_lo + LS_SPLIT;
+  if (s_hi > pos + 1) s_hi = pos + 1;
+
+  for (int i = tid; i < group * d; i += 128) {
+    const int g = i / d, c = i - g * d;
+    Qs[i] = ls_to_float<T>(q[((int64_t)tok * nq + kvh * group + g) * d + c]);
+  }
+  for (int g = tid; g < group; g += 128) {
+    St[g * 3 + 0] = -CUDART_INF_F;
+    St[g * 3 + 1] = 0.f;
+    St[g * 3 + 2] = 1.f;
+  }
+  float acc[DEC_ACC];
+#pragma unroll
+  for (int j = 0; j < DEC_ACC; ++j) acc[j] = 0.f;
+
+  const int cpr = d / VEC;                   // 16-byte chunks per row
+  int t_first = s_lo;
+  if (row_lo > s_lo) t_first = s_lo + ((row_lo - s_lo) / DEC_TILE) * DEC_TILE;
+
+  for (int n0 = t_first; n0 < s_hi; n0 += DEC_TILE) {
+    __syncthreads();
+    for (int i = tid; i < DEC_TILE * cpr; i += 128) {
+      const int n = i / cpr, c = i - n * cpr;
+      const int key = n0 + n;
+      uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+      if (key < s_hi && key >= row_lo) {
+        const T* kp = page_ptr<T>(pages, table_row, key, 0, kvh, nkv, page_size, d, num_pages, err);
+        if (kp != nullptr) {
+          kv = *reinterpret_cast<const uint4*>(kp + c * VEC);
+          vv = *reinterpret_cast<const uint4*>(kp + (int64_t)nkv * page_size * d + c * VEC);
+        }
+      }
+      *reinterpret_cast<uint4*>(Ks + n * kstride + c * VEC) = kv;
+      *reinterpret_cast<uint4*>(Vs + n * d + c * VEC) = vv;
+    }
+    __syncthreads();
+
+    for (int u = tid; u < group * DEC_TILE; u += 128) {
+      const int g = u / DEC_TILE, n = u - g * DEC_TILE;
+      const int key = n0 + n;
+      const T* kr = Ks + n * kstride;
+      const float* qr = Qs + g * d;
+      float dot = 0.f;
+      for (int c = 0; c < d; c += VEC) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(kr + c);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int x = 0; x < VEC; ++x) dot = fmaf(qr[c + x], ls_to_float<T>(e[x]), dot);
+      }
+      const bool keep = key < s_hi && key >= row_lo;
+      Ss[u] = keep ? dot * scale : -CUDART_INF_F;
+    }
+    __syncthreads();
+
+    for (int g = warp; g < group; g += 4) {
+      const float s0 = Ss[g * DEC_TILE + lane], s1 = Ss[g * DEC_TILE + lane + 32];
+      const float tile_max = ls_warp_max(fmaxf(s0, s1));
+      const float m_old = St[g * 3 + 0];
+      const float m_new = fmaxf(m_old, tile_max);
+      float alpha = 1.f, p0 = 0.f, p1 = 0.f;
+      if (m_new != -CUDART_INF_F) {
+        alpha = (m_old == -CUDART_INF_F) ? 0.f : expf(m_old - m_new);
+        p0 = (s0 == -CUDART_INF_F) ? 0.f : expf(s0 - m_new);
+        p1 = (s1 == -CUDART_INF_F) ? 0.f : expf(s1 - m_new);
+      }
+      const float psum = ls_warp_sum(p0 + p1);
+      Ss[g * DEC_TILE + lane] = p0;
+      Ss[g * DEC_TILE + lane + 32] = p1;
+      if (lane == 0) {
+        St[g * 3 + 0] = m_new;
+        St[g * 3 + 1] = fmaf(St[g * 3 + 1], alpha, psum);
+        St[g * 3 + 2] = alpha;
+      }
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int j = 0; j < DEC_ACC; ++j) {
+      const int u = tid + 128 * j;
+      if (u < group * d) {
+        const int g = u / d, c = u - g * d;
+        float a = acc[j] * St[g * 3 + 2];
+        const float* pr = Ss + g * DEC_TILE;
+        const T* vc = Vs + c;
+        for (int n = 0; n < DEC_TILE; ++n) a = fmaf(pr[n], ls_to_float<T>(vc[n * d]), a);
+        acc[j] = a;
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < DEC_ACC; ++j) {
+    const int u = tid + 128 * j;
+    if (u < group * d) {
+      const int g = u / d, c = u - g * d;
+      part_acc[((int64_t)slot * nq + kvh * group + g) * d + c] = acc[j];
+    }
+  }
+  for (int g = tid; g < group; g += 128) {
+    part_ml[((int64_t)slot * nq + kvh * group + g) * 2 + 0] = St[g * 3 + 0];
+    part_ml[((int64_t)slot * nq + kvh * group + g) * 2 + 1] = St[g * 3 + 1];
+  }
+}
+
+// --------------------------------------------------------------------------
+// combine: fold the partials of a row in ascending split order
+// combine item (4 ints): token (packed index), first slot, slot stride, splits
+// --------------------------------------------------------------------------
+template <typename T>
+__global__ void attention_combine_kernel(const float* __restrict__ part_acc,
+                                         const float* __restrict__ part_ml, T* __restrict__ out,
+                                         const int* __restrict__ items, int nq, int d) {
+  const int* it = items + (int64_t)blockIdx.x * 4;
+  const int tok = it[0], first = it[1], stride = it[2], n = it[3];
+  const int h = blockIdx.y;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float acc = 0.f, m_run = -CUDART_INF_F, l_run = 0.f;
+    for (int s = 0; s < n; ++s) {
+      const int64_t slot = (int64_t)first + (int64_t)s * stride;
+      const float m_s = part_ml[(slot * nq + h) * 2 + 0];
+      const float l_s = part_ml[(slot * nq + h) * 2 + 1];
+      float alpha, beta, m_new;
+      ls_fold_scales(m_run, m_s, alpha, beta, m_new);
+      if (m_s != -CUDART_INF_F) {
+        acc = ls_fold_value(acc, alpha, part_acc[(slot * nq + h) * d + c], beta);
+        l_run = ls_fold_value(l_run, alpha, l_s, beta);
+        m_run = m_new;
+      }
+    }
+    out[((int64_t)tok * nq + h) * d + c] = ls_from_float<T>(l_run > 0.f ? __fdiv_rn(acc, l_run) : 0.f);
+  }
+}
+
+size_t tile_smem_bytes(int d) {
+  return sizeof(float) * ((size_t)TILE_M * (d + 1) + (size_t)TILE_N * (d + 1) + (size_t)TILE_N * d +
+                          (size_t)TILE_M * (TILE_N + 1));
+}
+
+size_t decode_smem_bytes(int d, int group, int elem) {
+  const int vec = 16 / elem;
+  return (size_t)elem * ((size_t)DEC_TILE * (d + vec) + (size_t)DEC_TILE * d) +
+         sizeof(float) * ((size_t)group * d + (size_t)group * DEC_TILE + (size_t)group * 3);
+}
+
+bool shape_ok(int nq, int nkv, int d, int page_size, int tile) {
+  return nq > 0 && nkv > 0 && nq % nkv == 0 && d >= 16 && d <= MAX_D && d % 16 == 0 &&
+         page_size > 0 && tile % page_size == 0;
+}
+
+}  // namespace
+
+LS_API int ls_attention_split_size() { return LS_SPLIT; }
+
+LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float* part_acc,
+                             float* part_ml, int dtype, const int* work, int n_work,
+                             const int* block_table, int table_stride, int nq, int nkv, int d,
+                             int page_size, int num_pages, int window, float scale, int* err,
+                             cudaStream_t stream) {
+  if (n_work <= 0) return 0;
+  if (!shape_ok(nq, nkv, d, page_size, LS_SPLIT)) return LS_E_SIZE;
+  if (nq > 65535) return LS_E_SIZE;
+  const size_t smem = tile_smem_bytes(d);
+  dim3 grid(n_work, nq);
+  cudaError_t e;
+  if (dtype == LS_F32) {
+    e = cudaFuncSetAttribute(attention_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return LS_E_SMEM;
+    attention_tile_kernel<float><<<grid, 128, smem, stream>>>(
+        (const float*)q, (const float*)pages, (float*)out, part_acc, part_ml, work, block_table,
+        table_stride, nq, nkv, d, page_size, num_pages, window, scale, err);
+  } else if (dtype == LS_BF16) {
+    e = cudaFuncSetAttribute(attention_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return LS_E_SMEM;
+    attention_tile_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, part_acc,
+        part_ml, work, block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale,
+        err);
+  } else {
+    return LS_E_DTYPE;
+  }
+  return ls_launch_status();
+}
+
+// Returns LS_E_SIZE for shapes it does not take (group * d > 1024); the caller
+// then uses ls_attention_tile in parallel mode, which takes them all.
+LS_API int ls_attention_decode(const void* q, const void* pages, float* part_acc, float* part_ml,
+                               int dtype, const int* work, int n_work, const int* block_table,
+                               int table_stride, int nq, int nkv, int d, int page_size,
+                               int num_pages, int window, float scale, int* err,
+                               cudaStream_t stream) {
+  if (n_work <= 0) return 0;
+  if (!shape_ok(nq, nkv, d, page_size, DEC_TILE)) return LS_E_SIZE;
+  const int group = nq / nkv;
+  if (group * d > 128 * DEC_ACC || nkv > 65535) return LS_E_SIZE;
+  dim3 grid(n_work, nkv);
+  cudaError_t e;
+  if (dtype == LS_F32) {
+    const size_t smem = decode_smem_bytes(d, group, 4);
+    e = cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return LS_E_SMEM;
+    attention_decode_kernel<float><<<grid, 128, smem, stream>>>(
+        (const float*)q, (const float*)pages, part_acc, part_ml, work, block_table, table_stride,
+        nq, nkv, d, page_size, num_pages, window, scale, err);
+  } else if (dtype == LS_BF16) {
+    const size_t smem = decode_smem_bytes(d, group, 2);
+    e = cudaFuncSetAttribute(attention_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return LS_E_SMEM;
+    attention_decode_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, part_acc, part_ml, work,
+        block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, err);
+  } else {
+    return LS_E_DTYPE;
+  }
+  return ls_launch_status();
+}
+
+LS_API int ls_attention_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
+                                const int* items, int n_items, int nq, int d,
+                                cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (nq > 65535) return LS_E_SIZE;
+  dim3 grid(n_items, nq);
+  const int threads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
+  if (dtype == LS_F32)
+    attention_combine_kernel<float><<<grid, threads, 0, stream>>>(part_acc, part_ml, (float*)out, items, nq, d);
+  else if (dtype == LS_BF16)
+    attention_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, items, nq, d);
+  else
+    return LS_E_DTYPE;
+  return ls_launch_status();
+}

@@ -1,0 +1,228 @@
+// Row-wise kernels of the step: embedding gather, RMSNorm, and the fused
+// per-head norm + rotary position encoding + paged cache write.
+//
+// All reductions run in float32 in an order fixed by the row's own width, so
+// a row's result does not depend on what else is in the batch.
+#include "common.cuh"
+
+// --------------------------------------------------------------------------
+// embedding: out[t, :] = table[ids[t], :]   (out is the float32 residual stream)
+// --------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                    float* __restrict__ out, int width, int vocab, int* err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* dst = out + (int64_t)t * width;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) ls_record_fault(err, LS_DEV_TOKEN_RANGE, t);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = 0.f;
+    return;
+  }
+  const T* src = table + (int64_t)id * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = ls_to_float<T>(src[i]);
+}
+
+LS_API int ls_embed_gather(const int* ids, const void* table, int table_dtype, float* out,
+                           int tokens, int width, int vocab, int* err, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (table_dtype == LS_F32)
+    embed_gather_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, width, vocab, err);
+  else if (table_dtype == LS_BF16)
+    embed_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, width, vocab, err);
+  else
+    return LS_E_DTYPE;
+  return ls_launch_status();
+}
+
+// --------------------------------------------------------------------------
+// RMSNorm over float32 rows: y = x * rsqrt(mean(x^2) + eps) * gain
+// rows may be gathered through row_index (the rows whose logits are wanted).
+// --------------------------------------------------------------------------
+template <typename TO, typename TG>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
+                               const TG* __restrict__ gain, TO* __restrict__ y, int width,
+                               int src_rows, float eps, int* err) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  int src = row_index ? row_index[r] : r;
+  if (src < 0 || src >= src_rows) {
+    if (threadIdx.x == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, r);
+    src = 0;
+  }
+  const float* xr = x + (int64_t)src * width;
+  TO* yr = y + (int64_t)r * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = xr[i];
+    ss = fmaf(v, v, ss);
+  }
+  const float total = ls_block_sum(ss, scratch);
+  const float rstd = 1.0f / sqrtf(total / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    yr[i] = ls_from_float<TO>(xr[i] * rstd * ls_to_float<TG>(gain[i]));
+}
+
+LS_API int ls_rmsnorm(const float* x, const int* row_index, const void* gain, int gain_dtype,
+                      void* y, int y_dtype, int rows, int width, int src_rows, float eps,
+                      int* err, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  // the block size depends on the width alone, so the summation order does too
+  const int threads = width >= 2048 ? 256 : 128;
+#define LS_RMS(TO, TG)                                                                        \
+  rmsnorm_kernel<TO, TG><<<rows, threads, 0, stream>>>(x, row_index, (const TG*)gain, (TO*)y, \
+                                                      width, src_rows, eps, err)
+  if (y_dtype == LS_F32 && gain_dtype == LS_F32) LS_RMS(float, float);
+  else if (y_dtype == LS_F32 && gain_dtype == LS_BF16) LS_RMS(float, __nv_bfloat16);
+  else if (y_dtype == LS_BF16 && gain_dtype == LS_F32) LS_RMS(__nv_bfloat16, float);
+  else if (y_dtype == LS_BF16 && gain_dtype == LS_BF16) LS_RMS(__nv_bfloat16, __nv_bfloat16);
+  else return LS_E_DTYPE;
+#undef LS_RMS
+  return ls_launch_status();
+}
+
+// --------------------------------------------------------------------------
+// Per-head RMSNorm (optional) + rotary position encoding (optional) of q and k,
+// and the write of k and v into the paged cache.  One warp per (token, head).
+//
+// qkv:   [tokens, (nq + 2*nkv) * d]   projections of this step's tokens
+// q_out: [tokens, nq * d]
+// pages: [num_pages, 2, nkv, page_size, d]   one layer of one cache group
+// The page of a token is block_table[req_row[token] * table_stride + pos / page_size].
+// --------------------------------------------------------------------------
+template <typename T, typename TG>
+__global__ void qk_norm_rope_store_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ pages,
+    const TG* __restrict__ q_gain, const TG* __restrict__ k_gain,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table,
+    const int* __restrict__ positions, const int* __restrict__ token_req,
+    const int* __restrict__ block_table, int table_stride, int tokens, int nq, int nkv, int d,
+    int rot_dim, int page_size, int num_pages, int max_positions, float eps, int write_cache,
+    int* err) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y * warps_per_block + (threadIdx.x >> 5);
+  const int t = blockIdx.x;
+  const int heads_total = nq + 2 * nkv;
+  if (head >= heads_total) return;
+  const bool is_q = head < nq;
+  const bool is_k = !is_q && head < nq + nkv;
+  if (!is_q && !write_cache) return;
+
+  const T* src = qkv + (int64_t)t * heads_total * d + (int64_t)head * d;
+  const int pos = positions[t];
+
+  T* dst;
+  if (is_q) {
+    dst = q_out + ((int64_t)t * nq + head) * d;
+  } else {
+    const int kvh = is_k ? head - nq : head - nq - nkv;
+    const int row = token_req[t];
+    const int page = block_table[(int64_t)row * table_stride + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (lane == 0) ls_record_fault(err, LS_DEV_PAGE_RANGE, t);
+      return;
+    }
+    dst = pages + ((((int64_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + (pos % page_size)) * d;
+  }
+
+  if (!is_q && !is_k) {  // v: copied as it is
+    for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    return;
+  }
+
+  const TG* gain = is_q ? q_gain : k_gain;
+  float rstd = 1.f;
+  if (gain != nullptr) {
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) {
+      const float v = ls_to_float<T>(src[i]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = ls_warp_sum(ss);
+    rstd = 1.0f / sqrtf(ss / (float)d + eps);
+  }
+  const int half = rot_dim >> 1;
+  if (half > 0 && (pos < 0 || pos >= max_positions)) {
+    if (lane == 0) ls_record_fault(err, LS_DEV_POSITION_RANGE, t);
+    return;
+  }
+  const float* cs = cos_table + (int64_t)pos * half;
+  const float* sn = sin_table + (int64_t)pos * half;
+  for (int i = lane; i < half; i += 32) {
+    float lo = ls_to_float<T>(src[i]) * rstd;
+    float hi = ls_to_float<T>(src[i + half]) * rstd;
+    if (gain != nullptr) {
+      lo *= ls_to_float<TG>(gain[i]);
+      hi *= ls_to_float<TG>(gain[i + half]);
+    }
+    const float c = cs[i], s = sn[i];
+    dst[i] = ls_from_float<T>(lo * c - hi * s);
+    dst[i + half] = ls_from_float<T>(hi * c + lo * s);
+  }
+  for (int i = rot_dim + lane; i < d; i += 32) {  // dims past the rotary part
+    float v = ls_to_float<T>(src[i]) * rstd;
+    if (gain != nullptr) v *= ls_to_float<TG>(gain[i]);
+    dst[i] = ls_from_float<T>(v);
+  }
+}
+
+LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int dtype,
+                                 const void* q_gain, const void* k_gain, int gain_dtype,
+                                 const float* cos_table, const float* sin_table,
+                                 const int* positions, const int* token_req,
+                                 const int* block_table, int table_stride, int tokens, int nq,
+                                 int nkv, int d, int rot_dim, int page_size, int num_pages,
+                                 int max_positions, float eps, int write_cache, int* err,
+                                 cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return LS_E_SIZE;
+  const int heads = nq + 2 * nkv;
+  const int warps = 4;
+  dim3 grid(tokens, (heads + warps - 1) / warps);
+#define LS_QK(T, TG)                                                                          \
+  qk_norm_rope_store_kernel<T, TG><<<grid, warps * 32, 0, stream>>>(                          \
+      (const T*)qkv, (T*)q_out, (T*)pages, (const TG*)q_gain, (const TG*)k_gain, cos_table,   \
+      sin_table, positions, token_req, block_table, table_stride, tokens, nq, nkv, d, rot_dim, \
+      page_size, num_pages, max_positions, eps, write_cache, err)
+  if (dtype == LS_F32 && gain_dtype == LS_F32) LS_QK(float, float);
+  else if (dtype == LS_F32 && gain_dtype == LS_BF16) LS_QK(float, __nv_bfloat16);
+  else if (dtype == LS_BF16 && gain_dtype == LS_F32) LS_QK(__nv_bfloat16, float);
+  else if (dtype == LS_BF16 && gain_dtype == LS_BF16) LS_QK(__nv_bfloat16, __nv_bfloat16);
+  else return LS_E_DTYPE;
+#undef LS_QK
+  return ls_launch_status();
+}
+
+// --------------------------------------------------------------------------
+// silu(gate) * up on [rows, 2*width] -> [rows, width]  (gate in the first half)
+// used where the product is not fused into the GEMM that makes gate and up
+// --------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t rows,
+                                int width) {
+  const int64_t n = rows * width;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / width;
+    const int c = (int)(i - r * width);
+    const float g = ls_to_float<T>(gate_up[r * 2 * width + c]);
+    const float u = ls_to_float<T>(gate_up[r * 2 * width + width + c]);
+    out[i] = ls_from_float<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+LS_API int ls_silu_mul(const void* gate_up, void* out, int dtype, int rows, int width,
+                       cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int64_t n = (int64_t)rows * width;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  if (dtype == LS_F32)
+    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, rows, width);
+  else if (dtype == LS_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, width);
+  else
+    return LS_E_DTYPE;
+  return ls_launch_status();
+}

@@ -1,0 +1,112 @@
+"""The step function: one batch in, logits at the wanted places out.
+
+``ModelRunner`` owns the model's parts, its weights and the cache manager.
+``step`` runs only the tokens it is given, as one batch, on top of what earlier
+steps left in the cache: portions of prompts beside single decoded tokens, cut
+anywhere.  Generation, the scheduler and trace replay all go through it.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+
+import torch
+
+from .. import kernels as K
+from ..cache import CacheManager
+from ..config import load_config
+from ..parts import Runtime
+from ..weights import load_weights
+from .batch import StepContext, StepEntry
+from .model import Model
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype must be bfloat16 or float32, got {dtype!r}") from None
+
+
+class ModelRunner:
+    def __init__(self, model_dir, dtype="bfloat16", device="cuda:0", num_pages: int = 512,
+                 page_size: int = 16, max_live: int = 64, max_seq_len: int | None = None):
+        K.require_cuda()
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.dtype = parse_dtype(dtype)
+        self.config = load_config(model_dir)
+        self.spec = self.config.model_spec()
+        self.max_seq_len = int(max_seq_len or self.spec.max_positions)
+        K.library("core")
+        self.split_size = K.attention_split_size()
+        if self.split_size % page_size or page_size <= 0:
+            raise ValueError(
+                f"page_size {page_size} must divide the attention split of {self.split_size} tokens "
+                "and the 32- and 64-token key tiles")
+        if 32 % page_size and page_size % 32:
+            raise ValueError(f"page_size {page_size} is not supported (use 8, 16, 32 or 64)")
+        self.page_size = int(page_size)
+        self.err = K.new_error_word(self.device)
+        self.rt = Runtime(device=self.device, dtype=self.dtype, page_size=self.page_size,
+                          max_positions=self.max_seq_len, err=self.err)
+        self.model = Model(self.spec, self.rt)
+        tensors = load_weights(Path(model_dir), self.model.weight_specs(), self.dtype, self.device,
+                               aliases=self.model.aliases())
+        self.model.bind(tensors)
+        self.cache = CacheManager(self.model.cache_needs(), num_pages=num_pages, page_size=page_size,
+                                  max_live=max_live, max_seq_len=self.max_seq_len, dtype=self.dtype,
+                                  device=self.device)
+        self.steps_run = 0
+
+    # -- requests -----------------------------------------------------------
+    def open(self, uid: str) -> int:
+        return self.cache.create(uid)
+
+    def close(self, uid: str) -> None:
+        self.cache.release(uid)
+
+    def kv_len(self, uid: str) -> int:
+        return self.cache.lengths[uid]
+
+    # -- the step -----------------------------------------------------------
+    @torch.no_grad()
+    def step(self, entries: list[StepEntry], check: bool = True) -> torch.Tensor:
+        """Run one batch; returns float32 logits [wanted, vocab] in the order of
+        the entries and of their ``want`` lists.  Every entry's request must be
+        open and ``start`` must equal the number of tokens it already holds."""
+        if not entries:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        seen = set()
+        for e in entries:
+            if e.uid in seen:
+                raise ValueError(f"request {e.uid!r} appears twice in one step")
+            seen.add(e.uid)
+            have = self.cache.lengths.get(e.uid)
+            if have is None:
+                raise KeyError(f"request {e.uid!r} is not open")
+            if e.start != have:
+                raise ValueError(f"{e.uid}: portion starts at {e.start} but the cache holds {have} tokens")
+            self.cache.reserve(e.uid, e.start + len(e.tokens))
+        self.cache.sync()
+        slots = [self.cache.slots[e.uid] for e in entries]
+        ctx = StepContext(entries, slots, self.device, self.err, self.split_size)
+
+        model = self.model
+        h = model.embedding.forward(ctx)
+        for run in self.spec.schedule:
+            model.blocks[run.layer].forward(h, ctx, self.cache.view(run.cache, run.writes_cache))
+        if ctx.n_wanted:
+            y = model.final_norm.forward(h, ctx.wanted_rows)
+            logits = model.head.forward(y)
+        else:
+            logits = torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        for e in entries:
+            self.cache.advance(e.uid, e.start + len(e.tokens))
+        self.steps_run += 1
+        if check:
+            K.raise_on_fault(self.err)
+        return logits

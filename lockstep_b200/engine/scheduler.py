@@ -1,0 +1,274 @@
+"""Continuous batching above the step function (after LockStep's
+engine/sched/scheduler.py, with a token budget and lazy page reservation).
+
+Each step: admit waiting requests while slots and pages allow; give every
+decoding request its one token first, then cut the prompts of the others into
+portions under the step's token budget, oldest first; run the batch; sample for
+the requests whose context is now complete; finish and free.
+
+When pages run out: pages are taken step by step as a request grows, so a step
+may find the pool short.  Then cached prefix pages that no request holds are
+evicted first; if that is not enough the most recently admitted running request
+is preempted (its pages are given back, its tokens kept, it returns to the front
+of the queue and is computed again when readmitted); a request that cannot run
+even alone raises ``OutOfPages``.  A request larger than the whole pool is
+refused at ``submit``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+from ..cache import OutOfPages, PrefixIndex
+from ..sampling import SamplingParams
+from .batch import StepEntry
+from .policy import DefaultPolicy, Policy, SchedulerState
+
+
+@dataclass
+class Request:
+    """r = (uid, prompt, sampling parameters, seed); names as in LockStep
+    (engine/sched/scheduler.py:19-28)."""
+
+    uid: str
+    prompt: list[int]
+    seed: int = 0
+    max_new_tokens: int = 8
+    temperature: float = 0.0
+    top_p: float = 1.0
+
+    generated: list[int] = field(default_factory=list)
+    finished: bool = False
+    kv_len: int = 0
+    preempt_count: int = 0
+    cache_hit_tokens: int = 0
+
+    def context(self) -> list[int]:
+        return self.prompt + self.generated
+
+    def total_tokens(self) -> int:
+        return len(self.prompt) + len(self.generated)
+
+
+class OversizedRequest(ValueError):
+    """A request that cannot fit even when the pool is empty."""
+
+
+class Scheduler:
+    """``backend`` gives ``cache`` (a CacheManager), ``step(entries) -> logits``
+    and ``sample(logits, params) -> tokens``; ``ModelRunner`` with a ``Sampler``
+    is one, a host-side fake is another (the scheduler's decisions are tested
+    without a device)."""
+
+    def __init__(self, backend, max_step_tokens: int = 2048, policy: Policy | None = None,
+                 eos_token_ids=None, audit: bool = False, enable_prefix_cache: bool = False,
+                 max_running: int = 32):
+        self.backend = backend
+        self.cache = backend.cache
+        self.max_step_tokens = int(max_step_tokens)
+        if self.max_step_tokens < 1:
+            raise ValueError("max_step_tokens must be at least 1")
+        self.policy = policy or DefaultPolicy(max_running=max_running)
+        self.eos = set(eos_token_ids or ())
+        self.audit_enabled = audit
+        self.waiting: list[Request] = []
+        self.running: list[Request] = []
+        self.done: list[Request] = []
+        self.step_index = 0
+        self.events: list[tuple] = []          # (step, event, uid, detail)
+        self.stats = {"preemptions": 0, "evictions": 0, "steps": 0, "tokens_run": 0,
+                      "mixed_steps": 0, "budget_cuts": 0}
+        self.prefix = None
+        if enable_prefix_cache:
+            if len(self.cache.paged) != 1 or self.cache.paged[0].window or self.cache.states:
+                raise ValueError("prefix reuse needs a cache of one paged group that keeps all keys")
+            self.prefix = PrefixIndex(page_size=self.cache.page_size)
+
+    # -- bookkeeping ----------------------------------------------------------
+    def _event(self, name: str, uid: str, detail=()):
+        self.events.append((self.step_index, name, uid, tuple(detail)))
+
+    def _pages_for(self, tokens: int) -> int:
+        return -(-tokens // self.cache.page_size)
+
+    def _reclaimable(self) -> int:
+        return len(self.prefix.evictable(self.cache.paged[0])) if self.prefix else 0
+
+    def _state(self) -> SchedulerState:
+        return SchedulerState(
+            step=self.step_index, waiting=tuple(r.uid for r in self.waiting),
+            running=tuple(r.uid for r in self.running), free_blocks=self.cache.free_pages(),
+            total_blocks=self.cache.total_pages(), reclaimable_blocks=self._reclaimable())
+
+    def submit(self, request: Request) -> None:
+        if not request.prompt:
+            raise ValueError(f"{request.uid}: the prompt is empty")
+        total = len(request.prompt) + request.max_new_tokens
+        if self._pages_for(total) > self.cache.total_pages() or total > self.cache.max_seq_len:
+            raise OversizedRequest(
+                f"{request.uid} needs {self._pages_for(total)} pages ({len(request.prompt)} prompt + "
+                f"{request.max_new_tokens} new tokens at page size {self.cache.page_size}) but the pool "
+                f"holds {self.cache.total_pages()} and a sequence at most {self.cache.max_seq_len} tokens")
+        if any(r.uid == request.uid for r in self.waiting + self.running):
+            raise ValueError(f"a request with uid {request.uid!r} is already queued")
+        self.waiting.append(request)
+
+    # -- admission ------------------------------------------------------------
+    def _admit(self, request: Request, state: SchedulerState) -> None:
+        self.cache.create(request.uid)
+        request.kv_len = 0
+        request.cache_hit_tokens = 0
+        if self.prefix is not None:
+            group = self.cache.paged[0]
+            context = request.context()
+            hit, pages = self.prefix.lookup(context)
+            if hit >= len(context) and pages:       # keep something to compute
+                hit -= self.cache.page_size
+                pages = pages[:-1]
+            if hit and self.policy.honor_cache_hit(state, request.uid, hit):
+                group.adopt(request.uid, pages)
+                request.kv_len = request.cache_hit_tokens = hit
+                self.cache.lengths[request.uid] = hit
+                self._event("cache_hit", request.uid, (hit,))
+        self._event("resume" if request.preempt_count else "admit", request.uid)
+
+    def _preempt(self, request: Request) -> None:
+        self.cache.release(request.uid)
+        request.kv_len = 0
+        request.preempt_count += 1
+        self.running.remove(request)
+        self.waiting.insert(0, request)
+        self.stats["preemptions"] += 1
+        self._event("preempt", request.uid)
+
+    def _make_room(self, request: Request, tokens: int, planned: list) -> bool:
+        """Reserve pages so that ``request`` holds ``tokens``; evict, then preempt
+        younger requests, as needed.  False if the request itself had to go."""
+        while True:
+            if self.cache.can_reserve(request.uid, tokens):
+                self.cache.reserve(request.uid, tokens)
+                return True
+            if self.prefix is not None:
+                group = self.cache.paged[0]
+                candidates = self.prefix.evictable(group)
+                if candidates:
+                    victim = self.policy.evict_victim(self._state(), tuple(candidates))
+                    if victim not in candidates:
+                        raise ValueError(f"policy {self.policy.name} chose page {victim}, which is not evictable")
+                    self.prefix.evict(victim, group)
+                    self.stats["evictions"] += 1
+                    self._event("evict", request.uid, (victim,))
+                    continue
+            victim = self.running[-1]
+            if victim is request:
+                if len(self.running) == 1:
+                    raise OutOfPages(
+                        f"{request.uid} needs {self.cache.pages_short(request.uid, tokens)} more pages, "
+                        f"{self.cache.free_pages()} are free and no other request holds any")
+                self._preempt(request)
+                return False
+            planned[:] = [p for p in planned if p[0] is not victim]
+            self._preempt(victim)
+
+    # -- one step ---------------------------------------------------------------
+    def step(self) -> bool:
+        if not self.waiting and not self.running:
+            return False
+        state = self._state()
+        for request in list(self.waiting):
+            need = self._pages_for(request.total_tokens() + 1)
+            if not self.cache.has_slot() or not self.policy.admit(state, request.uid, need):
+                continue
+            self.waiting.remove(request)
+            self._admit(request, state)
+            self.running.append(request)
+            state = self._state()
+        if not self.running:
+            smallest = min(self._pages_for(r.total_tokens() + 1) for r in self.waiting)
+            raise OutOfPages(
+                f"{len(self.waiting)} requests waiting, the smallest needs {smallest} pages, "
+                f"{self.cache.free_pages()} free, nothing running that could free more")
+
+        for request in list(self.running):
+            if request.kv_len and request.generated and self.policy.should_preempt(state, request.uid):
+                self._preempt(request)
+                state = self._state()
+        if not self.running:
+            self.step_index += 1
+            return True
+
+        # decoding requests first, then prompts, each group oldest first
+        budget = self.max_step_tokens
+        planned: list[tuple[Request, int]] = []
+        order = [r for r in self.running if len(r.context()) - r.kv_len == 1] + \
+                [r for r in self.running if len(r.context()) - r.kv_len > 1]
+        for request in order:
+            if request not in self.running or budget <= 0:
+                continue
+            remaining = len(request.context()) - request.kv_len
+            take = self.policy.chunk_boundary(state, request.uid, remaining)
+            if not 1 <= take <= remaining:
+                raise ValueError(f"policy {self.policy.name} returned a portion of {take} for "
+                                 f"{request.uid} with {remaining} remaining")
+            if take > budget:
+                take = budget
+                self.stats["budget_cuts"] += 1
+            if self._make_room(request, request.kv_len + take, planned):
+                planned.append((request, take))
+                budget -= take
+        planned = [(r, n) for r, n in planned if r in self.running]
+        if not planned:
+            self.step_index += 1
+            return True
+
+        entries = []
+        for request, take in planned:
+            context = request.context()
+            start = request.kv_len
+            last = start + take == len(context)
+            entries.append(StepEntry(uid=request.uid, tokens=context[start:start + take], start=start,
+                                     want=[take - 1] if last else []))
+            self._event("decode" if take == 1 and last else "chunk", request.uid, (start, take))
+        kinds = {len(e.tokens) == 1 for e in entries}
+        if len(kinds) == 2:
+            self.stats["mixed_steps"] += 1
+        logits = self.backend.step(entries)
+        self.stats["steps"] += 1
+        self.stats["tokens_run"] += sum(len(e.tokens) for e in entries)
+
+        params, owners = [], []
+        for (request, take), e in zip(planned, entries):
+            request.kv_len = e.start + take
+            if e.want:
+                params.append(SamplingParams(uid=request.uid, seed=request.seed,
+                                             temperature=request.temperature, top_p=request.top_p,
+                                             position=request.total_tokens() - 1))
+                owners.append(request)
+        if owners:
+            tokens = self.backend.sample(logits, params)
+            for request, token in zip(owners, tokens):
+                request.generated.append(int(token))
+
+        if self.audit_enabled:
+            self.cache.audit()
+
+        for request in owners:
+            if len(request.generated) >= request.max_new_tokens or request.generated[-1] in self.eos:
+                request.finished = True
+                self.running.remove(request)
+                self.done.append(request)
+                if self.prefix is not None:
+                    group = self.cache.paged[0]
+                    self.prefix.insert(request.context()[:request.kv_len],
+                                       group.seqs[request.uid].pages, group)
+                self.cache.release(request.uid)
+                self._event("finish", request.uid)
+        self.step_index += 1
+        return True
+
+    def run(self, max_steps: int = 1 << 30) -> dict[str, list[int]]:
+        while self.step_index < max_steps and self.step():
+            pass
+        if self.audit_enabled:
+            self.cache.audit()
+        return {r.uid: list(r.generated) for r in self.done}

@@ -1,0 +1,279 @@
+"""Python faces of the CUDA kernels in ``csrc/``.
+
+Each function checks what it is given (device, element type, contiguity,
+shapes), launches on torch's current stream and raises ``KernelError`` when the
+launcher refuses the arguments or the launch fails.  There is no CPU path: a
+tensor that is not on a CUDA device is an error, and so is a missing or
+unbuildable extension.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+EPILOGUE_STORE, EPILOGUE_RESIDUAL, EPILOGUE_SILU_MUL = 0, 1, 2
+
+_REFUSALS = {
+    -1: "unsupported element type combination",
+    -2: "a size this kernel does not take",
+    -3: "a pointer or stride that is not aligned as required",
+    -4: "needs more shared memory than the device offers",
+}
+
+DEVICE_FAULTS = {
+    1: "token id outside the embedding table (token index {d})",
+    2: "block table names a page outside the pool (at {d})",
+    3: "position outside the rotary table (token index {d})",
+    4: "a bounded wait inside a kernel ran out (code {d})",
+    5: "row index outside its tensor (row {d})",
+}
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments, a launch failed, or a kernel recorded a fault."""
+
+
+_SIGNATURES = {
+    "core": {
+        "ls_embed_gather": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+        "ls_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                       c_float, c_void_p, c_void_p],
+        "ls_qk_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                  c_void_p, c_void_p],
+        "ls_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "ls_gemm_nt_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                            c_int64, c_int64, c_int64, c_int, c_void_p],
+        "ls_attention_split_size": [],
+        "ls_attention_tile": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                              c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_float, c_void_p, c_void_p],
+        "ls_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                c_void_p, c_void_p],
+        "ls_attention_combine": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                 c_void_p],
+        "ls_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "ls_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                      c_int, c_void_p],
+    },
+}
+
+_libs: dict[str, ctypes.CDLL] = {}
+
+
+def library(name: str = "core") -> ctypes.CDLL:
+    """The loaded extension library `name` (compiled at first use)."""
+    lib = _libs.get(name)
+    if lib is None:
+        lib = _build.load(name)
+        for fn, argtypes in _SIGNATURES.get(name, {}).items():
+            f = getattr(lib, fn)
+            f.argtypes = argtypes
+            f.restype = c_int
+        _libs[name] = lib
+    return lib
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError(
+            "lockstep_b200 runs on a CUDA device only (sm_100a); there is no CPU fallback")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"element type {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device; there is no CPU fallback")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _opt(t, name, dtype=None) -> int:
+    return 0 if t is None else _dev(t, name, dtype)
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{what}: {_REFUSALS.get(status, f'refused with code {status}')}")
+    raise KernelError(f"{what}: CUDA launch failed with error {status}")
+
+
+def new_error_word(device) -> torch.Tensor:
+    """Two int32 on the device: the first fault a kernel recorded and its detail."""
+    return torch.zeros(2, dtype=torch.int32, device=device)
+
+
+def raise_on_fault(err: torch.Tensor) -> None:
+    """Read the error word (synchronises) and raise if a kernel recorded a fault."""
+    code, detail = err.tolist()
+    if code != 0:
+        err.zero_()
+        raise KernelError("device fault: " + DEVICE_FAULTS.get(code, "code {d}").format(d=detail))
+
+
+# ---------------------------------------------------------------------------
+
+def attention_split_size() -> int:
+    return int(library().ls_attention_split_size())
+
+
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor) -> None:
+    tokens, width = out.shape
+    if ids.numel() != tokens or table.shape[1] != width:
+        raise KernelError("embed_gather: shapes do not agree")
+    _check(library().ls_embed_gather(
+        _dev(ids, "ids", torch.int32), _dev(table, "table"), _code(table),
+        _dev(out, "out", torch.float32), tokens, width, table.shape[0], _dev(err, "err", torch.int32),
+        _stream()), "embed_gather")
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float, err: torch.Tensor,
+            row_index: torch.Tensor | None = None) -> None:
+    rows, width = out.shape
+    if x.shape[1] != width or gain.numel() != width:
+        raise KernelError("rmsnorm: shapes do not agree")
+    if row_index is None and x.shape[0] != rows:
+        raise KernelError("rmsnorm: row counts do not agree")
+    if row_index is not None and row_index.numel() != rows:
+        raise KernelError("rmsnorm: row_index does not match the output rows")
+    _check(library().ls_rmsnorm(
+        _dev(x, "x", torch.float32), _opt(row_index, "row_index", torch.int32), _dev(gain, "gain"),
+        _code(gain), _dev(out, "out"), _code(out), rows, width, x.shape[0], float(eps),
+        _dev(err, "err", torch.int32), _stream()), "rmsnorm")
+
+
+def qk_norm_rope_store(qkv, q_out, pages, q_gain, k_gain, cos, sin, positions, token_req,
+                       block_table, nq: int, nkv: int, d: int, rot_dim: int, eps: float,
+                       write_cache: bool, err) -> None:
+    """pages: [num_pages, 2, nkv, page_size, d] of one cache layer (may be None if not written)."""
+    tokens = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * d or q_out.shape != (tokens, nq * d):
+        raise KernelError("qk_norm_rope_store: shapes do not agree")
+    if (q_gain is None) != (k_gain is None):
+        raise KernelError("qk_norm_rope_store: q and k gains come together")
+    if write_cache:
+        if pages.dtype != qkv.dtype or pages.shape[1:3] != (2, nkv) or pages.shape[4] != d:
+            raise KernelError("qk_norm_rope_store: cache pages do not match the projections")
+        num_pages, page_size = pages.shape[0], pages.shape[3]
+    else:
+        num_pages, page_size = 0, 1
+    half = rot_dim // 2
+    if rot_dim:
+        if cos.shape != sin.shape or cos.shape[1] != half:
+            raise KernelError("qk_norm_rope_store: rotary tables do not match rot_dim")
+    gain_code = _code(q_gain) if q_gain is not None else F32
+    if q_gain is not None and (q_gain.dtype != k_gain.dtype or q_gain.numel() != d or k_gain.numel() != d):
+        raise KernelError("qk_norm_rope_store: gains do not match the head size")
+    _check(library().ls_qk_norm_rope_store(
+        _dev(qkv, "qkv"), _dev(q_out, "q_out", qkv.dtype), _opt(pages if write_cache else None, "pages"),
+        _code(qkv), _opt(q_gain, "q_gain"), _opt(k_gain, "k_gain"), gain_code,
+        _opt(cos if rot_dim else None, "cos", torch.float32),
+        _opt(sin if rot_dim else None, "sin", torch.float32),
+        _dev(positions, "positions", torch.int32), _dev(token_req, "token_req", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[-1], tokens, nq, nkv, d,
+        rot_dim, page_size, num_pages, cos.shape[0] if rot_dim else 0, float(eps),
+        1 if write_cache else 0, _dev(err, "err", torch.int32), _stream()), "qk_norm_rope_store")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    rows, width = out.shape
+    if gate_up.shape != (rows, 2 * width) or gate_up.dtype != out.dtype:
+        raise KernelError("silu_mul: shapes do not agree")
+    _check(library().ls_silu_mul(_dev(gate_up, "gate_up"), _dev(out, "out"), _code(out), rows, width,
+                                 _stream()), "silu_mul")
+
+
+def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> None:
+    """c = a @ w.T on the CUDA cores with the chosen epilogue (see csrc/gemm_simt.cu)."""
+    m, k = a.shape
+    n = c.shape[1]
+    rows_w = 2 * n if epilogue == EPILOGUE_SILU_MUL else n
+    if w.shape != (rows_w, k) or c.shape[0] != m or a.dtype != w.dtype:
+        raise KernelError(f"gemm_nt: shapes do not agree: a {tuple(a.shape)} w {tuple(w.shape)} c {tuple(c.shape)}")
+    _check(library().ls_gemm_nt_simt(
+        _dev(a, "a"), _dev(w, "w"), _dev(c, "c"), _code(a), _code(c), m, n, k, k, k, n, epilogue,
+        _stream()), "gemm_nt_simt")
+
+
+def attention_tile(q, pages, out, part_acc, part_ml, work, n_work, block_table, nq, nkv, d,
+                   window, scale, err) -> None:
+    _check(library().ls_attention_tile(
+        _dev(q, "q"), _dev(pages, "pages", q.dtype), _opt(out, "out", q.dtype),
+        _opt(part_acc, "part_acc", torch.float32), _opt(part_ml, "part_ml", torch.float32), _code(q),
+        _dev(work, "work", torch.int32), n_work, _dev(block_table, "block_table", torch.int32),
+        block_table.shape[-1], nq, nkv, d, pages.shape[3], pages.shape[0], int(window), float(scale),
+        _dev(err, "err", torch.int32), _stream()), "attention_tile")
+
+
+def attention_decode(q, pages, part_acc, part_ml, work, n_work, block_table, nq, nkv, d, window,
+                     scale, err) -> bool:
+    """Returns False (and launches nothing) for shapes the decode kernel does not take."""
+    status = library().ls_attention_decode(
+        _dev(q, "q"), _dev(pages, "pages", q.dtype), _dev(part_acc, "part_acc", torch.float32),
+        _dev(part_ml, "part_ml", torch.float32), _code(q), _dev(work, "work", torch.int32), n_work,
+        _dev(block_table, "block_table", torch.int32), block_table.shape[-1], nq, nkv, d,
+        pages.shape[3], pages.shape[0], int(window), float(scale), _dev(err, "err", torch.int32),
+        _stream())
+    if status == -2:
+        return False
+    _check(status, "attention_decode")
+    return True
+
+
+def attention_combine(part_acc, part_ml, out, items, n_items, nq, d) -> None:
+    _check(library().ls_attention_combine(
+        _dev(part_acc, "part_acc", torch.float32), _dev(part_ml, "part_ml", torch.float32),
+        _dev(out, "out"), _code(out), _dev(items, "items", torch.int32), n_items, nq, d, _stream()),
+        "attention_combine")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    rows, vocab = logits.shape
+    _check(library().ls_argmax(_dev(logits, "logits", torch.float32), _dev(out, "out", torch.int32),
+                               rows, vocab, _stream()), "argmax")
+
+
+def sample(logits, probs, temperature, top_p, keys, positions, out) -> None:
+    """keys, positions: [rows, 2] int32 holding the low and high 32 bits."""
+    rows, vocab = logits.shape
+    if probs.shape != logits.shape:
+        raise KernelError("sample: probs scratch does not match the logits")
+    _check(library().ls_sample(
+        _dev(logits, "logits", torch.float32), _dev(probs, "probs", torch.float32),
+        _dev(temperature, "temperature", torch.float32), _dev(top_p, "top_p", torch.float32),
+        _dev(keys, "keys", torch.int32), _dev(positions, "positions", torch.int32),
+        _dev(out, "out", torch.int32), rows, vocab, _stream()), "sample")
+
+
+def gemm_nt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> None:
+    """c = a @ w.T with float32 accumulation and the chosen epilogue.
+
+    a [m, k] and w [n, k] (or [2n, k] for the silu-mul epilogue) share an element
+    type; c is [m, n] in that type, or float32 (always for the residual epilogue,
+    where the product is added into c in place)."""
+    gemm_nt_simt(a, w, c, epilogue)

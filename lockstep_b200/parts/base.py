@@ -1,0 +1,149 @@
+"""Interfaces of the parts a layer is put together from.
+
+A part is built from a ``PartSpec`` (its sizes and constants) and a
+``Runtime`` (device, element type, page size, error word).  It declares the
+tensors it needs with names relative to its own prefix, receives them in
+``bind``, and does its work in ``forward``.  No part knows which model it is in.
+
+Shapes: ``x`` and the outputs of norms are [tokens, width] in the engine's
+element type; the residual stream ``h`` is [tokens, hidden] float32, and a
+mixer or feed-forward adds its result into it in place.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Mapping
+
+import torch
+
+from ..config.spec import PartSpec
+
+
+@dataclass(frozen=True)
+class WeightSpec:
+    """A tensor a part needs.  role: "matrix" (used in a product), "table"
+    (looked up by integer id) or "gain" (a norm's scale vector)."""
+
+    shape: tuple[int, ...]
+    role: str = "matrix"
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """What a mixer keeps between steps.
+
+    kind "paged_kv": keys and values of ``kv_heads`` x ``head_dim`` per token in
+    pages; ``window`` > 0 means only the last ``window`` positions are read, so
+    pages behind it can be given back.  kind "state": one tensor of
+    ``state_shape`` per request, of fixed size, in a slot.
+    """
+
+    kind: str
+    kv_heads: int = 0
+    head_dim: int = 0
+    window: int = 0
+    state_shape: tuple[int, ...] = ()
+    state_dtype: torch.dtype = torch.float32
+
+    def group_key(self):
+        if self.kind == "paged_kv":
+            return ("paged_kv", self.kv_heads, self.head_dim, self.window)
+        return ("state", tuple(self.state_shape), str(self.state_dtype))
+
+
+@dataclass
+class Runtime:
+    """What every part of one model shares."""
+
+    device: torch.device
+    dtype: torch.dtype
+    page_size: int
+    max_positions: int
+    err: torch.Tensor            # int32[2] device error word
+    options: dict = field(default_factory=dict)
+
+
+class Part:
+    """Base of all parts."""
+
+    def weight_specs(self) -> dict[str, WeightSpec]:
+        return {}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        if tensors:
+            raise ValueError(f"{type(self).__name__} takes no weights")
+
+
+class Norm(Part):
+    def forward(self, h: torch.Tensor, row_index: torch.Tensor | None = None) -> torch.Tensor:
+        """Normalise float32 rows of ``h`` (all, or those ``row_index`` names) into
+        a new tensor of the engine's element type."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotary(self):
+        """(cos, sin, rot_dim) tables [max_positions, rot_dim/2] for a mixer that
+        rotates its queries and keys, or None."""
+        return None
+
+
+class Mixer(Part):
+    def cache_need(self) -> CacheNeed | None:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache, residual: torch.Tensor) -> None:
+        """Mix tokens of ``x`` [tokens, hidden] (using and updating ``cache``) and
+        add the result into ``residual`` [tokens, hidden] float32."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Block(Part):
+    def cache_need(self) -> CacheNeed | None:
+        raise NotImplementedError
+
+    def forward(self, h: torch.Tensor, ctx, cache) -> None:
+        """Run the layer on the residual stream ``h`` in place."""
+        raise NotImplementedError
+
+
+# ---------------------------------------------------------------------------
+# registries: (category, kind) -> builder(spec, runtime, **extra) -> Part
+# ---------------------------------------------------------------------------
+
+CATEGORIES = ("block", "mixer", "feed_forward", "norm", "position", "embedding", "head")
+_BUILDERS: dict[tuple[str, str], Callable[..., Part]] = {}
+
+
+def register_part(category: str, kind: str):
+    if category not in CATEGORIES:
+        raise ValueError(f"unknown part category {category!r}; one of {CATEGORIES}")
+
+    def wrap(builder):
+        _BUILDERS[(category, kind)] = builder
+        return builder
+
+    return wrap
+
+
+def unregister_part(category: str, kind: str) -> None:
+    _BUILDERS.pop((category, kind), None)
+
+
+def build_part(category: str, spec: PartSpec, runtime: Runtime, **extra: Any) -> Part:
+    try:
+        builder = _BUILDERS[(category, spec.kind)]
+    except KeyError:
+        known = sorted(k for c, k in _BUILDERS if c == category)
+        raise KeyError(f"no {category} part is registered as {spec.kind!r}; known: {known}") from None
+    return builder(spec, runtime, **extra)
+
+
+def known_parts(category: str) -> list[str]:
+    return sorted(k for c, k in _BUILDERS if c == category)

@@ -1,0 +1,55 @@
+"""Arrangement of a layer's parts.  "pre_norm":
+h += mixer(norm_a(h)); h += feed_forward(norm_b(h))  (LockStep: engine/model/qwen3.py:242-287).
+The names under which the layer's tensors are stored are parameters of the
+arrangement, so the same arrangement serves architectures that name them otherwise."""
+
+from __future__ import annotations
+
+from .base import Block, Runtime, build_part, register_part
+
+_DEFAULT_NAMES = {
+    "mixer_norm": "input_layernorm",
+    "mixer": "self_attn",
+    "feed_forward_norm": "post_attention_layernorm",
+    "feed_forward": "mlp",
+}
+
+
+class PreNormBlock(Block):
+    def __init__(self, layer_spec, runtime: Runtime):
+        names = dict(_DEFAULT_NAMES)
+        names.update(layer_spec.block.get("names", {}) or {})
+        self.names = names
+        self.position = build_part("position", layer_spec.position, runtime)
+        self.mixer_norm = build_part("norm", layer_spec.mixer_norm, runtime)
+        self.mixer = build_part("mixer", layer_spec.mixer, runtime, position=self.position)
+        self.feed_forward_norm = build_part("norm", layer_spec.feed_forward_norm, runtime)
+        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, runtime)
+
+    def _children(self):
+        return [(self.names[k], getattr(self, k)) for k in _DEFAULT_NAMES]
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def weight_specs(self):
+        out = {}
+        for name, part in self._children():
+            for local, spec in part.weight_specs().items():
+                out[f"{name}.{local}"] = spec
+        return out
+
+    def bind(self, tensors):
+        for name, part in self._children():
+            own = {k[len(name) + 1:]: v for k, v in tensors.items() if k.startswith(name + ".")}
+            if own or part.weight_specs():
+                part.bind(own)
+
+    def forward(self, h, ctx, cache):
+        self.mixer.forward(self.mixer_norm.forward(h), ctx, cache, h)
+        self.feed_forward.forward(self.feed_forward_norm.forward(h), ctx, h)
+
+
+@register_part("block", "pre_norm")
+def _build(spec, runtime, layer_spec=None, **_):
+    return PreNormBlock(layer_spec, runtime)
