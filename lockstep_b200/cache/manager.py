@@ -252,6 +252,19 @@ class CacheManager:
             g.clear(slot)
         return slot
 
+    def peak_pages(self, total_tokens: int, max_portion: int) -> int:
+        """The most pages a request of ``total_tokens`` holds in any group at any
+        time when no step runs more than ``max_portion`` of its tokens: all of
+        them where every key is kept; the window, the portion and one page of
+        slack where pages behind the window are given back."""
+        worst = 0
+        for g in self.paged:
+            need = -(-total_tokens // self.page_size)
+            if g.window and total_tokens > max_portion:
+                need = min(need, -(-(g.window - 1 + max_portion) // self.page_size) + 1)
+            worst = max(worst, need)
+        return worst
+
     def pages_short(self, uid: str, total_tokens: int) -> int:
         """The most new pages any group needs to hold ``total_tokens`` of ``uid``."""
         return max((g.pages_short(uid, total_tokens) for g in self.paged), default=0)

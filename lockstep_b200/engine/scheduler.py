@@ -89,7 +89,7 @@ class Scheduler:
         self.events.append((self.step_index, name, uid, tuple(detail)))
 
     def _pages_for(self, tokens: int) -> int:
-        return -(-tokens // self.cache.page_size)
+        return self.cache.peak_pages(tokens, min(tokens, self.max_step_tokens))
 
     def _reclaimable(self) -> int:
         return len(self.prefix.evictable(self.cache.paged[0])) if self.prefix else 0

@@ -1,0 +1,151 @@
+"""The cache manager's books (no device): no page lost, held twice or freed twice,
+under random orders of requests; windows give pages back; slots; prefix reuse."""
+
+from __future__ import annotations
+
+import random
+
+import pytest
+
+from lockstep_b200.cache import AuditFailure, CacheManager, OutOfPages, PageAllocator, PrefixIndex
+from lockstep_b200.parts import CacheNeed
+
+FULL = CacheNeed("paged_kv", kv_heads=2, head_dim=16, window=0)
+WIN = CacheNeed("paged_kv", kv_heads=2, head_dim=16, window=40)
+STATE = CacheNeed("state", state_shape=(3, 4))
+
+
+def manager(needs, pages=32, page=8, live=4, seq=512):
+    return CacheManager(needs, num_pages=pages, page_size=page, max_live=live, max_seq_len=seq, allocate=False)
+
+
+def test_allocator_lowest_first_and_reuse():
+    a = PageAllocator(4)
+    assert [a.take() for _ in range(3)] == [0, 1, 2]
+    a.release(1)
+    assert a.take() == 1 and a.stats["reused"] == 1
+    a.take()
+    with pytest.raises(OutOfPages):
+        a.take()
+    a.release(0)
+    with pytest.raises(AuditFailure):
+        a.release(0)          # freed twice
+
+
+def test_audit_catches_lost_and_double_held_pages():
+    m = manager([FULL, FULL])
+    m.create("a")
+    m.reserve("a", 20)
+    m.audit()
+    g = m.paged[0]
+    g.allocator.refcount[g.seqs["a"].pages[0]] += 1        # a reference nobody holds
+    with pytest.raises(AuditFailure):
+        m.audit()
+    g.allocator.refcount[g.seqs["a"].pages[0]] -= 1
+    g.seqs["a"].pages[1] = g.seqs["a"].pages[0]             # one page under two logical places
+    with pytest.raises(AuditFailure):
+        m.audit()
+
+
+def test_groups_by_need_have_pages_of_their_own():
+    m = manager([FULL, WIN, WIN, FULL, STATE, None])
+    assert len(m.paged) == 2 and len(m.states) == 1
+    assert sorted(tuple(g.entries) for g in m.paged) == [(0, 3), (1, 2)]
+    m.create("a")
+    m.reserve("a", 100)
+    full = next(g for g in m.paged if not g.window)
+    win = next(g for g in m.paged if g.window)
+    assert full.allocator.free_pages == 32 - 13 and win.allocator.free_pages == 32 - 13
+    freed = m.advance("a", 100)
+    # positions < 100 - 40 + 1 = 61 are behind every later query: pages 0..6 (7 * 8 = 56 <= 61)
+    assert freed == 7 and win.allocator.free_pages == 32 - 6 and full.allocator.free_pages == 32 - 13
+    assert win.seqs["a"].pages[:7] == [-1] * 7
+    m.audit()
+    m.reserve("a", 101)
+    m.release("a")
+    m.audit()
+    assert m.free_pages() == 32 and m.live == 0
+
+
+def test_reserve_takes_nothing_when_a_group_is_short():
+    m = manager([FULL, WIN], pages=4, page=8)
+    m.create("a")
+    m.reserve("a", 30)
+    m.create("b")
+    with pytest.raises(OutOfPages):
+        m.reserve("b", 9)
+    m.audit()
+    assert all(len(g.seqs["b"].pages) == 0 for g in m.paged)
+
+
+def test_slots_are_unique_and_returned():
+    m = manager([FULL], live=3)
+    slots = [m.create(u) for u in "abc"]
+    assert sorted(slots) == [0, 1, 2] and not m.has_slot()
+    with pytest.raises(OutOfPages):
+        m.create("d")
+    m.release("b")
+    assert m.create("d") == slots[1]
+    m.audit()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_the_books(seed):
+    rng = random.Random(seed)
+    m = manager([FULL, WIN, FULL], pages=24, page=8, live=4, seq=400)
+    live: dict[str, int] = {}
+    n = 0
+    for _ in range(600):
+        op = rng.random()
+        if op < 0.25 and m.has_slot():
+            uid = f"r{n}"
+            n += 1
+            m.create(uid)
+            live[uid] = 0
+        elif op < 0.8 and live:
+            uid = rng.choice(sorted(live))
+            grow = live[uid] + rng.choice([1, 1, 1, 2, 7, 19, 40])
+            if grow <= 400 and m.can_reserve(uid, grow):
+                m.reserve(uid, grow)
+                m.advance(uid, grow)
+                live[uid] = grow
+            elif grow <= 400:
+                with pytest.raises(OutOfPages):
+                    m.reserve(uid, grow)
+        elif live:
+            uid = rng.choice(sorted(live))
+            m.release(uid)
+            del live[uid]
+        m.audit()
+        for g in m.paged:
+            held = sum(1 for s in g.seqs.values() for p in s.pages if p >= 0)
+            assert held + g.allocator.free_pages == g.allocator.num_pages
+    for uid in list(live):
+        m.release(uid)
+    m.audit()
+    assert m.free_pages() == 24 and m.reused_pages() > 0
+
+
+def test_prefix_index_shares_whole_pages():
+    m = manager([FULL], pages=16, page=4)
+    g = m.paged[0]
+    idx = PrefixIndex(page_size=4)
+    toks = list(range(11))
+    m.create("a")
+    m.reserve("a", 11)
+    assert idx.insert(toks, g.seqs["a"].pages, g) == 2      # two whole pages
+    m.release("a")
+    m.audit()
+    assert g.allocator.free_pages == 14 and idx.evictable(g) == [0, 1]
+    hit, pages = idx.lookup(toks[:9] + [99, 98])
+    assert hit == 8 and pages == [0, 1]
+    m.create("b")
+    g.adopt("b", pages)
+    m.reserve("b", 11)
+    m.audit()
+    assert idx.evictable(g) == []                          # a running request holds them
+    m.release("b")
+    assert idx.evict(0, g) and idx.evict(1, g)
+    m.audit()
+    assert g.allocator.free_pages == 16
+    assert idx.lookup(toks)[0] == 0

@@ -1,0 +1,208 @@
+"""The scheduler's decisions, on the host: a fake step function stands in for the model.
+
+The fake's next token depends on the request's whole context, so any token that
+the scheduler loses, repeats or feeds at a wrong position changes the output.
+"""
+
+from __future__ import annotations
+
+import pytest
+
+from lockstep_b200.cache import CacheManager, OutOfPages
+from lockstep_b200.engine import (FixedChunkPolicy, OversizedRequest, Request, Scheduler, ScriptedPolicy)
+from lockstep_b200.parts import CacheNeed
+
+VOCAB = 97
+
+
+def next_token(context):
+    h = 7
+    for i, t in enumerate(context):
+        h = (h * 31 + t * (i + 1)) % 1000003
+    return h % VOCAB
+
+
+class FakeBackend:
+    def __init__(self, pages=64, page=4, live=8, seq=4096, window=0):
+        need = CacheNeed("paged_kv", kv_heads=1, head_dim=16, window=window)
+        self.cache = CacheManager([need], num_pages=pages, page_size=page, max_live=live,
+                                  max_seq_len=seq, allocate=False)
+        self.history: dict[str, list[int]] = {}
+        self.steps: list[list[tuple[str, int, int]]] = []
+        self.sampled = []
+
+    def step(self, entries):
+        out = []
+        self.steps.append([(e.uid, e.start, len(e.tokens)) for e in entries])
+        for e in entries:
+            hist = self.history.setdefault(e.uid, [])
+            if e.start < len(hist):        # recomputed after a preemption or a prefix hit
+                del hist[e.start:]
+            if e.start > len(hist):        # a prefix hit: the shared pages hold these tokens
+                hist.extend([None] * (e.start - len(hist)))
+            assert e.start == len(hist) == self.cache.lengths[e.uid]
+            hist.extend(e.tokens)
+            self.cache.reserve(e.uid, e.start + len(e.tokens))
+            self.cache.advance(e.uid, e.start + len(e.tokens))
+            for w in e.want:
+                assert w == len(e.tokens) - 1
+                out.append(e.uid)
+        return out
+
+    def sample(self, logits, params):
+        self.sampled.extend(params)
+        return [next_token(self._context[p.uid]()) for p in params]
+
+
+def run(requests, **kw):
+    backend_kw = {k: kw.pop(k) for k in ("pages", "page", "live", "seq", "window") if k in kw}
+    backend = FakeBackend(**backend_kw)
+    sched = Scheduler(backend, audit=True, **kw)
+    backend._context = {}
+    for r in requests:
+        backend._context[r.uid] = r.context
+        sched.submit(r)
+    out = sched.run(max_steps=10000)
+    return out, sched, backend
+
+
+def expected(prompt, n, eos=()):
+    ctx, out = list(prompt), []
+    for _ in range(n):
+        t = next_token(ctx)
+        out.append(t)
+        ctx.append(t)
+        if t in eos:
+            break
+    return out
+
+
+def make(n=5, new=9):
+    return [Request(uid=f"r{i}", prompt=[(3 * i + 5 * j) % VOCAB for j in range(3 + 11 * i)],
+                    max_new_tokens=new + i) for i in range(n)]
+
+
+def test_generation_is_right_and_budget_is_kept():
+    for budget in (1, 3, 8, 64, 4096):
+        out, sched, backend = run(make(), max_step_tokens=budget)
+        for r in make():
+            assert out[r.uid] == expected(r.prompt, r.max_new_tokens), (budget, r.uid)
+        assert all(sum(n for _, _, n in step) <= budget for step in backend.steps)
+        assert sched.cache.free_pages() == sched.cache.total_pages()
+
+
+def test_decoding_requests_go_first_and_prompts_are_cut():
+    reqs = [Request("short", [1, 2], max_new_tokens=20), Request("long", list(range(50)), max_new_tokens=2)]
+    out, sched, backend = run(reqs, max_step_tokens=8)
+    mixed = [s for s in backend.steps if {n == 1 for _, _, n in s} == {True, False}]
+    assert mixed and sched.stats["mixed_steps"] == len(mixed)
+    for step in mixed:
+        assert step[0][0] == "short" and step[0][2] == 1     # the decoded token leads
+        assert step[1][0] == "long" and step[1][2] <= 7      # the prompt gets the rest of the budget
+    assert sum(step[1][2] == 7 for step in mixed) >= 5
+    assert sched.stats["budget_cuts"] > 0
+    assert out["long"] == expected(list(range(50)), 2)
+
+
+def test_portions_follow_the_policy_down_to_two_tokens():
+    reqs = [Request("a", list(range(40)), max_new_tokens=3)]
+    out, sched, backend = run(reqs, policy=ScriptedPolicy(chunk_plan=(7, 2, 17, 2)))
+    sizes = [n for step in backend.steps for _, _, n in step]
+    assert sizes[:5] == [7, 2, 17, 2, 7] and out["a"] == expected(list(range(40)), 3)
+    out2, _, b2 = run([Request("a", list(range(40)), max_new_tokens=3)], policy=FixedChunkPolicy(16))
+    assert [n for s in b2.steps for _, _, n in s][:3] == [16, 16, 8] and out2 == out
+
+
+def test_when_pages_run_out_the_youngest_is_preempted_and_recomputed():
+    reqs = make(4, new=30)
+    # 12 pages of 4 tokens: the four requests need far more together than the pool has
+    out, sched, backend = run(reqs, pages=24, page=4, max_step_tokens=16)
+    assert sched.stats["preemptions"] > 0
+    for r in make(4, new=30):
+        assert out[r.uid] == expected(r.prompt, r.max_new_tokens), r.uid
+    victims = [e[2] for e in sched.events if e[1] == "preempt"]
+    assert "r0" not in victims                     # the oldest request is never the victim
+    resumed = [e[2] for e in sched.events if e[1] == "resume"]
+    assert set(resumed) == set(victims)
+    assert sched.cache.free_pages() == 24 and sched.cache.reused_pages() > 0
+
+
+def test_oversized_request_is_refused_at_submit():
+    backend = FakeBackend(pages=4, page=4)
+    sched = Scheduler(backend)
+    with pytest.raises(OversizedRequest, match="needs 5 pages"):
+        sched.submit(Request("big", list(range(10)), max_new_tokens=8))
+    with pytest.raises(ValueError, match="empty"):
+        sched.submit(Request("none", []))
+
+
+def test_a_request_that_cannot_run_alone_raises():
+    backend = FakeBackend(pages=4, page=4)
+    sched = Scheduler(backend)
+    backend._context = {}
+    r = Request("a", list(range(10)), max_new_tokens=6)
+    backend._context["a"] = r.context
+    sched.submit(r)
+    backend.cache.paged[0].allocator.take()        # a page that nothing will give back
+    with pytest.raises(OutOfPages):
+        sched.run()
+
+
+def test_requests_wait_for_a_slot():
+    out, sched, backend = run(make(6, new=4), live=2)
+    assert max(len(s) for s in backend.steps) <= 2
+    for r in make(6, new=4):
+        assert out[r.uid] == expected(r.prompt, r.max_new_tokens)
+
+
+def test_eos_finishes_early():
+    r = Request("a", [5, 6, 7], max_new_tokens=50)
+    full = expected(r.prompt, 50)
+    eos = full[4]
+    out, _, _ = run([r], eos_token_ids={eos})
+    assert out["a"] == full[:full.index(eos) + 1]
+
+
+def test_sampling_parameters_and_position():
+    r = Request("a", [1, 2, 3, 4], seed=9, max_new_tokens=3, temperature=0.7, top_p=0.9)
+    _, _, backend = run([r])
+    assert [(p.position, p.seed, p.temperature, p.top_p) for p in backend.sampled] == \
+        [(3, 9, 0.7, 0.9), (4, 9, 0.7, 0.9), (5, 9, 0.7, 0.9)]
+
+
+def test_scripted_preemption_recomputes_the_context():
+    reqs = [Request("a", list(range(9)), max_new_tokens=8), Request("b", [4, 4], max_new_tokens=8)]
+    out, sched, backend = run(reqs, policy=ScriptedPolicy(preempt_at=[(3, "a")]))
+    assert [e[2] for e in sched.events if e[1] == "preempt"] == ["a"]
+    assert out["a"] == expected(list(range(9)), 8) and out["b"] == expected([4, 4], 8)
+    again = [s for s in backend.steps if any(u == "a" and start == 0 for u, start, _ in s)]
+    assert len(again) == 2                         # the prompt and, later, the whole context again
+
+
+def test_prefix_reuse_skips_shared_pages_and_evicts_under_pressure():
+    shared = list(range(20))
+    first = Request("a", shared + [50, 51], max_new_tokens=4)
+    out, sched, backend = run([first], pages=16, page=4, enable_prefix_cache=True)
+    second = Request("b", shared + [60], max_new_tokens=4)
+    backend._context["b"] = second.context
+    sched.submit(second)
+    sched.run()
+    starts = [start for step in backend.steps for u, start, _ in step if u == "b"]
+    assert starts[0] == 20 and second.cache_hit_tokens == 20     # five whole pages were adopted
+    assert second.generated == expected(second.prompt, 4)
+    big = Request("c", [9] * 40, max_new_tokens=8)               # needs the cached pages' room
+    backend._context["c"] = big.context
+    sched.submit(big)
+    sched.run()
+    assert sched.stats["evictions"] > 0 and big.generated == expected(big.prompt, 8)
+    sched.cache.audit()
+
+
+def test_windowed_group_frees_pages_while_decoding():
+    r = Request("a", list(range(30)), max_new_tokens=60)
+    out, sched, backend = run([r], pages=8, page=4, window=12, seq=128, max_step_tokens=16)
+    assert out["a"] == expected(r.prompt, 60)      # 90 tokens went through 8 pages of 4
+    with pytest.raises(OversizedRequest):          # a portion of 64 beside the window needs more
+        run([Request("a", list(range(30)), max_new_tokens=60)], pages=8, page=4, window=12, seq=128,
+            max_step_tokens=64)
+    assert sched.cache.reused_pages() > 0
