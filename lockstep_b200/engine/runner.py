@@ -72,6 +72,21 @@ class ModelRunner:
     def kv_len(self, uid: str) -> int:
         return self.cache.lengths[uid]
 
+    def fill_random(self, uid: str, tokens: int, seed: int = 0) -> None:
+        """Give the open request ``uid`` a context of ``tokens`` positions whose keys
+        and values are random numbers, without running the model (for timing decode
+        steps at a long context; the values do not change a step's work)."""
+        if self.cache.lengths[uid] != 0:
+            raise ValueError(f"{uid} already holds tokens")
+        self.cache.reserve(uid, tokens)
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        for group in self.cache.paged:
+            ids = torch.tensor([p for p in group.seqs[uid].pages if p >= 0], device=self.device)
+            shape = (group.pages.shape[0], ids.numel(), *group.pages.shape[2:])
+            group.pages[:, ids] = torch.randn(shape, generator=gen, device=self.device,
+                                              dtype=torch.float32).to(group.pages.dtype)
+        self.cache.advance(uid, tokens)
+
     # -- the step -----------------------------------------------------------
     @torch.no_grad()
     def step(self, entries: list[StepEntry], check: bool = True) -> torch.Tensor:

@@ -115,8 +115,13 @@ def _opt(t, name, dtype=None) -> int:
     return 0 if t is None else _dev(t, name, dtype)
 
 
+# launcher calls since the counter was last cleared (each is at least one kernel)
+LAUNCHES = [0]
+
+
 def _check(status: int, what: str) -> None:
     if status == 0:
+        LAUNCHES[0] += 1
         return
     if status < 0:
         raise KernelError(f"{what}: {_REFUSALS.get(status, f'refused with code {status}')}")

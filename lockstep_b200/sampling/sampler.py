@@ -37,15 +37,21 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, params: list[SamplingParams]) -> list[int]:
         """One token per row of ``logits`` [rows, vocab] (float32, on the device)."""
+        if logits.shape[0] == 0:
+            return []
+        return self.sample_device(logits, params).tolist()
+
+    def sample_device(self, logits: torch.Tensor, params: list[SamplingParams]) -> torch.Tensor:
+        """As ``sample``, but the tokens stay on the device (int32 [rows])."""
         rows, vocab = logits.shape
         if rows != len(params):
             raise ValueError("one SamplingParams per row of logits")
-        if rows == 0:
-            return []
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        if rows == 0:
+            return out
         if all(p.temperature <= 0 for p in params):
             K.argmax(logits, out)
-            return out.tolist()
+            return out
         for p in params:
             if p.temperature > 0 and not 0 < p.top_p <= 1:
                 raise ValueError(f"{p.uid}: top_p must lie in (0, 1], got {p.top_p}")
@@ -62,4 +68,4 @@ class Sampler:
         if self._probs is None or self._probs.shape[0] < rows or self._probs.shape[1] != vocab:
             self._probs = torch.empty((rows, vocab), dtype=torch.float32, device=self.device)
         K.sample(logits, self._probs[:rows], temperature, top_p, keys, positions, out)
-        return out.tolist()
+        return out
