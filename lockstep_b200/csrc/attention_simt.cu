@@ -479,3 +479,60 @@ LS_API int ls_attention_combine(const float* part_acc, const float* part_ml, voi
     return LS_E_DTYPE;
   return ls_launch_status();
 }
+
+// --------------------------------------------------------------------------
+// The entry point that allocates nothing (see no_alloc.h).
+// --------------------------------------------------------------------------
+#include <mutex>
+
+#include "no_alloc.h"
+
+namespace {
+
+// Partial results of ls_attention_decode_noalloc.  In host code this name is
+// only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float ls_noalloc_scratch[LS_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+std::mutex noalloc_mutex;
+
+// Device address of the scratch on the current device, looked up once per device.
+int noalloc_scratch(float** ptr) {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= NOALLOC_MAX_DEVICES)
+    return LS_E_NOALLOC_SETUP;
+  std::lock_guard<std::mutex> guard(noalloc_mutex);
+  if (noalloc_ptr[device] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, ls_noalloc_scratch) != cudaSuccess || p == nullptr)
+      return LS_E_NOALLOC_SETUP;
+    noalloc_ptr[device] = p;
+  }
+  *ptr = noalloc_ptr[device];
+  return 0;
+}
+
+}  // namespace
+
+LS_API int ls_attention_decode_noalloc(const void* q, const void* pages, void* out, int dtype,
+                                       const int* work, int n_work, const int* combine,
+                                       int n_combine, int n_slots, const int* block_table,
+                                       int table_stride, int nq, int nkv, int d, int page_size,
+                                       int num_pages, int window, float scale, int* err,
+                                       cudaStream_t stream) {
+  if (n_work <= 0 || n_combine <= 0) return 0;
+  if (n_slots <= 0 || nq <= 0 || d <= 0) return LS_E_SIZE;
+  const long long need = (long long)n_slots * nq * (d + 2);
+  if (need > (long long)LS_NOALLOC_SCRATCH_FLOATS) return LS_E_NOALLOC_TOO_LARGE;
+  float* scratch = nullptr;
+  const int setup = noalloc_scratch(&scratch);
+  if (setup != 0) return setup;
+  float* part_acc = scratch;                                   // [n_slots, nq, d]
+  float* part_ml = scratch + (size_t)n_slots * nq * d;         // [n_slots, nq, 2]
+  const int status = ls_attention_decode(q, pages, part_acc, part_ml, dtype, work, n_work,
+                                         block_table, table_stride, nq, nkv, d, page_size,
+                                         num_pages, window, scale, err, stream);
+  if (status != 0) return status;
+  return ls_attention_combine(part_acc, part_ml, out, dtype, combine, n_combine, nq, d, stream);
+}
