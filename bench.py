@@ -245,6 +245,15 @@ def run_ours(args):
                         max_seq_len=CONTEXT)
     runner = engine.runner
     launches = [0]
+    if args.only == "decode":
+        ms = time_decode(runner, engine.sampler, args.batch, args.context, args.steps, args.warmup, launches)
+        print(json.dumps({"only": "decode", "layers": layers, "batch": args.batch, "context": args.context,
+                          "ms_per_step": round(ms, 4), "launches": launches[0]}))
+        return 0
+    if args.only == "prefill":
+        pre_ms = time_prefill(runner, PREFILL_TOKENS, repeats=max(1, args.steps))
+        print(json.dumps({"only": "prefill", "layers": layers, "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 3)}))
+        return 0
     clocks = ClockSampler()
     points = {}
     for b in batches:
@@ -302,6 +311,9 @@ def main():
     ap.add_argument("--layers", type=int, default=0,
                     help="run fewer layers than the model has (named in config)")
     ap.add_argument("--quick", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="time only this part and print a short line (for profiling a small case)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="context length of the decode steps")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this engine")
