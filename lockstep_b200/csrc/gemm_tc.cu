@@ -1,0 +1,377 @@
+// C[T, N] = X[T, K] * W[N, K]^T in bfloat16 on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory, operands staged by TMA).
+//
+// Orientation: the weight tile is the MMA's M side (128 rows of W), the tokens
+// are its N side (16..256 per tile), so one orientation serves a batch of one
+// decoded token and a prompt of thousands; only the token tile's width varies
+// with T.  Each block owns one 128 x BN output tile and walks all of K in
+// ascending 64-element blocks (no split-K), so an output element is the same
+// sum whatever the batch.
+//
+// Roles inside a block (192 threads): warp 0 issues TMA loads into a ring of
+// shared-memory stages, warp 1 issues the MMAs and commits stages back, warps
+// 2..5 read the accumulator from tensor memory and write the epilogue:
+//   0 store     C[t, n]  = acc                      (bfloat16 or float32)
+//   1 residual  C[t, n] += acc                      (float32, in place)
+//   2 silu-mul  C[t, n]  = silu(acc_gate) * acc_up  (W holds gate rows [0, N)
+//                                                    and up rows [N, 2N))
+// Every wait on a barrier is bounded; a wait that runs out records
+// LS_DEV_WAIT_TIMEOUT in the error word and the block winds down (waits for its
+// own copies in flight, frees its tensor memory, returns).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;           // rows of W per tile (MMA M)
+constexpr int BK = 64;            // K elements per stage: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr int A_BYTES = BM * BK * 2;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// bounded wait: false when the limit ran out
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// shared-memory matrix descriptor: K-major rows of 128 bytes with 128-byte
+// swizzle, groups of 8 rows 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// instruction descriptor: D float32, A and B bfloat16, both K-major, M x N
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                     uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+constexpr int tmem_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
+
+template <int BN, int EPI>
+struct Shape {
+  static constexpr int A_TILES = EPI == 2 ? 2 : 1;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
+  static constexpr int STAGES_FIT = (200 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
+  static constexpr int ACC_COLS = tmem_cols(A_TILES * BN);
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int BN, int EPI, typename TC>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               TC* __restrict__ C, int T, int N, int K, int64_t ldc, int* err) {
+  using S = Shape<BN, EPI>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)S::STAGES * S::STAGE_BYTES);
+  uint64_t* full = bars;                   // [STAGES]
+  uint64_t* empty = bars + S::STAGES;      // [STAGES]
+  uint64_t* accum = bars + 2 * S::STAGES;  // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S::STAGES + 1);
+  volatile uint32_t* failed = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM;
+  const int t0 = blockIdx.y * BN;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(S::ACC_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % S::STAGES;
+        const uint32_t phase = (uint32_t)(kb / S::STAGES) & 1u;
+        if (*failed || !mbar_wait(&empty[s], phase ^ 1u)) {
+          *failed = 1;
+          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 100 + s);
+          break;
+        }
+        const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+        mbar_expect_tx(&full[s], S::STAGE_BYTES);
+        tma_load_2d(stage, &map_w, kb * BK, n0, &full[s]);
+        if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kb * BK, N + n0, &full[s]);
+        tma_load_2d(stage + S::A_TILES * A_BYTES, &map_x, kb * BK, t0, &full[s]);
+        issued = kb + 1;
+      }
+      if (*failed) {
+        // wait (bounded) for the copies still in flight before the block exits
+        const int first = issued > S::STAGES ? issued - S::STAGES : 0;
+        for (int kb = first; kb < issued; ++kb)
+          mbar_wait(&full[kb % S::STAGES], (uint32_t)(kb / S::STAGES) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % S::STAGES;
+        const uint32_t phase = (uint32_t)(kb / S::STAGES) & 1u;
+        if (*failed || !mbar_wait(&full[s], phase)) {
+          *failed = 1;
+          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 200 + s);
+          ok = false;
+          break;
+        }
+        fence_after_sync();
+        const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint64_t bdesc = smem_desc(stage + S::A_TILES * A_BYTES + k * UMMA_K * 2);
+          const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
+          umma(tmem_base, smem_desc(stage + k * UMMA_K * 2), bdesc, idesc, acc);
+          if (EPI == 2) umma(tmem_base + BN, smem_desc(stage + A_BYTES + k * UMMA_K * 2), bdesc, idesc, acc);
+        }
+        umma_commit(&empty[s]);
+      }
+      if (ok) umma_commit(accum);
+    }
+  } else {
+    // epilogue: warp w may touch tensor-memory lanes 32*(w%4) .. +32
+    const int quad = warp & 3;
+    const int n = n0 + quad * 32 + lane;
+    bool ok = mbar_wait(accum, 0);
+    if (!ok) {
+      *failed = 1;
+      if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 300 + quad);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    fence_after_sync();
+    if (ok) {
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (t0 + c0 >= T) break;          // uniform across the warp
+        uint32_t g[16], u[16];
+        tmem_ld16(lane_base + c0, g);
+        if (EPI == 2) tmem_ld16(lane_base + BN + c0, u);
+        tmem_ld_wait();
+        if (n < N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c0 + j;
+            if (t < T) {
+              TC* c = C + (int64_t)t * ldc + n;
+              const float a = __uint_as_float(g[j]);
+              if (EPI == 0) {
+                *c = ls_from_float<TC>(a);
+              } else if (EPI == 1) {
+                *c = ls_from_float<TC>(ls_to_float<TC>(*c) + a);
+              } else {
+                *c = ls_from_float<TC>(a / (1.0f + expf(-a)) * __uint_as_float(u[j]));
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(S::ACC_COLS)
+                 : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)p;
+  }
+  return fn;
+}
+
+// rows x K bfloat16, row pitch ld elements; box of box_rows x 64 with 128-byte swizzle
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, int box_rows) {
+  EncodeTiled enc = encode_fn();
+  if (enc == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int EPI, typename TC>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int64_t ldc,
+           int* err, cudaStream_t stream) {
+  using S = Shape<BN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)S::SMEM) != cudaSuccess)
+      return LS_E_SMEM;
+    configured = true;
+  }
+  dim3 grid((N + BM - 1) / BM, (T + BN - 1) / BN);
+  gemm_tc_kernel<BN, EPI, TC><<<grid, 192, S::SMEM, stream>>>(mw, mx, (TC*)C, T, N, K, ldc, err);
+  return ls_launch_status();
+}
+
+template <int BN>
+int dispatch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int c_dtype, int T, int N, int K,
+             int64_t ldc, int epilogue, int* err, cudaStream_t stream) {
+  typedef __nv_bfloat16 bf16;
+  if (epilogue == 0 && c_dtype == LS_BF16) return launch<BN, 0, bf16>(mw, mx, C, T, N, K, ldc, err, stream);
+  if (epilogue == 0 && c_dtype == LS_F32) return launch<BN, 0, float>(mw, mx, C, T, N, K, ldc, err, stream);
+  if (epilogue == 1 && c_dtype == LS_F32) return launch<BN, 1, float>(mw, mx, C, T, N, K, ldc, err, stream);
+  if (epilogue == 2 && c_dtype == LS_BF16) {
+    if constexpr (BN <= 128) return launch<BN, 2, bf16>(mw, mx, C, T, N, K, ldc, err, stream);
+  }
+  return LS_E_DTYPE;
+}
+
+}  // namespace
+
+// The token tile for T tokens (a function of T alone; it does not change any sum).
+LS_API int ls_gemm_tc_token_tile(int T, int epilogue) {
+  const int cap = epilogue == 2 ? 128 : 256;
+  int bn = 16;
+  while (bn < T && bn < cap) bn *= 2;
+  return bn;
+}
+
+// X [T, K] and W [N, K] (or [2N, K] for silu-mul) bfloat16 with row pitches ldx,
+// ldw; C [T, N].  Refuses (LS_E_ALIGN, LS_E_SIZE) what TMA cannot address, so
+// that the caller can use the CUDA-core product instead.
+LS_API int ls_gemm_nt_tc(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
+                         int64_t ldx, int64_t ldw, int64_t ldc, int epilogue, int* err,
+                         cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (K <= 0 || epilogue < 0 || epilogue > 2) return LS_E_SIZE;
+  if ((K % 8) || (ldx % 8) || (ldw % 8)) return LS_E_ALIGN;     // 16-byte row pitch
+  if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LS_E_ALIGN;
+  if ((N + BM - 1) / BM > 2147483647 / 2 || (T + 15) / 16 > 65535) return LS_E_SIZE;
+  const int bn = ls_gemm_tc_token_tile(T, epilogue);
+  const int w_rows = epilogue == 2 ? 2 * N : N;
+  CUtensorMap mw, mx;
+  if (!make_map(&mw, W, w_rows, K, ldw, BM)) return LS_E_SIZE;
+  if (!make_map(&mx, X, T, K, ldx, bn)) return LS_E_SIZE;
+  switch (bn) {
+    case 16: return dispatch<16>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, err, stream);
+    case 32: return dispatch<32>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, err, stream);
+    case 64: return dispatch<64>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, err, stream);
+    case 128: return dispatch<128>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, err, stream);
+    case 256: return dispatch<256>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, err, stream);
+  }
+  return LS_E_SIZE;
+}

@@ -68,6 +68,12 @@ _SIGNATURES = {
     },
 }
 
+_SIGNATURES["tc"] = {
+    "ls_gemm_tc_token_tile": [c_int, c_int],
+    "ls_gemm_nt_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                      c_int, c_void_p, c_void_p],
+}
+
 _libs: dict[str, ctypes.CDLL] = {}
 
 
@@ -275,10 +281,44 @@ def sample(logits, probs, temperature, top_p, keys, positions, out) -> None:
         _dev(out, "out", torch.int32), rows, vocab, _stream()), "sample")
 
 
-def gemm_nt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE) -> None:
+# bfloat16 products go to the tensor cores unless this is cleared (a debugging aid)
+USE_TENSOR_CORES = [True]
+
+
+def gemm_nt_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, err: torch.Tensor) -> bool:
+    """c = a @ w.T on the tcgen05 tensor cores (csrc/gemm_tc.cu).  Returns False,
+    having launched nothing, when TMA cannot address the operands (a row pitch
+    that is no multiple of 16 bytes): the caller then uses the CUDA-core product."""
+    m, k = a.shape
+    n = c.shape[1]
+    rows_w = 2 * n if epilogue == EPILOGUE_SILU_MUL else n
+    if w.shape != (rows_w, k) or c.shape[0] != m or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_nt_tc: shapes or types do not agree: a {tuple(a.shape)} w {tuple(w.shape)} c {tuple(c.shape)}")
+    status = library("tc").ls_gemm_nt_tc(
+        _dev(a, "a"), _dev(w, "w"), _dev(c, "c"), _code(c), m, n, k, k, k, n, epilogue,
+        _dev(err, "err", torch.int32), _stream())
+    if status == -3:
+        return False
+    _check(status, "gemm_nt_tc")
+    return True
+
+
+_tc_err: dict = {}
+
+
+def gemm_nt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int = EPILOGUE_STORE,
+            err: torch.Tensor | None = None) -> None:
     """c = a @ w.T with float32 accumulation and the chosen epilogue.
 
     a [m, k] and w [n, k] (or [2n, k] for the silu-mul epilogue) share an element
     type; c is [m, n] in that type, or float32 (always for the residual epilogue,
-    where the product is added into c in place)."""
+    where the product is added into c in place).  bfloat16 operands go to the
+    tensor cores, float32 operands to the CUDA cores (true 32-bit)."""
+    if a.dtype == torch.bfloat16 and USE_TENSOR_CORES[0]:
+        if err is None:
+            err = _tc_err.get(a.device)
+            if err is None:
+                err = _tc_err[a.device] = new_error_word(a.device)
+        if gemm_nt_tc(a, w, c, epilogue, err):
+            return
     gemm_nt_simt(a, w, c, epilogue)

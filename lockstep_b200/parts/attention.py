@@ -60,7 +60,7 @@ class GQAttention(Mixer):
         nq, nkv, d = self.nq, self.nkv, self.d
         dev, dt = x.device, x.dtype
         qkv = torch.empty((t, (nq + 2 * nkv) * d), dtype=dt, device=dev)
-        K.gemm_nt(x, self.w_qkv, qkv)
+        K.gemm_nt(x, self.w_qkv, qkv, err=self.rt.err)
         q = torch.empty((t, nq * d), dtype=dt, device=dev)
         rot = self.position.rotary()
         cos, sin, rot_dim = rot if rot is not None else (None, None, 0)
@@ -85,7 +85,7 @@ class GQAttention(Mixer):
                                  plan.n_split, cache.block_table, nq, nkv, d, self.window,
                                  self.scale, self.rt.err)
             K.attention_combine(part_acc, part_ml, attn, plan.combine_items, plan.n_combine, nq, d)
-        K.gemm_nt(attn, self.w_o, residual, K.EPILOGUE_RESIDUAL)
+        K.gemm_nt(attn, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=self.rt.err)
 
 
 @register_part("mixer", "gqa_attention")

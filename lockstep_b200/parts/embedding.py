@@ -43,7 +43,7 @@ class LinearHead(Part):
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
         logits = torch.empty((y.shape[0], self.vocab), dtype=torch.float32, device=y.device)
-        K.gemm_nt(y, self.weight, logits)
+        K.gemm_nt(y, self.weight, logits, err=self.rt.err)
         return logits
 
 

@@ -29,8 +29,8 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, ctx, residual):
         act = torch.empty((x.shape[0], self.i), dtype=x.dtype, device=x.device)
-        K.gemm_nt(x, self.w_gate_up, act, K.EPILOGUE_SILU_MUL)
-        K.gemm_nt(act, self.w_down, residual, K.EPILOGUE_RESIDUAL)
+        K.gemm_nt(x, self.w_gate_up, act, K.EPILOGUE_SILU_MUL, err=self.rt.err)
+        K.gemm_nt(act, self.w_down, residual, K.EPILOGUE_RESIDUAL, err=self.rt.err)
 
 
 @register_part("feed_forward", "swiglu")

@@ -1,0 +1,90 @@
+"""The tensor-core product (tcgen05, TMA, tensor memory) alone, against float64:
+token counts that fill each tile width and spill over it, widths and depths
+that are no multiple of the tile, all three epilogues; and that a row's bits do
+not depend on the batch it is in."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+SHAPES = [
+    # tokens, out features, depth
+    (1, 128, 64), (8, 256, 128), (16, 384, 1024), (17, 100, 72), (33, 500, 80), (64, 1024, 200),
+    (100, 130, 136), (129, 3072, 1024), (300, 264, 328), (2048, 512, 256), (5, 1187, 40),
+]
+
+
+@pytest.mark.parametrize("t,n,k", SHAPES)
+def test_tensor_core_product_and_epilogues(t, n, k):
+    from lockstep_b200 import kernels as K
+
+    g = torch.Generator().manual_seed(t * 7 + n)
+    x = torch.randn(t, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * n, k, generator=g) * 0.3).to(torch.bfloat16)
+    xd, wd = x.to(dev()), w.to(dev())
+    err = K.new_error_word(dev())
+    want = x.double() @ w[:n].double().T
+    scale = float(want.abs().max()) + 1e-6
+
+    c = torch.empty(t, n, dtype=torch.bfloat16, device=dev())
+    assert K.gemm_nt_tc(xd, wd[:n].contiguous(), c, K.EPILOGUE_STORE, err)
+    K.raise_on_fault(err)
+    assert (c.cpu().double() - want).abs().max() <= 1e-2 * scale
+
+    cf = torch.empty(t, n, dtype=torch.float32, device=dev())
+    assert K.gemm_nt_tc(xd, wd[:n].contiguous(), cf, K.EPILOGUE_STORE, err)
+    assert (cf.cpu().double() - want).abs().max() <= 2e-5 * scale
+
+    res = torch.randn(t, n, generator=g)
+    rd = res.to(dev()).clone()
+    assert K.gemm_nt_tc(xd, wd[:n].contiguous(), rd, K.EPILOGUE_RESIDUAL, err)
+    assert (rd.cpu().double() - (res.double() + want)).abs().max() <= 2e-5 * scale + 1e-5
+
+    up = x.double() @ w[n:].double().T
+    want_act = want * torch.sigmoid(want) * up
+    act = torch.empty(t, n, dtype=torch.bfloat16, device=dev())
+    assert K.gemm_nt_tc(xd, wd, act, K.EPILOGUE_SILU_MUL, err)
+    assert (act.cpu().double() - want_act).abs().max() <= 1e-2 * (float(want_act.abs().max()) + 1e-6)
+    K.raise_on_fault(err)
+
+    # the CUDA-core product of the same operands agrees to float32 rounding
+    cs = torch.empty(t, n, dtype=torch.float32, device=dev())
+    K.gemm_nt_simt(xd, wd[:n].contiguous(), cs)
+    assert (cs - cf).abs().max().item() <= 2e-5 * scale
+
+
+def test_a_row_has_the_same_bits_in_every_batch():
+    from lockstep_b200 import kernels as K
+
+    g = torch.Generator().manual_seed(5)
+    k, n = 1024, 640
+    x = torch.randn(300, k, generator=g).to(torch.bfloat16).to(dev())
+    w = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16).to(dev())
+    err = K.new_error_word(dev())
+    full = torch.empty(300, n, dtype=torch.float32, device=dev())
+    assert K.gemm_nt_tc(x, w, full, K.EPILOGUE_STORE, err)
+    for lo, hi in [(0, 1), (7, 8), (5, 21), (100, 133), (0, 64), (40, 169), (299, 300)]:
+        part = torch.empty(hi - lo, n, dtype=torch.float32, device=dev())
+        assert K.gemm_nt_tc(x[lo:hi].contiguous(), w, part, K.EPILOGUE_STORE, err)
+        assert torch.equal(part, full[lo:hi]), (lo, hi)
+    K.raise_on_fault(err)
+
+
+def test_unaligned_depth_falls_back_to_the_cuda_cores():
+    from lockstep_b200 import kernels as K
+
+    x = torch.randn(4, 45).to(torch.bfloat16).to(dev())
+    w = torch.randn(9, 45).to(torch.bfloat16).to(dev())
+    c = torch.empty(4, 9, dtype=torch.float32, device=dev())
+    err = K.new_error_word(dev())
+    assert not K.gemm_nt_tc(x, w, c, K.EPILOGUE_STORE, err)
+    K.gemm_nt(x, w, c, err=err)
+    assert (c.cpu().double() - x.cpu().double() @ w.cpu().double().T).abs().max() < 1e-4
