@@ -70,6 +70,8 @@ _SIGNATURES = {
 
 _SIGNATURES["tc"] = {
     "ls_gemm_tc_token_tile": [c_int, c_int],
+    "ls_attention_decode_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "ls_gemm_nt_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                       c_int, c_void_p, c_void_p],
 }
@@ -120,6 +122,9 @@ def _dev(t: torch.Tensor, name: str, dtype=None) -> int:
 def _opt(t, name, dtype=None) -> int:
     return 0 if t is None else _dev(t, name, dtype)
 
+
+# bfloat16 work goes to the tensor cores unless this is cleared (a debugging aid)
+USE_TENSOR_CORES = [True]
 
 # launcher calls since the counter was last cleared (each is at least one kernel)
 LAUNCHES = [0]
@@ -256,6 +261,24 @@ def attention_decode(q, pages, part_acc, part_ml, work, n_work, block_table, nq,
     return True
 
 
+def attention_decode_mma(q, pages, part_acc, part_ml, work, n_work, block_table, nq, nkv, d, window,
+                         scale, err) -> bool:
+    """Decode attention on mma.sync with TMA-fed pages (csrc/attention_decode_mma.cu): bfloat16,
+    head size 64 or 128, groups up to 16.  Returns False (nothing launched) otherwise."""
+    if q.dtype != torch.bfloat16 or not USE_TENSOR_CORES[0]:
+        return False
+    status = library("tc").ls_attention_decode_mma(
+        _dev(q, "q"), _dev(pages, "pages", q.dtype), _dev(part_acc, "part_acc", torch.float32),
+        _dev(part_ml, "part_ml", torch.float32), _dev(work, "work", torch.int32), n_work,
+        _dev(block_table, "block_table", torch.int32), block_table.shape[-1], nq, nkv, d,
+        pages.shape[3], pages.shape[0], int(window), float(scale), _dev(err, "err", torch.int32),
+        _stream())
+    if status == -2:
+        return False
+    _check(status, "attention_decode_mma")
+    return True
+
+
 def attention_combine(part_acc, part_ml, out, items, n_items, nq, d) -> None:
     _check(library().ls_attention_combine(
         _dev(part_acc, "part_acc", torch.float32), _dev(part_ml, "part_ml", torch.float32),
@@ -280,9 +303,6 @@ def sample(logits, probs, temperature, top_p, keys, positions, out) -> None:
         _dev(keys, "keys", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(out, "out", torch.int32), rows, vocab, _stream()), "sample")
 
-
-# bfloat16 products go to the tensor cores unless this is cleared (a debugging aid)
-USE_TENSOR_CORES = [True]
 
 
 def gemm_nt_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, err: torch.Tensor) -> bool:

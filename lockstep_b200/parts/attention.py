@@ -77,6 +77,10 @@ class GQAttention(Mixer):
             part_ml = torch.empty((plan.n_slots, nq, 2), dtype=torch.float32, device=dev)
             done = False
             if not self.exact:
+                done = K.attention_decode_mma(q, cache.pages, part_acc, part_ml, plan.split_work,
+                                              plan.n_split, cache.block_table, nq, nkv, d, self.window,
+                                              self.scale, self.rt.err)
+            if not done and not self.exact:
                 done = K.attention_decode(q, cache.pages, part_acc, part_ml, plan.split_work,
                                           plan.n_split, cache.block_table, nq, nkv, d, self.window,
                                           self.scale, self.rt.err)

@@ -179,7 +179,10 @@ def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel):
         ml = torch.empty(n_slots, nq, 2, dtype=torch.float32, device=D)
         w = torch.from_numpy(sp).to(D)
         done = False
-        if decode_kernel:
+        if decode_kernel == "mma":
+            done = k.attention_decode_mma(qd, pd, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err)
+            assert done
+        elif decode_kernel:
             done = k.attention_decode(qd, pd, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err)
             assert done
         if not done:
@@ -190,7 +193,8 @@ def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nq,nkv,d,page", [(4, 2, 16, 16), (6, 3, 48, 8), (8, 1, 64, 32), (16, 8, 128, 16), (2, 2, 256, 64)])
+@pytest.mark.parametrize("nq,nkv,d,page", [(4, 2, 16, 16), (6, 3, 48, 8), (8, 1, 64, 32), (16, 8, 128, 16), (2, 2, 256, 64),
+                                           (12, 1, 128, 8), (16, 1, 64, 64), (5, 5, 128, 32)])
 @pytest.mark.parametrize("window", [0, 100])
 def test_attention_prefix_portion_and_decode(dtype, nq, nkv, d, page, window):
     """A portion (tile kernel, serial splits) and a single token (split kernels
@@ -211,8 +215,10 @@ def test_attention_prefix_portion_and_decode(dtype, nq, nkv, d, page, window):
     # single tokens at telling places: first, page edges, split edges, last
     for pos in [0, 1, page - 1, page, 255, 256, 257, 511, 512, 699]:
         sub_pages, sub_ids = pages, ids
-        for decode_kernel in (False, True):
+        for decode_kernel in (False, True, "mma"):
             if decode_kernel and (nq // nkv) * d > 1024:
+                continue
+            if decode_kernel == "mma" and (dtype != torch.bfloat16 or d not in (64, 128)):
                 continue
             got = run_attention(k, q[pos:pos + 1], sub_pages, sub_ids, pos, window, scale, decode_kernel)
             assert (got[0] - want[pos]).abs().max() <= bound, (pos, decode_kernel)
@@ -224,11 +230,12 @@ def test_attention_prefix_portion_and_decode(dtype, nq, nkv, d, page, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_attention_finds_one_far_key(dtype):
+@pytest.mark.parametrize("d", [32, 128])
+def test_attention_finds_one_far_key(dtype, d):
     """One key among hundreds is made to stand out for the last query; the output
     must be that key's value.  A fault in a far page, split or tile shows here."""
     k = K()
-    nq, nkv, d, page = 4, 2, 32, 16
+    nq, nkv, page = 4, 2, 16
     g = torch.Generator().manual_seed(9)
     total = 600
     for far in [0, 15, 16, 255, 256, 300, 511, 512, 598]:
@@ -241,7 +248,8 @@ def test_attention_finds_one_far_key(dtype):
         kk[far] = direction * 30.0
         q, kk, vv = q.to(dtype), kk.to(dtype), vv.to(dtype)
         pages, ids = paged_from_dense(kk, vv, page, 64, seed=far)
-        for decode_kernel in (False, True):
+        kinds = (False, True, "mma") if (dtype == torch.bfloat16 and d == 128) else (False, True)
+        for decode_kernel in kinds:
             got = run_attention(k, q[-1:], pages, ids, total - 1, 0, 1.0, decode_kernel)
             for h in range(nq):
                 assert (got[0, h] - vv[far, h // 2].float()).abs().max() <= 2e-2, (far, decode_kernel)
