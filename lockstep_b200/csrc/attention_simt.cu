@@ -78,6 +78,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
 
   const int* w = work + (int64_t)blockIdx.x * 8;
   const int req_row = w[0], tok0 = w[1], ntok = w[2], pos0 = w[3];
+  if (ntok == 0) return;                     // padding item of a recorded launch
   const int split_begin = w[4], split_end = w[5], slot_base = w[6];
   const int h = blockIdx.y;
   const int kvh = h / (nq / nkv);
@@ -240,6 +241,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
   float* St = Ss + group * DEC_TILE;                       // [group][3]: m, l, alpha
 
   const int* w = work + (int64_t)blockIdx.x * 8;
+  if (w[2] == 0) return;                     // padding item of a recorded launch
   const int req_row = w[0], tok = w[1], pos = w[3], split = w[4], slot = w[6];
   const int kvh = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -362,6 +364,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
                                          const int* __restrict__ items, int nq, int d) {
   const int* it = items + (int64_t)blockIdx.x * 4;
   const int tok = it[0], first = it[1], stride = it[2], n = it[3];
+  if (n == 0) return;                        // padding item of a recorded launch
   const int h = blockIdx.y;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float acc = 0.f, m_run = -CUDART_INF_F, l_run = 0.f;
@@ -412,15 +415,20 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
   const size_t smem = tile_smem_bytes(d);
   dim3 grid(n_work, nq);
   cudaError_t e;
+  static size_t set_f32 = 0, set_bf16 = 0;     // largest size configured so far
   if (dtype == LS_F32) {
-    e = cudaFuncSetAttribute(attention_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = smem <= set_f32 ? cudaSuccess
+                        : cudaFuncSetAttribute(attention_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
+    if (smem > set_f32) set_f32 = smem;
     attention_tile_kernel<float><<<grid, 128, smem, stream>>>(
         (const float*)q, (const float*)pages, (float*)out, part_acc, part_ml, work, block_table,
         table_stride, nq, nkv, d, page_size, num_pages, window, scale, err);
   } else if (dtype == LS_BF16) {
-    e = cudaFuncSetAttribute(attention_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = smem <= set_bf16 ? cudaSuccess
+                         : cudaFuncSetAttribute(attention_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
+    if (smem > set_bf16) set_bf16 = smem;
     attention_tile_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, part_acc,
         part_ml, work, block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale,
@@ -444,17 +452,22 @@ LS_API int ls_attention_decode(const void* q, const void* pages, float* part_acc
   if (group * d > 128 * DEC_ACC || nkv > 65535) return LS_E_SIZE;
   dim3 grid(n_work, nkv);
   cudaError_t e;
+  static size_t set_f32 = 0, set_bf16 = 0;     // largest size configured so far
   if (dtype == LS_F32) {
     const size_t smem = decode_smem_bytes(d, group, 4);
-    e = cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = smem <= set_f32 ? cudaSuccess
+                        : cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
+    if (smem > set_f32) set_f32 = smem;
     attention_decode_kernel<float><<<grid, 128, smem, stream>>>(
         (const float*)q, (const float*)pages, part_acc, part_ml, work, block_table, table_stride,
         nq, nkv, d, page_size, num_pages, window, scale, err);
   } else if (dtype == LS_BF16) {
     const size_t smem = decode_smem_bytes(d, group, 2);
-    e = cudaFuncSetAttribute(attention_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = smem <= set_bf16 ? cudaSuccess
+                         : cudaFuncSetAttribute(attention_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
+    if (smem > set_bf16) set_bf16 = smem;
     attention_decode_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, part_acc, part_ml, work,
         block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, err);

@@ -4,8 +4,12 @@
 // Orientation: the weight tile is the MMA's M side (128 rows of W), the tokens
 // are its N side (16..256 per tile), so one orientation serves a batch of one
 // decoded token and a prompt of thousands; only the token tile's width varies
-// with T.  Each block owns one 128 x BN output tile and walks all of K in
-// ascending 64-element blocks (no split-K), so an output element is the same
+// with T.  A block walks its share of K in ascending 64-element blocks.  Where
+// the weight gives too few tiles to occupy the device (few rows of tiles, deep
+// K), K is cut into shares run by the blocks of one thread-block cluster, and
+// the shares' partial tiles are summed in ascending share order through
+// distributed shared memory.  The number of shares is a function of the
+// weight's shape alone (ls_gemm_tc_k_shares), so an output element is the same
 // sum whatever the batch.
 //
 // Roles inside a block (192 threads): warp 0 issues TMA loads into a ring of
@@ -21,6 +25,21 @@
 #include <cuda.h>
 
 #include "common.cuh"
+
+// Into how many shares K is cut for a weight of N rows and depth K: a function
+// of the weight's shape alone.  One share unless the weight has fewer than 96
+// row tiles; then enough shares to give about 128 blocks, each share at least
+// four 64-element blocks deep, at most 8 (the portable cluster size).
+LS_API int ls_gemm_tc_k_shares(int N, int K) {
+  const int tiles = (N + 127) / 128;
+  const int kb = (K + 63) / 64;
+  if (tiles >= 96) return 1;
+  int want = (128 + tiles - 1) / tiles;
+  if (want > 8) want = 8;
+  int by_depth = kb / 4;
+  if (by_depth < 1) by_depth = 1;
+  return want < by_depth ? want : by_depth;
+}
 
 namespace {
 
@@ -139,10 +158,30 @@ struct Shape {
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
 };
 
+template <int EPI, typename TC>
+__device__ __forceinline__ void epilogue_store(TC* c, float a, float up) {
+  if (EPI == 0) {
+    *c = ls_from_float<TC>(a);
+  } else if (EPI == 1) {
+    *c = ls_from_float<TC>(ls_to_float<TC>(*c) + a);
+  } else {
+    *c = ls_from_float<TC>(a / (1.0f + expf(-a)) * up);
+  }
+}
+
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+constexpr int MAX_SHARES = 8;
+
 template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               TC* __restrict__ C, int T, int N, int K, int64_t ldc, int* err) {
+               TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share, int shares,
+               int* err) {
   using S = Shape<BN, EPI>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -157,7 +196,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM;
   const int t0 = blockIdx.y * BN;
-  const int num_kb = (K + BK - 1) / BK;
+  const int total_kb = (K + BK - 1) / BK;
+  const int kb_first = (int)blockIdx.z * kb_per_share;          // this block's share of K
+  const int num_kb = (total_kb - kb_first < kb_per_share ? total_kb - kb_first : kb_per_share);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
@@ -193,9 +234,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
         mbar_expect_tx(&full[s], S::STAGE_BYTES);
-        tma_load_2d(stage, &map_w, kb * BK, n0, &full[s]);
-        if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kb * BK, N + n0, &full[s]);
-        tma_load_2d(stage + S::A_TILES * A_BYTES, &map_x, kb * BK, t0, &full[s]);
+        const int kx = (kb_first + kb) * BK;
+        tma_load_2d(stage, &map_w, kx, n0, &full[s]);
+        if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kx, N + n0, &full[s]);
+        tma_load_2d(stage + S::A_TILES * A_BYTES, &map_x, kx, t0, &full[s]);
         issued = kb + 1;
       }
       if (*failed) {
@@ -242,8 +284,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     ok = __all_sync(0xffffffffu, ok);
     fence_after_sync();
-    if (ok) {
-      const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    if (ok && shares == 1) {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (t0 + c0 >= T) break;          // uniform across the warp
@@ -255,21 +297,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int t = t0 + c0 + j;
-            if (t < T) {
-              TC* c = C + (int64_t)t * ldc + n;
-              const float a = __uint_as_float(g[j]);
-              if (EPI == 0) {
-                *c = ls_from_float<TC>(a);
-              } else if (EPI == 1) {
-                *c = ls_from_float<TC>(ls_to_float<TC>(*c) + a);
-              } else {
-                *c = ls_from_float<TC>(a / (1.0f + expf(-a)) * __uint_as_float(u[j]));
-              }
-            }
+            if (t < T)
+              epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, __uint_as_float(g[j]),
+                                      EPI == 2 ? __uint_as_float(u[j]) : 0.f);
           }
         }
       }
+    } else if (ok) {
+      // leave this share's partial tile in shared memory: part[column][row], float32
+      float* part = reinterpret_cast<float*>(aligned);
+      const int row = quad * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < S::A_TILES * BN; c0 += 16) {
+        uint32_t g[16];
+        tmem_ld16(lane_base + c0, g);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) part[(c0 + j) * BM + row] = __uint_as_float(g[j]);
+      }
     }
+  }
+  if (shares > 1) {
+    // all shares have left their partials; each block folds the columns c with
+    // c % shares == its rank, reading every share in ascending order
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp >= 2 && !*failed) {
+      const int quad = warp & 3;
+      const int row = quad * 32 + lane;
+      const int n = n0 + row;
+      uint32_t peer[MAX_SHARES];
+#pragma unroll
+      for (int r = 0; r < MAX_SHARES; ++r)
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[r]) : "r"(base), "r"(r < shares ? r : 0));
+      for (int c = (int)blockIdx.z; c < BN; c += shares) {
+        const int t = t0 + c;
+        if (t >= T) break;
+        const uint32_t off_g = (uint32_t)((c * BM + row) * 4), off_u = (uint32_t)(((BN + c) * BM + row) * 4);
+        float vg[MAX_SHARES], vu[MAX_SHARES];
+#pragma unroll
+        for (int r = 0; r < MAX_SHARES; ++r) {
+          vg[r] = r < shares ? ld_cluster_f32(peer[r] + off_g) : 0.f;
+          if (EPI == 2) vu[r] = r < shares ? ld_cluster_f32(peer[r] + off_u) : 0.f;
+        }
+        float g = 0.f, u = 0.f;
+#pragma unroll
+        for (int r = 0; r < MAX_SHARES; ++r) {
+          if (r < shares) {
+            g += vg[r];
+            if (EPI == 2) u += vu[r];
+          }
+        }
+        if (n < N) epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, g, u);
+      }
+    }
+    // no block may leave while a peer still reads its partial
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
   fence_before_sync();
   __syncthreads();
@@ -322,8 +406,25 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, 
       return LS_E_SMEM;
     configured = true;
   }
-  dim3 grid((N + BM - 1) / BM, (T + BN - 1) / BN);
-  gemm_tc_kernel<BN, EPI, TC><<<grid, 192, S::SMEM, stream>>>(mw, mx, (TC*)C, T, N, K, ldc, err);
+  const int total_kb = (K + BK - 1) / BK;
+  const int want = ls_gemm_tc_k_shares(N, K);
+  const int kb_per_share = (total_kb + want - 1) / want;
+  const int shares = (total_kb + kb_per_share - 1) / kb_per_share;   // every share has work
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((N + BM - 1) / BM, (T + BN - 1) / BN, shares);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = S::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = shares;
+  cfg.attrs = attr;
+  cfg.numAttrs = shares > 1 ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC>, mw, mx, (TC*)C, T, N, K, ldc,
+                                     kb_per_share, shares, err);
+  if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }
 

@@ -207,11 +207,62 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ probs,
   if (threadIdx.x == 0) out[r] = token;
 }
 
+// argmax in two stages, so that a few rows of a wide vocabulary fill the device:
+// stage 1 reduces contiguous chunks of a row, stage 2 the chunks' winners.
+constexpr int ARGMAX_CHUNKS = 64;
+
+__global__ void argmax_chunk_kernel(const float* __restrict__ logits, float* __restrict__ cval,
+                                    int* __restrict__ cidx, int vocab) {
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  const int r = blockIdx.x, c = blockIdx.y;
+  const int per = (vocab + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+  const int lo = c * per, hi = lo + per < vocab ? lo + per : vocab;
+  ArgMax best{-CUDART_INF_F, 0x7fffffff};
+  if (lo < hi) {
+    const ArgMax local = block_argmax(logits + (int64_t)r * vocab + lo, hi - lo, sval, sidx);
+    best.v = local.v;
+    best.i = local.i + lo;
+    // a chunk of NaN only: block_argmax reports index 0 with value -inf; keep it out of the way
+    if (!(local.v > -CUDART_INF_F)) best.i = 0x7fffffff;
+  }
+  if (threadIdx.x == 0) {
+    cval[r * ARGMAX_CHUNKS + c] = best.v;
+    cidx[r * ARGMAX_CHUNKS + c] = best.i;
+  }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ cval, const int* __restrict__ cidx,
+                                    int* __restrict__ out) {
+  const int r = blockIdx.x;
+  ArgMax best{cval[r * ARGMAX_CHUNKS + threadIdx.x], cidx[r * ARGMAX_CHUNKS + threadIdx.x]};
+  // 64 candidates: two per lane of one warp
+  if (threadIdx.x < 32) {
+    ArgMax second{cval[r * ARGMAX_CHUNKS + 32 + threadIdx.x], cidx[r * ARGMAX_CHUNKS + 32 + threadIdx.x]};
+    best = better(best, second);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ArgMax peer{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+      best = better(best, peer);
+    }
+    if (threadIdx.x == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+  }
+}
+
 }  // namespace
 
-LS_API int ls_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+// scratch: rows * 64 floats followed by rows * 64 ints (the caller's; rows * 512 bytes)
+LS_API int ls_argmax(const float* logits, int* out, void* scratch, int rows, int vocab,
+                     cudaStream_t stream) {
   if (rows <= 0) return 0;
-  argmax_kernel<<<rows, 512, 0, stream>>>(logits, out, vocab);
+  if (scratch == nullptr || vocab < 4 * ARGMAX_CHUNKS) {
+    argmax_kernel<<<rows, 512, 0, stream>>>(logits, out, vocab);
+    return ls_launch_status();
+  }
+  float* cval = (float*)scratch;
+  int* cidx = (int*)(cval + (size_t)rows * ARGMAX_CHUNKS);
+  argmax_chunk_kernel<<<dim3(rows, ARGMAX_CHUNKS), 256, 0, stream>>>(logits, cval, cidx, vocab);
+  argmax_final_kernel<<<rows, 32, 0, stream>>>(cval, cidx, out);
   return ls_launch_status();
 }
 

@@ -1,0 +1,138 @@
+"""Decode steps recorded as CUDA graphs.
+
+A step whose entries all bring one token launches a few hundred small kernels;
+recorded once and replayed, the host's share of the step shrinks to filling one
+pinned buffer.  A graph is keyed by (number of requests, capacity of the
+attention work list).  Everything that changes from step to step (token ids,
+positions, slots, wanted rows, the attention work lists) lives in one device
+buffer that is refilled before each replay; work lists are padded to the
+capacity with null items, which the kernels skip.  Nothing about the
+arithmetic changes: the same kernels run on the same values.
+
+Only models whose parts are all ``graph_safe`` are recorded.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .batch import AttentionPlan, plan_attention
+
+
+class StaticStepContext:
+    """What parts see of a recorded decode step: views into the graph's buffer."""
+
+    def __init__(self, batch: int, capacity: int, windows: list[int], device, err, split_size: int):
+        self.batch, self.capacity, self.windows = batch, capacity, list(windows)
+        self.device, self.err, self.split_size = device, err, split_size
+        self.num_tokens = self.n_wanted = batch
+        per_window = capacity * 8 + batch * 4
+        self.size = 4 * batch + len(self.windows) * per_window
+        self.host = torch.zeros(self.size, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(self.size, dtype=torch.int32, device=device)
+        b = batch
+        self.token_ids, self.positions = self.dev[0:b], self.dev[b:2 * b]
+        self.token_slot, self.wanted_rows = self.dev[2 * b:3 * b], self.dev[3 * b:4 * b]
+        self._plans: dict[int, AttentionPlan] = {}
+        self._offsets: dict[int, int] = {}
+        off = 4 * b
+        for w in self.windows:
+            self._offsets[w] = off
+            self._plans[w] = AttentionPlan(
+                tile_work=None, n_tile=0,
+                split_work=self.dev[off:off + capacity * 8].view(capacity, 8), n_split=capacity,
+                combine_items=self.dev[off + capacity * 8:off + per_window].view(batch, 4),
+                n_combine=batch, n_slots=capacity)
+            off += per_window
+        self.portions: list = []
+        self.entries: list = []
+        self.slots: list = []
+        self.copied = torch.cuda.Event()
+        self._pending = False
+
+    def attention_plan(self, window: int) -> AttentionPlan:
+        try:
+            return self._plans[window]
+        except KeyError:
+            raise KeyError(f"a part asked for the attention plan of window {window}, which it did not "
+                           "declare in attention_windows()") from None
+
+    def fill(self, entries, slots) -> None:
+        """Write this step's values into the pinned buffer and start its copy."""
+        if self._pending:
+            self.copied.synchronize()      # the last copy has read the pinned buffer
+        b, h = self.batch, self.host_np
+        self.entries, self.slots = entries, slots
+        self.portions = [(slot, i, e.start, 1) for i, (e, slot) in enumerate(zip(entries, slots))]
+        h[0:b] = [e.tokens[0] for e in entries]
+        h[b:2 * b] = [e.start for e in entries]
+        h[2 * b:3 * b] = slots
+        h[3 * b:4 * b] = np.arange(b, dtype=np.int32)
+        for w in self.windows:
+            _, split, combine, _ = plan_attention(self.portions, w, self.split_size)
+            off = self._offsets[w]
+            n = split.size
+            h[off:off + n] = split.reshape(-1)
+            h[off + n:off + self.capacity * 8] = 0
+            h[off + self.capacity * 8:off + self.capacity * 8 + combine.size] = combine.reshape(-1)
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+        self._pending = True
+
+
+def split_items(entries, windows: list[int], split_size: int) -> int:
+    """The longest attention work list of a decode step over ``entries``."""
+    worst = 0
+    for w in windows:
+        n = 0
+        for e in entries:
+            lo = max(0, e.start - w + 1) if w else 0
+            n += e.start // split_size - lo // split_size + 1
+        worst = max(worst, n)
+    return worst
+
+
+class DecodeGraphs:
+    def __init__(self, runner, round_to: int = 32):
+        self.runner, self.round_to = runner, round_to
+        self.windows = sorted(set().union(*(b.attention_windows() for b in runner.model.blocks)) or {0})
+        self.graphs: dict[tuple[int, int], tuple] = {}
+        self.pool = None
+        self.replays = 0
+
+    def capacity_for(self, entries) -> int:
+        n = split_items(entries, self.windows, self.runner.split_size)
+        return -(-n // self.round_to) * self.round_to
+
+    def ready(self, key) -> bool:
+        return key in self.graphs
+
+    def record(self, key) -> None:
+        """Record the model's forward for ``key`` (nothing runs while recording)."""
+        r = self.runner
+        batch, capacity = key
+        ctx = StaticStepContext(batch, capacity, self.windows, r.device, r.err, r.split_size)
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize()
+        from .. import kernels as K
+
+        before = K.LAUNCHES[0]
+        with torch.cuda.graph(graph, pool=self.pool):
+            logits = r.forward(ctx)
+        recorded = K.LAUNCHES[0] - before
+        K.LAUNCHES[0] = before               # recording launches nothing
+        self.graphs[key] = (graph, ctx, logits, recorded)
+
+    def replay(self, key, entries, slots) -> torch.Tensor:
+        from .. import kernels as K
+
+        graph, ctx, logits, recorded = self.graphs[key]
+        ctx.fill(entries, slots)
+        graph.replay()
+        K.LAUNCHES[0] += recorded
+        self.replays += 1
+        return logits

@@ -33,7 +33,8 @@ def parse_dtype(dtype) -> torch.dtype:
 
 class ModelRunner:
     def __init__(self, model_dir, dtype="bfloat16", device="cuda:0", num_pages: int = 512,
-                 page_size: int = 16, max_live: int = 64, max_seq_len: int | None = None):
+                 page_size: int = 16, max_live: int = 64, max_seq_len: int | None = None,
+                 use_graphs: bool = True):
         K.require_cuda()
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
@@ -61,6 +62,13 @@ class ModelRunner:
                                   max_live=max_live, max_seq_len=self.max_seq_len, dtype=self.dtype,
                                   device=self.device)
         self.steps_run = 0
+        # decode steps are recorded as CUDA graphs when every part allows it
+        self.graphs = None
+        if use_graphs and all(part.graph_safe for part in
+                              [self.model.embedding, self.model.final_norm, self.model.head, *self.model.blocks]):
+            from .graphs import DecodeGraphs
+
+            self.graphs = DecodeGraphs(self)
 
     # -- requests -----------------------------------------------------------
     def open(self, uid: str) -> int:
@@ -89,10 +97,25 @@ class ModelRunner:
 
     # -- the step -----------------------------------------------------------
     @torch.no_grad()
-    def step(self, entries: list[StepEntry], check: bool = True) -> torch.Tensor:
+    def forward(self, ctx) -> torch.Tensor:
+        """The model on one packed batch: embedding, the scheduled layers, final norm
+        and head at the wanted rows.  Launches kernels only; no host synchronisation."""
+        model = self.model
+        h = model.embedding.forward(ctx)
+        for run in self.spec.schedule:
+            model.blocks[run.layer].forward(h, ctx, self.cache.view(run.cache, run.writes_cache))
+        if ctx.n_wanted:
+            return model.head.forward(model.final_norm.forward(h, ctx.wanted_rows))
+        return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+
+    @torch.no_grad()
+    def step(self, entries: list[StepEntry], check: bool = True, static_logits: bool = False) -> torch.Tensor:
         """Run one batch; returns float32 logits [wanted, vocab] in the order of
         the entries and of their ``want`` lists.  Every entry's request must be
-        open and ``start`` must equal the number of tokens it already holds."""
+        open and ``start`` must equal the number of tokens it already holds.
+        ``check=False`` skips reading the device error word (no synchronisation);
+        ``static_logits=True`` lets a replayed decode step return its graph's own
+        output buffer, which the next replay overwrites."""
         if not entries:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         seen = set()
@@ -108,17 +131,19 @@ class ModelRunner:
             self.cache.reserve(e.uid, e.start + len(e.tokens))
         self.cache.sync()
         slots = [self.cache.slots[e.uid] for e in entries]
-        ctx = StepContext(entries, slots, self.device, self.err, self.split_size)
-
-        model = self.model
-        h = model.embedding.forward(ctx)
-        for run in self.spec.schedule:
-            model.blocks[run.layer].forward(h, ctx, self.cache.view(run.cache, run.writes_cache))
-        if ctx.n_wanted:
-            y = model.final_norm.forward(h, ctx.wanted_rows)
-            logits = model.head.forward(y)
-        else:
-            logits = torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        logits = None
+        if self.graphs is not None and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
+            key = (len(entries), self.graphs.capacity_for(entries))
+            if self.graphs.ready(key):
+                logits = self.graphs.replay(key, entries, slots)
+                if not static_logits:
+                    logits = logits.clone()
+            else:
+                # this step runs eagerly (it also warms every kernel up); later ones replay
+                logits = self.forward(StepContext(entries, slots, self.device, self.err, self.split_size))
+                self.graphs.record(key)
+        if logits is None:
+            logits = self.forward(StepContext(entries, slots, self.device, self.err, self.split_size))
         for e in entries:
             self.cache.advance(e.uid, e.start + len(e.tokens))
         self.steps_run += 1

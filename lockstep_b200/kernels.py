@@ -62,7 +62,7 @@ _SIGNATURES = {
                                 c_void_p, c_void_p],
         "ls_attention_combine": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                  c_void_p],
-        "ls_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "ls_argmax": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "ls_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_void_p],
     },
@@ -70,6 +70,7 @@ _SIGNATURES = {
 
 _SIGNATURES["tc"] = {
     "ls_gemm_tc_token_tile": [c_int, c_int],
+    "ls_gemm_tc_k_shares": [c_int, c_int],
     "ls_attention_decode_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "ls_gemm_nt_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
@@ -126,7 +127,8 @@ def _opt(t, name, dtype=None) -> int:
 # bfloat16 work goes to the tensor cores unless this is cleared (a debugging aid)
 USE_TENSOR_CORES = [True]
 
-# launcher calls since the counter was last cleared (each is at least one kernel)
+# kernel launches since the counter was last cleared: launcher calls (each is at
+# least one kernel) plus, for a replayed graph, the calls that were recorded in it
 LAUNCHES = [0]
 
 
@@ -288,8 +290,9 @@ def attention_combine(part_acc, part_ml, out, items, n_items, nq, d) -> None:
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     rows, vocab = logits.shape
+    scratch = torch.empty(rows * 128, dtype=torch.int32, device=logits.device)
     _check(library().ls_argmax(_dev(logits, "logits", torch.float32), _dev(out, "out", torch.int32),
-                               rows, vocab, _stream()), "argmax")
+                               _dev(scratch, "scratch"), rows, vocab, _stream()), "argmax")
 
 
 def sample(logits, probs, temperature, top_p, keys, positions, out) -> None:

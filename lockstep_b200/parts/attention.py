@@ -17,6 +17,8 @@ from .base import CacheNeed, Mixer, PositionEncoding, Runtime, WeightSpec, regis
 
 
 class GQAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden_size, num_heads, num_kv_heads, head_dim, scale, window, qk_norm_eps,
                  position: PositionEncoding, runtime: Runtime):
         if num_heads % num_kv_heads:
@@ -35,6 +37,9 @@ class GQAttention(Mixer):
 
     def cache_need(self):
         return CacheNeed("paged_kv", kv_heads=self.nkv, head_dim=self.d, window=self.window)
+
+    def attention_windows(self):
+        return {self.window}
 
     def weight_specs(self):
         specs = {

@@ -67,6 +67,17 @@ class Runtime:
 class Part:
     """Base of all parts."""
 
+    # True when ``forward`` only launches kernels whose arguments are device
+    # tensors of the step context and shapes that depend on the batch's token
+    # count alone: such a part may be recorded in a CUDA graph and replayed with
+    # new contents in the same buffers.  A part that reads host-side values of the
+    # context (``ctx.portions``) in ``forward`` must leave it False.
+    graph_safe = False
+
+    def attention_windows(self) -> set[int]:
+        """Window sizes for which this part asks ``ctx.attention_plan``."""
+        return set()
+
     def weight_specs(self) -> dict[str, WeightSpec]:
         return {}
 

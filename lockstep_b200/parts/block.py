@@ -32,6 +32,13 @@ class PreNormBlock(Block):
     def cache_need(self):
         return self.mixer.cache_need()
 
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for _, part in self._children()) and self.position.graph_safe
+
+    def attention_windows(self):
+        return set().union(*(part.attention_windows() for _, part in self._children()))
+
     def weight_specs(self):
         out = {}
         for name, part in self._children():

@@ -11,6 +11,8 @@ from .base import Part, Runtime, WeightSpec, register_part
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, width: int, runtime: Runtime):
         self.vocab, self.width, self.rt = int(vocab_size), int(width), runtime
         self.table = None
@@ -31,6 +33,8 @@ class TokenEmbedding(Part):
 
 
 class LinearHead(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, width: int, tied: bool, runtime: Runtime):
         self.vocab, self.width, self.tied, self.rt = int(vocab_size), int(width), bool(tied), runtime
         self.weight = None

@@ -12,6 +12,8 @@ from .base import FeedForward, Runtime, WeightSpec, register_part
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, runtime: Runtime):
         self.h, self.i, self.rt = int(hidden_size), int(intermediate_size), runtime
         self.w_gate_up = self.w_down = None

@@ -10,6 +10,8 @@ from .base import Norm, Runtime, WeightSpec, register_part
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, width: int, eps: float, runtime: Runtime):
         self.width, self.eps, self.rt = int(width), float(eps), runtime
         self.gain: torch.Tensor | None = None

@@ -15,6 +15,8 @@ from .base import PositionEncoding, Runtime, register_part
 
 
 class Rotary(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, dim: int, theta: float, runtime: Runtime):
         if dim % 2:
             raise ValueError(f"rotary dimension must be even, got {dim}")
@@ -32,7 +34,7 @@ class Rotary(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
-    pass
+    graph_safe = True
 
 
 @register_part("position", "rotary")

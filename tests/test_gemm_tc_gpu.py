@@ -19,6 +19,8 @@ SHAPES = [
     # tokens, out features, depth
     (1, 128, 64), (8, 256, 128), (16, 384, 1024), (17, 100, 72), (33, 500, 80), (64, 1024, 200),
     (100, 130, 136), (129, 3072, 1024), (300, 264, 328), (2048, 512, 256), (5, 1187, 40),
+    # deep and narrow: K is cut into shares over a cluster (8, 6 and 5 of them)
+    (8, 1024, 3072), (40, 256, 2056), (200, 1024, 2048), (3, 200, 1344), (16, 12800, 1024),
 ]
 
 
@@ -61,11 +63,22 @@ def test_tensor_core_product_and_epilogues(t, n, k):
     assert (cs - cf).abs().max().item() <= 2e-5 * scale
 
 
-def test_a_row_has_the_same_bits_in_every_batch():
+def test_k_shares_depend_on_the_weight_alone():
+    from lockstep_b200 import kernels as K
+
+    lib = K.library("tc")
+    assert lib.ls_gemm_tc_k_shares(4096, 1024) == 4      # q, k, v of the 0.6B sizes
+    assert lib.ls_gemm_tc_k_shares(1024, 2048) == 8      # o
+    assert lib.ls_gemm_tc_k_shares(1024, 3072) == 8      # down
+    assert lib.ls_gemm_tc_k_shares(151936, 1024) == 1    # head
+    assert lib.ls_gemm_tc_k_shares(128, 64) == 1
+
+
+@pytest.mark.parametrize("k,n", [(1024, 640), (3072, 384)])
+def test_a_row_has_the_same_bits_in_every_batch(k, n):
     from lockstep_b200 import kernels as K
 
     g = torch.Generator().manual_seed(5)
-    k, n = 1024, 640
     x = torch.randn(300, k, generator=g).to(torch.bfloat16).to(dev())
     w = (torch.randn(n, k, generator=g) * 0.1).to(torch.bfloat16).to(dev())
     err = K.new_error_word(dev())

@@ -82,6 +82,8 @@ def test_replay_matches_plain(zoo, name, dtype, mode):
             "no step held a portion beside a decoded token"
     if mode == "portions":
         assert any(len(t) == 2 for s in steps for _, t, _ in s["entries"])
+    if mode == "bulk_then_single":
+        assert runner.graphs is not None and runner.graphs.replays > 50, "decode steps were not replayed from graphs"
 
 
 @pytest.mark.parametrize("name", ["A", "B", "C"])
