@@ -86,7 +86,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // HALVES = d / 64.  Shared memory of a warp: K [HALVES][32 keys][128 B], then V the same.
 template <int HALVES>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 3)
 attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_bfloat16* __restrict__ q,
                             float* __restrict__ part_acc, float* __restrict__ part_ml,
                             const int* __restrict__ work, const int* __restrict__ block_table,
@@ -102,6 +102,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + WARPS * WARP_BYTES);   // [WARPS][2]
+  const uint32_t q_smem = base + WARPS * WARP_BYTES + 128;                      // [16 rows][D] bfloat16
 
   const int* w = work + (int64_t)blockIdx.x * 8;
   const int ntok = w[2];
@@ -127,20 +128,19 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
   }
   __syncwarp();
 
-  // rows of the MMA tile are the group's query heads; this thread holds rows r0 and r0 + 8
-  const int r0 = lane >> 2, cq = (lane & 3) * 2;
-  uint32_t qa[KSTEPS][4];
+  // rows of the MMA tile are the group's query heads (zero rows pad it to 16); the
+  // tile sits in shared memory with its 16-byte chunks swizzled by the row
   {
     const __nv_bfloat16* qb = q + ((int64_t)tok * nq + kvh * group) * D;
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks) {
-      const int c = ks * 16 + cq;
-      qa[ks][0] = r0 < group ? *reinterpret_cast<const uint32_t*>(qb + r0 * D + c) : 0u;
-      qa[ks][1] = r0 + 8 < group ? *reinterpret_cast<const uint32_t*>(qb + (r0 + 8) * D + c) : 0u;
-      qa[ks][2] = r0 < group ? *reinterpret_cast<const uint32_t*>(qb + r0 * D + c + 8) : 0u;
-      qa[ks][3] = r0 + 8 < group ? *reinterpret_cast<const uint32_t*>(qb + (r0 + 8) * D + c + 8) : 0u;
+    for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += WARPS * 32) {
+      const int row = idx / (D / 8), ch = idx % (D / 8);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row < group) v = *reinterpret_cast<const uint4*>(qb + row * D + ch * 8);
+      *reinterpret_cast<uint4*>(aligned + (q_smem - base) + row * (D * 2) + ((ch ^ (row & 7)) << 4)) = v;
     }
   }
+  __syncthreads();
+  const int r0 = lane >> 2, cq = (lane & 3) * 2;   // this thread holds rows r0 and r0 + 8
 
   float acc[DTILES][4];
 #pragma unroll
@@ -151,35 +151,50 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
   const int boxes = CHUNK / rows_per_box;
   uint32_t parity = 0;
 
-  // issue the loads of chunk `c0` (first key) : K on bar_k, V on bar_v
-  auto issue = [&](int c0, bool want_k, bool want_v) {
-    if (lane != 0) return;
-    const uint32_t bytes = (uint32_t)(HALVES * HALF_BYTES);
-    if (want_k) mbar_expect_tx(bar_k, bytes);
-    if (want_v) mbar_expect_tx(bar_v, bytes);
-    for (int b = 0; b < boxes; ++b) {
-      int key = c0 + b * rows_per_box;
-      if (key >= s_hi) key = s_hi - 1;          // beyond the split's end: any page that exists
-      if (key < row_lo) key = row_lo;           // behind the window: pages may have been given back
-      int page = table_row[key / page_size];
-      if (page < 0 || page >= num_pages) {
-        ls_record_fault(err, LS_DEV_PAGE_RANGE, key);
-        page = 0;
+  // the pages of this warp's chunks, looked up once: lane 4 * i + b holds box b of chunk i
+  const int n_iter = LS_SPLIT / (WARPS * CHUNK);
+  int my_page = 0;
+  {
+    const int i = lane >> 2, b = lane & 3;
+    if (i < n_iter && b < boxes) {
+      const int c0 = s_lo + (i * WARPS + warp) * CHUNK;
+      if (c0 < s_hi && c0 + CHUNK > row_lo) {
+        int key = c0 + b * rows_per_box;
+        if (key >= s_hi) key = s_hi - 1;          // beyond the split's end: any page that exists
+        if (key < row_lo) key = row_lo;           // behind the window: pages may have been given back
+        my_page = table_row[key / page_size];
+        if (my_page < 0 || my_page >= num_pages) {
+          ls_record_fault(err, LS_DEV_PAGE_RANGE, key);
+          my_page = 0;
+        }
       }
-      const int in_page = ((c0 + b * rows_per_box) % page_size) / rows_per_box * rows_per_box;
-      const int y_k = ((page * 2 + 0) * nkv + kvh) * page_size + in_page;
-      const int y_v = ((page * 2 + 1) * nkv + kvh) * page_size + in_page;
+    }
+  }
+
+  // issue the loads of chunk i (first key c0): K on bar_k, V on bar_v.  Called by the whole warp.
+  auto issue = [&](int i, int c0, bool want_k, bool want_v) {
+    const uint32_t bytes = (uint32_t)(HALVES * HALF_BYTES);
+    if (lane == 0) {
+      if (want_k) mbar_expect_tx(bar_k, bytes);
+      if (want_v) mbar_expect_tx(bar_v, bytes);
+    }
+    for (int b = 0; b < boxes; ++b) {
+      const int page = __shfl_sync(0xffffffffu, my_page, i * 4 + b);
+      if (lane == 0) {
+        const int in_page = ((c0 + b * rows_per_box) % page_size) / rows_per_box * rows_per_box;
+        const int y_k = ((page * 2 + 0) * nkv + kvh) * page_size + in_page;
+        const int y_v = ((page * 2 + 1) * nkv + kvh) * page_size + in_page;
 #pragma unroll
-      for (int h = 0; h < HALVES; ++h) {
-        const uint32_t off = (uint32_t)(h * HALF_BYTES + b * rows_per_box * 128);
-        if (want_k) tma_load_2d(k_smem + off, &map, h * 64, y_k, bar_k);
-        if (want_v) tma_load_2d(v_smem + off, &map, h * 64, y_v, bar_v);
+        for (int h = 0; h < HALVES; ++h) {
+          const uint32_t off = (uint32_t)(h * HALF_BYTES + b * rows_per_box * 128);
+          if (want_k) tma_load_2d(k_smem + off, &map, h * 64, y_k, bar_k);
+          if (want_v) tma_load_2d(v_smem + off, &map, h * 64, y_v, bar_v);
+        }
       }
     }
   };
 
   // chunks of this warp: keys c0 = s_lo + (i * WARPS + warp) * CHUNK that are not wholly outside [row_lo, s_hi)
-  const int n_iter = LS_SPLIT / (WARPS * CHUNK);
   auto chunk_start = [&](int i) { return s_lo + (i * WARPS + warp) * CHUNK; };
   auto chunk_live = [&](int i) {
     const int c0 = chunk_start(i);
@@ -188,7 +203,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
 
   int it = 0;
   while (it < n_iter && !chunk_live(it)) ++it;
-  if (it < n_iter) issue(chunk_start(it), true, true);
+  if (it < n_iter) issue(it, chunk_start(it), true, true);
 
   while (it < n_iter) {
     const int c0 = chunk_start(it);
@@ -206,16 +221,22 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
     for (int ks = 0; ks < KSTEPS; ++ks) {
       const int half = ks / 4;
       const int chunk16 = (ks % 4) * 2;          // 16-byte chunk of the 128-byte row
+      const int j = lane >> 3;                   // matrix this lane addresses
+      uint32_t qa[4];
+      {
+        const int row = (j & 1) * 8 + (lane & 7);
+        const int ch = ks * 2 + (j >> 1);
+        ldmatrix_x4(q_smem + row * (D * 2) + ((ch ^ (row & 7)) << 4), qa);
+      }
 #pragma unroll
       for (int np = 0; np < 2; ++np) {           // two key tiles per ldmatrix.x4
-        const int j = lane >> 3;                 // matrix this lane addresses
         const int key = np * 16 + (j >> 1) * 8 + (lane & 7);
         const int ch = chunk16 + (j & 1);
         const uint32_t addr = k_smem + half * HALF_BYTES + key * 128 + ((ch ^ (key & 7)) << 4);
         uint32_t b[4];
         ldmatrix_x4(addr, b);
-        mma_bf16(s[np * 2 + 0], qa[ks], b[0], b[1]);
-        mma_bf16(s[np * 2 + 1], qa[ks], b[2], b[3]);
+        mma_bf16(s[np * 2 + 0], qa, b[0], b[1]);
+        mma_bf16(s[np * 2 + 1], qa, b[2], b[3]);
       }
     }
     __syncwarp();
@@ -225,7 +246,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
       // the generic-proxy reads above are ordered before the async-proxy writes
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (more) issue(chunk_start(next), true, false);
+    if (more) issue(next, chunk_start(next), true, false);
 
     // mask, online softmax (rows r0 and r0 + 8; columns nt * 8 + cq, +1)
     float tile_max[2] = {-CUDART_INF_F, -CUDART_INF_F};
@@ -311,7 +332,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
     __syncwarp();
     if (more) {
       if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      issue(chunk_start(next), false, true);
+      issue(next, chunk_start(next), false, true);
     }
     parity ^= 1u;
     it = next;
@@ -383,7 +404,7 @@ template <int HALVES>
 int launch(const CUtensorMap& map, const void* q, float* part_acc, float* part_ml, const int* work,
            int n_work, const int* block_table, int table_stride, int nq, int nkv, int page_size,
            int num_pages, int window, float scale, int* err, cudaStream_t stream) {
-  const size_t smem = (size_t)WARPS * 2 * HALVES * CHUNK * 128 + WARPS * 2 * 8 + 1024;
+  const size_t smem = (size_t)WARPS * 2 * HALVES * CHUNK * 128 + 128 + 16 * HALVES * 128 + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_decode_mma_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,

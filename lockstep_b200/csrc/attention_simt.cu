@@ -368,16 +368,30 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
   const int h = blockIdx.y;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float acc = 0.f, m_run = -CUDART_INF_F, l_run = 0.f;
-    for (int s = 0; s < n; ++s) {
-      const int64_t slot = (int64_t)first + (int64_t)s * stride;
-      const float m_s = part_ml[(slot * nq + h) * 2 + 0];
-      const float l_s = part_ml[(slot * nq + h) * 2 + 1];
-      float alpha, beta, m_new;
-      ls_fold_scales(m_run, m_s, alpha, beta, m_new);
-      if (m_s != -CUDART_INF_F) {
-        acc = ls_fold_value(acc, alpha, part_acc[(slot * nq + h) * d + c], beta);
-        l_run = ls_fold_value(l_run, alpha, l_s, beta);
-        m_run = m_new;
+    // the partials of eight splits are fetched together (independent loads), then
+    // folded one after the other in ascending order
+    for (int s0 = 0; s0 < n; s0 += 8) {
+      float m_s[8], l_s[8], a_s[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (s0 + j < n) {
+          const int64_t slot = (int64_t)first + (int64_t)(s0 + j) * stride;
+          m_s[j] = part_ml[(slot * nq + h) * 2 + 0];
+          l_s[j] = part_ml[(slot * nq + h) * 2 + 1];
+          a_s[j] = part_acc[(slot * nq + h) * d + c];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (s0 + j < n) {
+          float alpha, beta, m_new;
+          ls_fold_scales(m_run, m_s[j], alpha, beta, m_new);
+          if (m_s[j] != -CUDART_INF_F) {
+            acc = ls_fold_value(acc, alpha, a_s[j], beta);
+            l_run = ls_fold_value(l_run, alpha, l_s[j], beta);
+            m_run = m_new;
+          }
+        }
       }
     }
     out[((int64_t)tok * nq + h) * d + c] = ls_from_float<T>(l_run > 0.f ? __fdiv_rn(acc, l_run) : 0.f);
