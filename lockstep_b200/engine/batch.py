@@ -37,10 +37,11 @@ class AttentionPlan:
     n_slots: int
 
 
-def plan_attention(portions, window: int, split_size: int):
+def plan_attention(portions, window: int, split_size: int, tile_tokens: int = TILE_TOKENS):
     """portions: (slot, token offset, start position, length) per entry.
     Returns numpy arrays (tile_work [n,8], split_work [n,8], combine [n,4]) and
-    the number of scratch slots."""
+    the number of scratch slots.  Tiles hold up to ``tile_tokens`` tokens and are
+    listed longest context first, so that the heaviest start first."""
     tile, split, combine = [], [], []
     n_slots = 0
     for slot, off, start, length in portions:
@@ -52,12 +53,13 @@ def plan_attention(portions, window: int, split_size: int):
                 split.append((slot, off, 1, start, s, s + 1, n_slots, 0))
                 n_slots += 1
         else:
-            for i in range(0, length, TILE_TOKENS):
-                ntok = min(TILE_TOKENS, length - i)
+            for i in range(0, length, tile_tokens):
+                ntok = min(tile_tokens, length - i)
                 pos0 = start + i
                 lo = max(0, pos0 - window + 1) if window else 0
                 tile.append((slot, off + i, ntok, pos0, lo // split_size,
                              (pos0 + ntok - 1) // split_size + 1, -1, 0))
+    tile.sort(key=lambda item: -(item[3] + item[2]))
     as_np = lambda rows, w: np.asarray(rows, dtype=np.int32).reshape(-1, w)
     return as_np(tile, 8), as_np(split, 8), as_np(combine, 4), n_slots
 
@@ -93,12 +95,15 @@ class StepContext:
         self.positions = dev[t:2 * t]
         self.token_slot = dev[2 * t:3 * t]
         self.wanted_rows = dev[3 * t:3 * t + self.n_wanted]
-        self._plans: dict[int, AttentionPlan] = {}
+        self._plans: dict[tuple[int, int], AttentionPlan] = {}
 
-    def attention_plan(self, window: int) -> AttentionPlan:
-        plan = self._plans.get(window)
+    def attention_plan(self, window: int, tile_tokens: int = TILE_TOKENS) -> AttentionPlan:
+        """Work lists for attention with ``window`` (0: all keys): portions of two or
+        more tokens cut into tiles of ``tile_tokens``, single tokens into one item
+        per split plus a combine item."""
+        plan = self._plans.get((window, tile_tokens))
         if plan is None:
-            tile, split, combine, n_slots = plan_attention(self.portions, window, self.split_size)
+            tile, split, combine, n_slots = plan_attention(self.portions, window, self.split_size, tile_tokens)
             flat = np.concatenate([tile.reshape(-1), split.reshape(-1), combine.reshape(-1)])
             dev = torch.from_numpy(flat).to(self.device) if flat.size else None
             a, b = tile.size, tile.size + split.size
@@ -107,5 +112,5 @@ class StepContext:
                 split_work=dev[a:b].view(-1, 8) if split.size else None, n_split=len(split),
                 combine_items=dev[b:].view(-1, 4) if combine.size else None, n_combine=len(combine),
                 n_slots=n_slots)
-            self._plans[window] = plan
+            self._plans[(window, tile_tokens)] = plan
         return plan

@@ -52,7 +52,7 @@ class StaticStepContext:
         self.copied = torch.cuda.Event()
         self._pending = False
 
-    def attention_plan(self, window: int) -> AttentionPlan:
+    def attention_plan(self, window: int, tile_tokens: int = 0) -> AttentionPlan:
         try:
             return self._plans[window]
         except KeyError:

@@ -73,10 +73,17 @@ class GQAttention(Mixer):
                              ctx.token_slot, cache.block_table, nq, nkv, d, rot_dim,
                              self.qk_norm_eps or 0.0, cache.writes, self.rt.err)
         attn = torch.empty((t, nq * d), dtype=dt, device=dev)
-        plan = ctx.attention_plan(self.window)
-        if plan.n_tile:
-            K.attention_tile(q, cache.pages, attn, None, None, plan.tile_work, plan.n_tile,
-                             cache.block_table, nq, nkv, d, self.window, self.scale, self.rt.err)
+        plan, done = None, False
+        if not self.exact and d in (64, 128):
+            plan = ctx.attention_plan(self.window, K.attention_prefill_tile_tokens())
+            done = not plan.n_tile or K.attention_prefill_mma(
+                q, cache.pages, attn, plan.tile_work, plan.n_tile, cache.block_table, nq, nkv, d,
+                self.window, self.scale, self.rt.err)
+        if not done:
+            plan = ctx.attention_plan(self.window)
+            if plan.n_tile:
+                K.attention_tile(q, cache.pages, attn, None, None, plan.tile_work, plan.n_tile,
+                                 cache.block_table, nq, nkv, d, self.window, self.scale, self.rt.err)
         if plan.n_split:
             part_acc = torch.empty((plan.n_slots, nq, d), dtype=torch.float32, device=dev)
             part_ml = torch.empty((plan.n_slots, nq, 2), dtype=torch.float32, device=dev)

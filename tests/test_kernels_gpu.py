@@ -166,12 +166,16 @@ def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel):
     split = k.attention_split_size()
     table = torch.full((2, 256), -1, dtype=torch.int32)
     table[1, :len(table_row)] = torch.tensor(table_row, dtype=torch.int32)
-    tile, sp, comb, n_slots = plan_attention([(1, 0, start, n)], window, split)
+    prefill_mma = decode_kernel == "prefill_mma"
+    tile, sp, comb, n_slots = plan_attention([(1, 0, start, n)], window, split, 64 if prefill_mma else 16)
     D = dev()
     err = k.new_error_word(D)
     qd, pd, td = q.reshape(n, nq * d).contiguous().to(D), pages.to(D), table.to(D)
     out = torch.empty(n, nq * d, dtype=q.dtype, device=D)
-    if len(tile):
+    if len(tile) and prefill_mma:
+        assert k.attention_prefill_mma(qd, pd, out, torch.from_numpy(tile).to(D), len(tile), td, nq, nkv, d,
+                                       window, scale, err)
+    elif len(tile):
         k.attention_tile(qd, pd, out, None, None, torch.from_numpy(tile).to(D), len(tile), td, nq, nkv, d,
                          window, scale, err)
     if len(sp):
@@ -182,7 +186,7 @@ def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel):
         if decode_kernel == "mma":
             done = k.attention_decode_mma(qd, pd, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err)
             assert done
-        elif decode_kernel:
+        elif decode_kernel and not prefill_mma:
             done = k.attention_decode(qd, pd, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err)
             assert done
         if not done:
@@ -212,6 +216,11 @@ def test_attention_prefix_portion_and_decode(dtype, nq, nkv, d, page, window):
     # the last 150 tokens as one portion (crosses the split edge at 512 and ends off a tile edge)
     got = run_attention(k, q[550:], pages, ids, 550, window, scale, False)
     assert (got - want[550:]).abs().max() <= bound
+    if dtype == torch.bfloat16 and d in (64, 128):
+        # the tensor-core kernel: a whole prompt, a ragged tail, two tokens at a tile's edge
+        for lo, hi in [(0, 700), (550, 700), (0, 1), (63, 65), (640, 642), (100, 229)]:
+            got = run_attention(k, q[lo:hi], pages, ids, lo, window, scale, "prefill_mma")
+            assert (got - want[lo:hi]).abs().max() <= bound, (lo, hi)
     # single tokens at telling places: first, page edges, split edges, last
     for pos in [0, 1, page - 1, page, 255, 256, 257, 511, 512, 699]:
         sub_pages, sub_ids = pages, ids
