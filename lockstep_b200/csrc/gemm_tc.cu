@@ -62,6 +62,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -154,7 +158,11 @@ struct Shape {
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
   static constexpr int STAGES_FIT = (200 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
-  static constexpr int ACC_COLS = tmem_cols(A_TILES * BN);
+  static constexpr int REGION_COLS = A_TILES * BN;      // one accumulator (gate and up for silu-mul)
+  // two accumulator regions where they fit in registers as running sums: a block that
+  // walks several shares of K fills one while the other is drained
+  static constexpr bool WALKS_SHARES = REGION_COLS <= 128;
+  static constexpr int ACC_COLS = tmem_cols(WALKS_SHARES ? 2 * REGION_COLS : REGION_COLS);
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
 };
 
@@ -177,35 +185,49 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
 
 constexpr int MAX_SHARES = 8;
 
+// K is cut into `shares` shares of kb_per_share 64-element blocks.  An output
+// element is  ((0 + p_0) + p_1) + ... + p_{shares-1}  with p_r the float32
+// accumulation of share r in ascending k.  The shares of a tile run either in
+// the `shares` blocks of a cluster (in_cluster: few tokens, many blocks wanted)
+// or one after the other in one block that keeps the running sum in registers;
+// both give the same bits.
 template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share, int shares,
-               int* err) {
+               int in_cluster, int* err) {
   using S = Shape<BN, EPI>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)S::STAGES * S::STAGE_BYTES);
-  uint64_t* full = bars;                   // [STAGES]
-  uint64_t* empty = bars + S::STAGES;      // [STAGES]
-  uint64_t* accum = bars + 2 * S::STAGES;  // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S::STAGES + 1);
+  uint64_t* full = bars;                        // [STAGES] operands landed
+  uint64_t* empty = bars + S::STAGES;           // [STAGES] MMAs have read the stage
+  uint64_t* acc_full = bars + 2 * S::STAGES;    // [2] a share's accumulator is complete
+  uint64_t* acc_empty = acc_full + 2;           // [2] the epilogue has drained it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* failed = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM;
   const int t0 = blockIdx.y * BN;
   const int total_kb = (K + BK - 1) / BK;
-  const int kb_first = (int)blockIdx.z * kb_per_share;          // this block's share of K
-  const int num_kb = (total_kb - kb_first < kb_per_share ? total_kb - kb_first : kb_per_share);
+  const int first_share = in_cluster ? (int)blockIdx.z : 0;
+  const int my_shares = in_cluster ? 1 : shares;
+  const int kb_begin = first_share * kb_per_share;
+  int kb_end = (first_share + my_shares) * kb_per_share;
+  if (kb_end > total_kb) kb_end = total_kb;
+  const int num_kb = kb_end - kb_begin;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum, 1);
+    for (int r = 0; r < 2; ++r) {
+      mbar_init(&acc_full[r], 1);
+      mbar_init(&acc_empty[r], 4);
+    }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -234,7 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
         mbar_expect_tx(&full[s], S::STAGE_BYTES);
-        const int kx = (kb_first + kb) * BK;
+        const int kx = (kb_begin + kb) * BK;
         tma_load_2d(stage, &map_w, kx, n0, &full[s]);
         if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kx, N + n0, &full[s]);
         tma_load_2d(stage + S::A_TILES * A_BYTES, &map_x, kx, t0, &full[s]);
@@ -251,73 +273,125 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BM, BN);
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % S::STAGES;
-        const uint32_t phase = (uint32_t)(kb / S::STAGES) & 1u;
-        if (*failed || !mbar_wait(&full[s], phase)) {
+      int kb = 0;
+      for (int r = 0; r < my_shares && ok; ++r) {
+        const int region = S::WALKS_SHARES ? (r & 1) : 0;
+        const uint32_t acc_addr = tmem_base + (uint32_t)(region * S::REGION_COLS);
+        // the region is free once the epilogue drained the share that used it before
+        if (r >= 2 && !mbar_wait(&acc_empty[region], (uint32_t)((r >> 1) - 1) & 1u)) {
           *failed = 1;
-          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 200 + s);
+          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 250 + region);
           ok = false;
           break;
         }
         fence_after_sync();
-        const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+        int share_end = (r + 1) * kb_per_share;
+        if (share_end > num_kb) share_end = num_kb;
+        for (bool first = true; kb < share_end; ++kb) {
+          const int s = kb % S::STAGES;
+          const uint32_t phase = (uint32_t)(kb / S::STAGES) & 1u;
+          if (*failed || !mbar_wait(&full[s], phase)) {
+            *failed = 1;
+            ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 200 + s);
+            ok = false;
+            break;
+          }
+          fence_after_sync();
+          const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          const uint64_t bdesc = smem_desc(stage + S::A_TILES * A_BYTES + k * UMMA_K * 2);
-          const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
-          umma(tmem_base, smem_desc(stage + k * UMMA_K * 2), bdesc, idesc, acc);
-          if (EPI == 2) umma(tmem_base + BN, smem_desc(stage + A_BYTES + k * UMMA_K * 2), bdesc, idesc, acc);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t bdesc = smem_desc(stage + S::A_TILES * A_BYTES + k * UMMA_K * 2);
+            const uint32_t acc = (first && k == 0) ? 0u : 1u;
+            umma(acc_addr, smem_desc(stage + k * UMMA_K * 2), bdesc, idesc, acc);
+            if (EPI == 2) umma(acc_addr + BN, smem_desc(stage + A_BYTES + k * UMMA_K * 2), bdesc, idesc, acc);
+          }
+          first = false;
+          umma_commit(&empty[s]);
         }
-        umma_commit(&empty[s]);
+        if (ok) umma_commit(&acc_full[region]);
       }
-      if (ok) umma_commit(accum);
     }
   } else {
     // epilogue: warp w may touch tensor-memory lanes 32*(w%4) .. +32
     const int quad = warp & 3;
-    const int n = n0 + quad * 32 + lane;
-    bool ok = mbar_wait(accum, 0);
-    if (!ok) {
-      *failed = 1;
-      if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 300 + quad);
-    }
-    ok = __all_sync(0xffffffffu, ok);
-    fence_after_sync();
+    const int row = quad * 32 + lane;
+    const int n = n0 + row;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
-    if (ok && shares == 1) {
+
+    if (my_shares == 1) {
+      bool ok = mbar_wait(&acc_full[0], 0);
+      if (!ok) {
+        *failed = 1;
+        if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 300 + quad);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      fence_after_sync();
+      if (ok && !in_cluster) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (t0 + c0 >= T) break;          // uniform across the warp
-        uint32_t g[16], u[16];
-        tmem_ld16(lane_base + c0, g);
-        if (EPI == 2) tmem_ld16(lane_base + BN + c0, u);
-        tmem_ld_wait();
-        if (n < N) {
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          if (t0 + c0 >= T) break;          // uniform across the warp
+          uint32_t g[16], u[16];
+          tmem_ld16(lane_base + c0, g);
+          if (EPI == 2) tmem_ld16(lane_base + BN + c0, u);
+          tmem_ld_wait();
+          if (n < N) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c0 + j;
-            if (t < T)
-              epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, __uint_as_float(g[j]),
-                                      EPI == 2 ? __uint_as_float(u[j]) : 0.f);
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c0 + j;
+              if (t < T)
+                epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, 0.f + __uint_as_float(g[j]),
+                                        EPI == 2 ? 0.f + __uint_as_float(u[j]) : 0.f);
+            }
           }
         }
-      }
-    } else if (ok) {
-      // leave this share's partial tile in shared memory: part[column][row], float32
-      float* part = reinterpret_cast<float*>(aligned);
-      const int row = quad * 32 + lane;
+      } else if (ok) {
+        // leave this share's partial tile in shared memory: part[column][row], float32
+        float* part = reinterpret_cast<float*>(aligned);
 #pragma unroll 1
-      for (int c0 = 0; c0 < S::A_TILES * BN; c0 += 16) {
-        uint32_t g[16];
-        tmem_ld16(lane_base + c0, g);
-        tmem_ld_wait();
+        for (int c0 = 0; c0 < S::REGION_COLS; c0 += 16) {
+          uint32_t g[16];
+          tmem_ld16(lane_base + c0, g);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) part[(c0 + j) * BM + row] = __uint_as_float(g[j]);
+          for (int j = 0; j < 16; ++j) part[(c0 + j) * BM + row] = __uint_as_float(g[j]);
+        }
+      }
+    } else if constexpr (S::WALKS_SHARES) {
+      // this block walks all shares: the running sum of the partials stays in registers
+      float sum[S::REGION_COLS];
+      bool ok = true;
+      for (int r = 0; r < my_shares; ++r) {
+        const int region = r & 1;
+        bool got = mbar_wait(&acc_full[region], (uint32_t)(r >> 1) & 1u);
+        if (!got) {
+          *failed = 1;
+          if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 350 + quad);
+        }
+        ok = __all_sync(0xffffffffu, got);
+        if (!ok) break;
+        fence_after_sync();
+#pragma unroll
+        for (int c0 = 0; c0 < S::REGION_COLS; c0 += 16) {
+          uint32_t g[16];
+          tmem_ld16(lane_base + (uint32_t)(region * S::REGION_COLS) + c0, g);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sum[c0 + j] = (r == 0 ? 0.f : sum[c0 + j]) + __uint_as_float(g[j]);
+        }
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[region]);
+      }
+      if (ok && n < N) {
+#pragma unroll
+        for (int c = 0; c < BN; ++c) {
+          const int t = t0 + c;
+          if (t < T) epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, sum[c], EPI == 2 ? sum[BN + c] : 0.f);
+        }
       }
     }
   }
-  if (shares > 1) {
+  if (in_cluster) {
     // all shares have left their partials; each block folds the columns c with
     // c % shares == its rank, reading every share in ascending order
     __syncwarp();
@@ -395,9 +469,30 @@ bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int64_t ld, in
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+struct Plan {
+  int shares, kb_per_share, in_cluster, bn;
+};
+
+// How a product of T tokens with a weight of N rows and depth K runs.  The shares
+// of K depend on the weight alone; T only decides where they run and how wide
+// the token tile is, neither of which changes a sum.
+Plan make_plan(int T, int N, int K, int epilogue) {
+  Plan p;
+  const int total_kb = (K + BK - 1) / BK;
+  const int want = ls_gemm_tc_k_shares(N, K);
+  p.kb_per_share = (total_kb + want - 1) / want;
+  p.shares = (total_kb + p.kb_per_share - 1) / p.kb_per_share;    // every share has work
+  p.in_cluster = p.shares > 1 && T <= 128;
+  int cap = epilogue == 2 ? 128 : 256;
+  if (p.shares > 1 && !p.in_cluster) cap = epilogue == 2 ? 64 : 128;   // running sums in registers
+  p.bn = 16;
+  while (p.bn < T && p.bn < cap) p.bn *= 2;
+  return p;
+}
+
 template <int BN, int EPI, typename TC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int64_t ldc,
-           int* err, cudaStream_t stream) {
+           const Plan& plan, int* err, cudaStream_t stream) {
   using S = Shape<BN, EPI>;
   static bool configured = false;
   if (!configured) {
@@ -406,12 +501,9 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, 
       return LS_E_SMEM;
     configured = true;
   }
-  const int total_kb = (K + BK - 1) / BK;
-  const int want = ls_gemm_tc_k_shares(N, K);
-  const int kb_per_share = (total_kb + want - 1) / want;
-  const int shares = (total_kb + kb_per_share - 1) / kb_per_share;   // every share has work
+  if (plan.shares > 1 && !plan.in_cluster && !S::WALKS_SHARES) return LS_E_SIZE;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((N + BM - 1) / BM, (T + BN - 1) / BN, shares);
+  cfg.gridDim = dim3((N + BM - 1) / BM, (T + BN - 1) / BN, plan.in_cluster ? plan.shares : 1);
   cfg.blockDim = dim3(192);
   cfg.dynamicSmemBytes = S::SMEM;
   cfg.stream = stream;
@@ -419,36 +511,33 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, 
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = shares;
+  attr[0].val.clusterDim.z = plan.shares;
   cfg.attrs = attr;
-  cfg.numAttrs = shares > 1 ? 1 : 0;
+  cfg.numAttrs = plan.in_cluster ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC>, mw, mx, (TC*)C, T, N, K, ldc,
-                                     kb_per_share, shares, err);
+                                     plan.kb_per_share, plan.shares, plan.in_cluster, err);
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }
 
 template <int BN>
 int dispatch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int c_dtype, int T, int N, int K,
-             int64_t ldc, int epilogue, int* err, cudaStream_t stream) {
+             int64_t ldc, int epilogue, const Plan& plan, int* err, cudaStream_t stream) {
   typedef __nv_bfloat16 bf16;
-  if (epilogue == 0 && c_dtype == LS_BF16) return launch<BN, 0, bf16>(mw, mx, C, T, N, K, ldc, err, stream);
-  if (epilogue == 0 && c_dtype == LS_F32) return launch<BN, 0, float>(mw, mx, C, T, N, K, ldc, err, stream);
-  if (epilogue == 1 && c_dtype == LS_F32) return launch<BN, 1, float>(mw, mx, C, T, N, K, ldc, err, stream);
+  if (epilogue == 0 && c_dtype == LS_BF16) return launch<BN, 0, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+  if (epilogue == 0 && c_dtype == LS_F32) return launch<BN, 0, float>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+  if (epilogue == 1 && c_dtype == LS_F32) return launch<BN, 1, float>(mw, mx, C, T, N, K, ldc, plan, err, stream);
   if (epilogue == 2 && c_dtype == LS_BF16) {
-    if constexpr (BN <= 128) return launch<BN, 2, bf16>(mw, mx, C, T, N, K, ldc, err, stream);
+    if constexpr (BN <= 128) return launch<BN, 2, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream);
   }
   return LS_E_DTYPE;
 }
 
 }  // namespace
 
-// The token tile for T tokens (a function of T alone; it does not change any sum).
-LS_API int ls_gemm_tc_token_tile(int T, int epilogue) {
-  const int cap = epilogue == 2 ? 128 : 256;
-  int bn = 16;
-  while (bn < T && bn < cap) bn *= 2;
-  return bn;
+// The token tile for T tokens of a product with an (N, K) weight (it does not change any sum).
+LS_API int ls_gemm_tc_token_tile(int T, int N, int K, int epilogue) {
+  return make_plan(T, N, K, epilogue).bn;
 }
 
 // X [T, K] and W [N, K] (or [2N, K] for silu-mul) bfloat16 with row pitches ldx,
@@ -462,17 +551,18 @@ LS_API int ls_gemm_nt_tc(const void* X, const void* W, void* C, int c_dtype, int
   if ((K % 8) || (ldx % 8) || (ldw % 8)) return LS_E_ALIGN;     // 16-byte row pitch
   if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LS_E_ALIGN;
   if ((N + BM - 1) / BM > 2147483647 / 2 || (T + 15) / 16 > 65535) return LS_E_SIZE;
-  const int bn = ls_gemm_tc_token_tile(T, epilogue);
+  const Plan plan = make_plan(T, N, K, epilogue);
+  const int bn = plan.bn;
   const int w_rows = epilogue == 2 ? 2 * N : N;
   CUtensorMap mw, mx;
   if (!make_map(&mw, W, w_rows, K, ldw, BM)) return LS_E_SIZE;
   if (!make_map(&mx, X, T, K, ldx, bn)) return LS_E_SIZE;
   switch (bn) {
-    case 16: return dispatch<16>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, err, stream);
-    case 32: return dispatch<32>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, err, stream);
-    case 64: return dispatch<64>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, err, stream);
-    case 128: return dispatch<128>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, err, stream);
-    case 256: return dispatch<256>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, err, stream);
+    case 16: return dispatch<16>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 32: return dispatch<32>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 64: return dispatch<64>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 128: return dispatch<128>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 256: return dispatch<256>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
   }
   return LS_E_SIZE;
 }

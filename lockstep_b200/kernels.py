@@ -69,7 +69,7 @@ _SIGNATURES = {
 }
 
 _SIGNATURES["tc"] = {
-    "ls_gemm_tc_token_tile": [c_int, c_int],
+    "ls_gemm_tc_token_tile": [c_int, c_int, c_int, c_int],
     "ls_gemm_tc_k_shares": [c_int, c_int],
     "ls_attention_decode_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],

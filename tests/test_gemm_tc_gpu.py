@@ -21,6 +21,8 @@ SHAPES = [
     (100, 130, 136), (129, 3072, 1024), (300, 264, 328), (2048, 512, 256), (5, 1187, 40),
     # deep and narrow: K is cut into shares over a cluster (8, 6 and 5 of them)
     (8, 1024, 3072), (40, 256, 2056), (200, 1024, 2048), (3, 200, 1344), (16, 12800, 1024),
+    # more than 128 tokens: one block walks the shares and keeps the running sum in registers
+    (300, 256, 2048), (1000, 384, 3080), (129, 1024, 1024),
 ]
 
 
