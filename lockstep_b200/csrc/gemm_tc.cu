@@ -62,10 +62,6 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                : "memory");
 }
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -139,6 +135,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -149,7 +152,7 @@ __device__ __forceinline__ void fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-constexpr int tmem_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
+__host__ __device__ constexpr int tmem_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
 template <int BN, int EPI>
 struct Shape {
@@ -159,10 +162,8 @@ struct Shape {
   static constexpr int STAGES_FIT = (200 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
   static constexpr int REGION_COLS = A_TILES * BN;      // one accumulator (gate and up for silu-mul)
-  // two accumulator regions where they fit in registers as running sums: a block that
-  // walks several shares of K fills one while the other is drained
-  static constexpr bool WALKS_SHARES = REGION_COLS <= 128;
-  static constexpr int ACC_COLS = tmem_cols(WALKS_SHARES ? 2 * REGION_COLS : REGION_COLS);
+  // a block that walks several shares of K gives each share an accumulator of its own
+  static constexpr int MAX_WALKED = 512 / REGION_COLS;  // shares that fit in tensor memory
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
 };
 
@@ -189,8 +190,8 @@ constexpr int MAX_SHARES = 8;
 // element is  ((0 + p_0) + p_1) + ... + p_{shares-1}  with p_r the float32
 // accumulation of share r in ascending k.  The shares of a tile run either in
 // the `shares` blocks of a cluster (in_cluster: few tokens, many blocks wanted)
-// or one after the other in one block that keeps the running sum in registers;
-// both give the same bits.
+// or one after the other in one block, each into an accumulator of its own in
+// tensor memory, summed in the epilogue; both give the same bits.
 template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -203,9 +204,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)S::STAGES * S::STAGE_BYTES);
   uint64_t* full = bars;                        // [STAGES] operands landed
   uint64_t* empty = bars + S::STAGES;           // [STAGES] MMAs have read the stage
-  uint64_t* acc_full = bars + 2 * S::STAGES;    // [2] a share's accumulator is complete
-  uint64_t* acc_empty = acc_full + 2;           // [2] the epilogue has drained it
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* acc_full = bars + 2 * S::STAGES;    // [1] every accumulator of this block is complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile uint32_t* failed = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -218,23 +218,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   int kb_end = (first_share + my_shares) * kb_per_share;
   if (kb_end > total_kb) kb_end = total_kb;
   const int num_kb = kb_end - kb_begin;
+  const uint32_t acc_cols = (uint32_t)tmem_cols(my_shares * S::REGION_COLS);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int r = 0; r < 2; ++r) {
-      mbar_init(&acc_full[r], 1);
-      mbar_init(&acc_empty[r], 4);
-    }
+    mbar_init(acc_full, 1);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"(S::ACC_COLS)
+                 "r"(acc_cols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -275,16 +273,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       bool ok = true;
       int kb = 0;
       for (int r = 0; r < my_shares && ok; ++r) {
-        const int region = S::WALKS_SHARES ? (r & 1) : 0;
-        const uint32_t acc_addr = tmem_base + (uint32_t)(region * S::REGION_COLS);
-        // the region is free once the epilogue drained the share that used it before
-        if (r >= 2 && !mbar_wait(&acc_empty[region], (uint32_t)((r >> 1) - 1) & 1u)) {
-          *failed = 1;
-          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 250 + region);
-          ok = false;
-          break;
-        }
-        fence_after_sync();
+        const uint32_t acc_addr = tmem_base + (uint32_t)(r * S::REGION_COLS);
         int share_end = (r + 1) * kb_per_share;
         if (share_end > num_kb) share_end = num_kb;
         for (bool first = true; kb < share_end; ++kb) {
@@ -308,8 +297,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           first = false;
           umma_commit(&empty[s]);
         }
-        if (ok) umma_commit(&acc_full[region]);
       }
+      if (ok) umma_commit(acc_full);
     }
   } else {
     // epilogue: warp w may touch tensor-memory lanes 32*(w%4) .. +32
@@ -318,75 +307,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int n = n0 + row;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
 
-    if (my_shares == 1) {
-      bool ok = mbar_wait(&acc_full[0], 0);
-      if (!ok) {
-        *failed = 1;
-        if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 300 + quad);
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      fence_after_sync();
-      if (ok && !in_cluster) {
+    bool ok = mbar_wait(acc_full, 0);
+    if (!ok) {
+      *failed = 1;
+      if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 300 + quad);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    fence_after_sync();
+    if (ok && in_cluster) {
+      // leave this share's partial tile in shared memory: part[column][row], float32
+      float* part = reinterpret_cast<float*>(aligned);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          if (t0 + c0 >= T) break;          // uniform across the warp
-          uint32_t g[16], u[16];
-          tmem_ld16(lane_base + c0, g);
-          if (EPI == 2) tmem_ld16(lane_base + BN + c0, u);
-          tmem_ld_wait();
-          if (n < N) {
+      for (int c0 = 0; c0 < S::REGION_COLS; c0 += 16) {
+        uint32_t g[16];
+        tmem_ld16(lane_base + c0, g);
+        tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int t = t0 + c0 + j;
-              if (t < T)
-                epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, 0.f + __uint_as_float(g[j]),
-                                        EPI == 2 ? 0.f + __uint_as_float(u[j]) : 0.f);
+        for (int j = 0; j < 16; ++j) part[(c0 + j) * BM + row] = __uint_as_float(g[j]);
+      }
+    } else if (ok) {
+      // sum the shares' accumulators in ascending order, eight columns at a time
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 8) {
+        if (t0 + c0 >= T) break;          // uniform across the warp
+        uint32_t g[S::MAX_WALKED < MAX_SHARES ? S::MAX_WALKED : MAX_SHARES][8];
+        uint32_t u[EPI == 2 ? (S::MAX_WALKED < MAX_SHARES ? S::MAX_WALKED : MAX_SHARES) : 1][8];
+#pragma unroll
+        for (int r = 0; r < MAX_SHARES; ++r) {
+          if (r < S::MAX_WALKED && r < my_shares) {
+            tmem_ld8(lane_base + (uint32_t)(r * S::REGION_COLS + c0), g[r]);
+            if (EPI == 2) tmem_ld8(lane_base + (uint32_t)(r * S::REGION_COLS + BN + c0), u[r]);
+          }
+        }
+        tmem_ld_wait();
+        float sg[8], su[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sg[j] = su[j] = 0.f;
+#pragma unroll
+        for (int r = 0; r < MAX_SHARES; ++r) {
+          if (r < S::MAX_WALKED && r < my_shares) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              sg[j] += __uint_as_float(g[r][j]);
+              if (EPI == 2) su[j] += __uint_as_float(u[r][j]);
             }
           }
         }
-      } else if (ok) {
-        // leave this share's partial tile in shared memory: part[column][row], float32
-        float* part = reinterpret_cast<float*>(aligned);
-#pragma unroll 1
-        for (int c0 = 0; c0 < S::REGION_COLS; c0 += 16) {
-          uint32_t g[16];
-          tmem_ld16(lane_base + c0, g);
-          tmem_ld_wait();
+        if (n < N) {
+          float old[8];
+          if (EPI == 1) {
+            // the residual rows are fetched together before any is written back
 #pragma unroll
-          for (int j = 0; j < 16; ++j) part[(c0 + j) * BM + row] = __uint_as_float(g[j]);
-        }
-      }
-    } else if constexpr (S::WALKS_SHARES) {
-      // this block walks all shares: the running sum of the partials stays in registers
-      float sum[S::REGION_COLS];
-      bool ok = true;
-      for (int r = 0; r < my_shares; ++r) {
-        const int region = r & 1;
-        bool got = mbar_wait(&acc_full[region], (uint32_t)(r >> 1) & 1u);
-        if (!got) {
-          *failed = 1;
-          if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 350 + quad);
-        }
-        ok = __all_sync(0xffffffffu, got);
-        if (!ok) break;
-        fence_after_sync();
+            for (int j = 0; j < 8; ++j)
+              old[j] = (t0 + c0 + j < T) ? ls_to_float<TC>(C[(int64_t)(t0 + c0 + j) * ldc + n]) : 0.f;
+          }
 #pragma unroll
-        for (int c0 = 0; c0 < S::REGION_COLS; c0 += 16) {
-          uint32_t g[16];
-          tmem_ld16(lane_base + (uint32_t)(region * S::REGION_COLS) + c0, g);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) sum[c0 + j] = (r == 0 ? 0.f : sum[c0 + j]) + __uint_as_float(g[j]);
-        }
-        fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[region]);
-      }
-      if (ok && n < N) {
-#pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          const int t = t0 + c;
-          if (t < T) epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, sum[c], EPI == 2 ? sum[BN + c] : 0.f);
+          for (int j = 0; j < 8; ++j) {
+            const int t = t0 + c0 + j;
+            if (t < T) {
+              TC* c = C + (int64_t)t * ldc + n;
+              if (EPI == 0) *c = ls_from_float<TC>(sg[j]);
+              else if (EPI == 1) *c = ls_from_float<TC>(old[j] + sg[j]);
+              else *c = ls_from_float<TC>(sg[j] / (1.0f + expf(-sg[j])) * su[j]);
+            }
+          }
         }
       }
     }
@@ -433,8 +417,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   if (warp == 2) {
     fence_after_sync();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(S::ACC_COLS)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(acc_cols)
                  : "memory");
   }
 }
@@ -484,7 +467,11 @@ Plan make_plan(int T, int N, int K, int epilogue) {
   p.shares = (total_kb + p.kb_per_share - 1) / p.kb_per_share;    // every share has work
   p.in_cluster = p.shares > 1 && T <= 128;
   int cap = epilogue == 2 ? 128 : 256;
-  if (p.shares > 1 && !p.in_cluster) cap = epilogue == 2 ? 64 : 128;   // running sums in registers
+  if (p.shares > 1 && !p.in_cluster) {
+    // every share gets an accumulator of its own: shares * columns <= 512
+    const int fit = 512 / (p.shares * (epilogue == 2 ? 2 : 1));
+    while (cap > fit) cap /= 2;
+  }
   p.bn = 16;
   while (p.bn < T && p.bn < cap) p.bn *= 2;
   return p;
@@ -501,7 +488,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, 
       return LS_E_SMEM;
     configured = true;
   }
-  if (plan.shares > 1 && !plan.in_cluster && !S::WALKS_SHARES) return LS_E_SIZE;
+  if (plan.shares > 1 && !plan.in_cluster && plan.shares > S::MAX_WALKED) return LS_E_SIZE;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((N + BM - 1) / BM, (T + BN - 1) / BN, plan.in_cluster ? plan.shares : 1);
   cfg.blockDim = dim3(192);
