@@ -40,39 +40,82 @@ LS_API int ls_embed_gather(const int* ids, const void* table, int table_dtype, f
 // RMSNorm over float32 rows: y = x * rsqrt(mean(x^2) + eps) * gain
 // rows may be gathered through row_index (the rows whose logits are wanted).
 // --------------------------------------------------------------------------
+// One warp per row: lane l takes the float4 groups l, l + 32, ... of the row, keeps
+// them in registers between the two passes (rows up to 8192 wide; wider rows are
+// read twice), sums its squares in that order and the lanes by an xor tree.  The
+// order depends on the width alone.
 template <typename TO, typename TG>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
-                               const TG* __restrict__ gain, TO* __restrict__ y, int width,
-                               int src_rows, float eps, int* err) {
-  __shared__ float scratch[32];
-  const int r = blockIdx.x;
+__global__ void __launch_bounds__(128)
+rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
+               const TG* __restrict__ gain, TO* __restrict__ y, int rows, int width, int src_rows,
+               float eps, int* err) {
+  constexpr int KEEP = 64;                    // floats a lane keeps: 16 float4
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
   int src = row_index ? row_index[r] : r;
   if (src < 0 || src >= src_rows) {
-    if (threadIdx.x == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, r);
+    if (lane == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, r);
     src = 0;
   }
   const float* xr = x + (int64_t)src * width;
   TO* yr = y + (int64_t)r * width;
+  const bool vec = (width & 3) == 0 && ((uintptr_t)xr & 15) == 0;
+  float keep[KEEP];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    const float v = xr[i];
-    ss = fmaf(v, v, ss);
+  if (vec) {
+    const int groups = width >> 2;
+#pragma unroll
+    for (int i = 0; i < KEEP / 4; ++i) {
+      const int g = lane + 32 * i;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (g < groups) v = *reinterpret_cast<const float4*>(xr + 4 * g);
+      keep[4 * i + 0] = v.x; keep[4 * i + 1] = v.y; keep[4 * i + 2] = v.z; keep[4 * i + 3] = v.w;
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    for (int g = lane + 32 * (KEEP / 4); g < groups; g += 32) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + 4 * g);
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+  } else {
+    for (int i = lane; i < width; i += 32) ss = fmaf(xr[i], xr[i], ss);
   }
-  const float total = ls_block_sum(ss, scratch);
-  const float rstd = 1.0f / sqrtf(total / (float)width + eps);
-  for (int i = threadIdx.x; i < width; i += blockDim.x)
-    yr[i] = ls_from_float<TO>(xr[i] * rstd * ls_to_float<TG>(gain[i]));
+  ss = ls_warp_sum(ss);
+  const float rstd = 1.0f / sqrtf(ss / (float)width + eps);
+  if (vec) {
+    const int groups = width >> 2;
+#pragma unroll
+    for (int i = 0; i < KEEP / 4; ++i) {
+      const int g = lane + 32 * i;
+      if (g < groups) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          yr[4 * g + e] = ls_from_float<TO>(keep[4 * i + e] * rstd * ls_to_float<TG>(gain[4 * g + e]));
+      }
+    }
+    for (int g = lane + 32 * (KEEP / 4); g < groups; g += 32) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + 4 * g);
+      yr[4 * g + 0] = ls_from_float<TO>(v.x * rstd * ls_to_float<TG>(gain[4 * g + 0]));
+      yr[4 * g + 1] = ls_from_float<TO>(v.y * rstd * ls_to_float<TG>(gain[4 * g + 1]));
+      yr[4 * g + 2] = ls_from_float<TO>(v.z * rstd * ls_to_float<TG>(gain[4 * g + 2]));
+      yr[4 * g + 3] = ls_from_float<TO>(v.w * rstd * ls_to_float<TG>(gain[4 * g + 3]));
+    }
+  } else {
+    for (int i = lane; i < width; i += 32)
+      yr[i] = ls_from_float<TO>(xr[i] * rstd * ls_to_float<TG>(gain[i]));
+  }
 }
 
 LS_API int ls_rmsnorm(const float* x, const int* row_index, const void* gain, int gain_dtype,
                       void* y, int y_dtype, int rows, int width, int src_rows, float eps,
                       int* err, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  // the block size depends on the width alone, so the summation order does too
-  const int threads = width >= 2048 ? 256 : 128;
-#define LS_RMS(TO, TG)                                                                        \
-  rmsnorm_kernel<TO, TG><<<rows, threads, 0, stream>>>(x, row_index, (const TG*)gain, (TO*)y, \
-                                                      width, src_rows, eps, err)
+  // few rows: one warp per block, so that the rows spread over the device
+  const int warps = rows >= 1024 ? 4 : 1;
+  const int blocks = (rows + warps - 1) / warps;
+#define LS_RMS(TO, TG)                                                                          \
+  rmsnorm_kernel<TO, TG><<<blocks, warps * 32, 0, stream>>>(x, row_index, (const TG*)gain, (TO*)y, \
+                                                            rows, width, src_rows, eps, err)
   if (y_dtype == LS_F32 && gain_dtype == LS_F32) LS_RMS(float, float);
   else if (y_dtype == LS_F32 && gain_dtype == LS_BF16) LS_RMS(float, __nv_bfloat16);
   else if (y_dtype == LS_BF16 && gain_dtype == LS_F32) LS_RMS(__nv_bfloat16, float);

@@ -422,6 +422,222 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 }
 
+// ---------------------------------------------------------------------------
+// The persistent form: a block per SM walks output tiles, and within a tile the
+// shares of K, in one stream.  Two accumulator regions in tensor memory
+// alternate share by share: while the MMA warp fills one, the epilogue warps
+// drain the other into the running sum they keep in registers
+// (((0 + p_0) + p_1) + ...), and after a tile's last share they write it out,
+// all while the next tile's products already run.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+template <int BN, int EPI, typename TC>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share, int shares,
+                    int tiles_n, int tiles_total, int* err) {
+  using S = Shape<BN, EPI>;
+  constexpr int COLS = S::REGION_COLS;           // at most 128: the running sum fits in registers
+  static_assert(COLS <= 128 && COLS % 16 == 0, "token tile too wide for register sums");
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)S::STAGES * S::STAGE_BYTES);
+  uint64_t* full = bars;                        // [STAGES]
+  uint64_t* empty = bars + S::STAGES;           // [STAGES]
+  uint64_t* acc_full = bars + 2 * S::STAGES;    // [2] a share's accumulator is complete
+  uint64_t* acc_empty = acc_full + 2;           // [2] the epilogue has drained it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* failed = tmem_slot + 1;
+  constexpr uint32_t ACC_COLS = (uint32_t)tmem_cols(2 * COLS);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int r = 0; r < 2; ++r) {
+      mbar_init(&acc_full[r], 1);
+      mbar_init(&acc_empty[r], 4);
+    }
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(ACC_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;                                 // k-blocks issued so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
+        const int n0 = (tile % tiles_n) * BM, t0 = (tile / tiles_n) * BN;
+        for (int kb = 0; kb < total_kb; ++kb, ++it) {
+          const int s = it % S::STAGES;
+          const uint32_t phase = (uint32_t)(it / S::STAGES) & 1u;
+          if (*failed || !mbar_wait(&empty[s], phase ^ 1u)) {
+            *failed = 1;
+            ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 100 + s);
+            ok = false;
+            break;
+          }
+          const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+          mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          tma_load_2d(stage, &map_w, kb * BK, n0, &full[s]);
+          if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kb * BK, N + n0, &full[s]);
+          tma_load_2d(stage + S::A_TILES * A_BYTES, &map_x, kb * BK, t0, &full[s]);
+        }
+      }
+      if (!ok) {
+        // wait (bounded) for the copies still in flight before the block exits
+        const int first = it > S::STAGES ? it - S::STAGES : 0;
+        for (int j = first; j < it; ++j) mbar_wait(&full[j % S::STAGES], (uint32_t)(j / S::STAGES) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BM, BN);
+      int it = 0, sc = 0;                         // k-blocks and shares consumed so far
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
+        for (int r = 0; r < shares && ok; ++r, ++sc) {
+          const int region = sc & 1;
+          const uint32_t acc_addr = tmem_base + (uint32_t)(region * COLS);
+          if (*failed || !mbar_wait(&acc_empty[region], ((uint32_t)(sc >> 1) & 1u) ^ 1u)) {
+            *failed = 1;
+            ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 250 + region);
+            ok = false;
+            break;
+          }
+          fence_after_sync();
+          const int kb_lo = r * kb_per_share;
+          int kb_hi = kb_lo + kb_per_share;
+          if (kb_hi > total_kb) kb_hi = total_kb;
+          for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+            const int s = it % S::STAGES;
+            const uint32_t phase = (uint32_t)(it / S::STAGES) & 1u;
+            if (*failed || !mbar_wait(&full[s], phase)) {
+              *failed = 1;
+              ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 200 + s);
+              ok = false;
+              break;
+            }
+            fence_after_sync();
+            const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t bdesc = smem_desc(stage + S::A_TILES * A_BYTES + k * UMMA_K * 2);
+              const uint32_t acc = (kb == kb_lo && k == 0) ? 0u : 1u;
+              umma(acc_addr, smem_desc(stage + k * UMMA_K * 2), bdesc, idesc, acc);
+              if (EPI == 2) umma(acc_addr + BN, smem_desc(stage + A_BYTES + k * UMMA_K * 2), bdesc, idesc, acc);
+            }
+            umma_commit(&empty[s]);
+          }
+          if (ok) umma_commit(&acc_full[region]);
+        }
+      }
+    }
+  } else {
+    // epilogue: warp w may touch tensor-memory lanes 32*(w%4) .. +32
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float sum[COLS];
+    int sc = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
+      const int n = (tile % tiles_n) * BM + row, t0 = (tile / tiles_n) * BN;
+      for (int r = 0; r < shares; ++r, ++sc) {
+        const int region = sc & 1;
+        bool got = mbar_wait(&acc_full[region], (uint32_t)(sc >> 1) & 1u);
+        if (!got) {
+          *failed = 1;
+          if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 350 + quad);
+        }
+        ok = __all_sync(0xffffffffu, got);
+        if (!ok) break;
+        fence_after_sync();
+#pragma unroll
+        for (int c0 = 0; c0 < COLS; c0 += 32) {
+          uint32_t g[32];
+          if (COLS - c0 >= 32) {
+            tmem_ld32(lane_base + (uint32_t)(region * COLS + c0), g);
+          } else {
+            tmem_ld16(lane_base + (uint32_t)(region * COLS + c0), g);
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < COLS) sum[c0 + j] = (r == 0 ? 0.f : sum[c0 + j]) + __uint_as_float(g[j]);
+        }
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[region]);
+      }
+      if (ok && n < N) {
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 8) {
+          if (t0 + c0 < T) {
+            float old[8];
+            if (EPI == 1) {
+              // the residual rows are fetched together before any is written back
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                old[j] = (t0 + c0 + j < T) ? ls_to_float<TC>(C[(int64_t)(t0 + c0 + j) * ldc + n]) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int t = t0 + c0 + j;
+              if (t < T) {
+                TC* c = C + (int64_t)t * ldc + n;
+                const float a = sum[c0 + j];
+                if (EPI == 0) *c = ls_from_float<TC>(a);
+                else if (EPI == 1) *c = ls_from_float<TC>(old[j] + a);
+                else *c = ls_from_float<TC>(a / (1.0f + expf(-a)) * sum[BN + c0 + j]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ACC_COLS)
+                 : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                 CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -466,12 +682,8 @@ Plan make_plan(int T, int N, int K, int epilogue) {
   p.kb_per_share = (total_kb + want - 1) / want;
   p.shares = (total_kb + p.kb_per_share - 1) / p.kb_per_share;    // every share has work
   p.in_cluster = p.shares > 1 && T <= 128;
-  int cap = epilogue == 2 ? 128 : 256;
-  if (p.shares > 1 && !p.in_cluster) {
-    // every share gets an accumulator of its own: shares * columns <= 512
-    const int fit = 512 / (p.shares * (epilogue == 2 ? 2 : 1));
-    while (cap > fit) cap /= 2;
-  }
+  int cap = 128;                                    // cluster: the partial tile is staged in shared memory
+  if (!p.in_cluster) cap = epilogue == 2 ? 64 : 128;   // walked: the running sum lives in registers
   p.bn = 16;
   while (p.bn < T && p.bn < cap) p.bn *= 2;
   return p;
@@ -488,9 +700,32 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, 
       return LS_E_SMEM;
     configured = true;
   }
-  if (plan.shares > 1 && !plan.in_cluster && plan.shares > S::MAX_WALKED) return LS_E_SIZE;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  if (!plan.in_cluster) {
+    if constexpr (S::REGION_COLS <= 128) {
+      static bool walk_configured = false;
+      if (!walk_configured) {
+        if (cudaFuncSetAttribute(gemm_tc_walk_kernel<BN, EPI, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)S::SMEM) != cudaSuccess)
+          return LS_E_SMEM;
+        walk_configured = true;
+      }
+      const int tiles_n = (N + BM - 1) / BM, tiles_t = (T + BN - 1) / BN;
+      const int tiles = tiles_n * tiles_t;
+      gemm_tc_walk_kernel<BN, EPI, TC><<<tiles < sms ? tiles : sms, 192, S::SMEM, stream>>>(
+          mw, mx, (TC*)C, T, N, K, ldc, plan.kb_per_share, plan.shares, tiles_n, tiles, err);
+      return ls_launch_status();
+    } else {
+      return LS_E_SIZE;
+    }
+  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((N + BM - 1) / BM, (T + BN - 1) / BN, plan.in_cluster ? plan.shares : 1);
+  cfg.gridDim = dim3((N + BM - 1) / BM, (T + BN - 1) / BN, plan.shares);
   cfg.blockDim = dim3(192);
   cfg.dynamicSmemBytes = S::SMEM;
   cfg.stream = stream;
@@ -500,9 +735,9 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, 
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = plan.shares;
   cfg.attrs = attr;
-  cfg.numAttrs = plan.in_cluster ? 1 : 0;
+  cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC>, mw, mx, (TC*)C, T, N, K, ldc,
-                                     plan.kb_per_share, plan.shares, plan.in_cluster, err);
+                                     plan.kb_per_share, plan.shares, 1, err);
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }
