@@ -92,6 +92,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
                             const int* __restrict__ work, const int* __restrict__ block_table,
                             int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
                             float scale, int* err) {
+  ls_dependency_sync();
   constexpr int D = HALVES * 64;
   constexpr int KSTEPS = D / 16;                 // k-steps of QK^T
   constexpr int DTILES = D / 8;                  // n-tiles of PV
@@ -413,7 +414,7 @@ int launch(const CUtensorMap& map, const void* q, float* part_acc, float* part_m
     configured = true;
   }
   dim3 grid(n_work, nkv);
-  attention_decode_mma_kernel<HALVES><<<grid, WARPS * 32, smem, stream>>>(
+  ls_launch(attention_decode_mma_kernel<HALVES>, grid, WARPS * 32, smem, stream, 
       map, (const __nv_bfloat16*)q, part_acc, part_ml, work, block_table, table_stride, nq, nkv, page_size,
       num_pages, window, scale, err);
   return ls_launch_status();

@@ -92,6 +92,7 @@ attention_prefill_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv
                              __nv_bfloat16* __restrict__ out, const int* __restrict__ work,
                              const int* __restrict__ block_table, int table_stride, int nq, int nkv,
                              int page_size, int num_pages, int window, float scale_log2, int* err) {
+  ls_dependency_sync();
   constexpr int D = HALVES * 64;
   constexpr int KSTEPS = D / 16;
   constexpr int DTILES = D / 8;
@@ -369,7 +370,7 @@ int launch(const CUtensorMap& map, const void* q, void* out, const int* work, in
     configured = true;
   }
   dim3 grid(n_work, nq);
-  attention_prefill_mma_kernel<HALVES><<<grid, (CONSUMERS + 1) * 32, smem, stream>>>(
+  ls_launch(attention_prefill_mma_kernel<HALVES>, grid, (CONSUMERS + 1) * 32, smem, stream, 
       map, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, work, block_table, table_stride, nq, nkv,
       page_size, num_pages, window, scale * 1.4426950408889634f, err);
   return ls_launch_status();

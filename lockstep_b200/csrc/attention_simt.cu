@@ -69,6 +69,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
                       const int* __restrict__ work, const int* __restrict__ block_table,
                       int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
                       int window, float scale, int* err) {
+  ls_dependency_sync();
   extern __shared__ float smem[];
   const int dp = d + 1;
   float* Qs = smem;                    // [TILE_M][d+1]
@@ -230,6 +231,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
                         const int* __restrict__ work, const int* __restrict__ block_table,
                         int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
                         int window, float scale, int* err) {
+  ls_dependency_sync();
   extern __shared__ __align__(16) unsigned char dsm[];
   constexpr int VEC = 16 / sizeof(T);        // elements per 16-byte chunk
   const int group = nq / nkv;
@@ -362,6 +364,7 @@ template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
                                          const float* __restrict__ part_ml, T* __restrict__ out,
                                          const int* __restrict__ items, int nq, int d) {
+  ls_dependency_sync();
   const int* it = items + (int64_t)blockIdx.x * 4;
   const int tok = it[0], first = it[1], stride = it[2], n = it[3];
   if (n == 0) return;                        // padding item of a recorded launch
@@ -435,7 +438,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
                         : cudaFuncSetAttribute(attention_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
     if (smem > set_f32) set_f32 = smem;
-    attention_tile_kernel<float><<<grid, 128, smem, stream>>>(
+    ls_launch(attention_tile_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, (float*)out, part_acc, part_ml, work, block_table,
         table_stride, nq, nkv, d, page_size, num_pages, window, scale, err);
   } else if (dtype == LS_BF16) {
@@ -443,7 +446,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
                          : cudaFuncSetAttribute(attention_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
     if (smem > set_bf16) set_bf16 = smem;
-    attention_tile_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(
+    ls_launch(attention_tile_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, part_acc,
         part_ml, work, block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale,
         err);
@@ -473,7 +476,7 @@ LS_API int ls_attention_decode(const void* q, const void* pages, float* part_acc
                         : cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
     if (smem > set_f32) set_f32 = smem;
-    attention_decode_kernel<float><<<grid, 128, smem, stream>>>(
+    ls_launch(attention_decode_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, part_acc, part_ml, work, block_table, table_stride,
         nq, nkv, d, page_size, num_pages, window, scale, err);
   } else if (dtype == LS_BF16) {
@@ -482,7 +485,7 @@ LS_API int ls_attention_decode(const void* q, const void* pages, float* part_acc
                          : cudaFuncSetAttribute(attention_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
     if (smem > set_bf16) set_bf16 = smem;
-    attention_decode_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(
+    ls_launch(attention_decode_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, part_acc, part_ml, work,
         block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, err);
   } else {
@@ -499,9 +502,9 @@ LS_API int ls_attention_combine(const float* part_acc, const float* part_ml, voi
   dim3 grid(n_items, nq);
   const int threads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
   if (dtype == LS_F32)
-    attention_combine_kernel<float><<<grid, threads, 0, stream>>>(part_acc, part_ml, (float*)out, items, nq, d);
+    ls_launch(attention_combine_kernel<float>, grid, threads, 0, stream, part_acc, part_ml, (float*)out, items, nq, d);
   else if (dtype == LS_BF16)
-    attention_combine_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(part_acc, part_ml, (__nv_bfloat16*)out, items, nq, d);
+    ls_launch(attention_combine_kernel<__nv_bfloat16>, grid, threads, 0, stream, part_acc, part_ml, (__nv_bfloat16*)out, items, nq, d);
   else
     return LS_E_DTYPE;
   return ls_launch_status();

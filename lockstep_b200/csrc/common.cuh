@@ -84,6 +84,40 @@ __device__ __forceinline__ float ls_block_sum(float v, float* scratch) {
   return total;
 }
 
+// Programmatic dependent launch: a kernel may be scheduled while its predecessor
+// in the stream still runs.  Every kernel calls ls_dependency_sync() before it
+// touches global memory: it lets the next kernel start being scheduled, then
+// waits until the previous kernel has completed and its writes are visible.
+__device__ __forceinline__ void ls_dependency_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void ls_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void ls_dependency_sync() {
+  ls_dependency_trigger();
+  ls_dependency_wait();
+}
+
+// one switch per library (set through ls_set_dependent_launch_<library>)
+inline int ls_dependent_launch = 1;
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ls_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ls_dependent_launch ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int ls_launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : (int)e;

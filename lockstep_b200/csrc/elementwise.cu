@@ -11,6 +11,7 @@
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                     float* __restrict__ out, int width, int vocab, int* err) {
+  ls_dependency_sync();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + (int64_t)t * width;
@@ -28,9 +29,9 @@ LS_API int ls_embed_gather(const int* ids, const void* table, int table_dtype, f
   if (tokens <= 0) return 0;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == LS_F32)
-    embed_gather_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, width, vocab, err);
+    ls_launch(embed_gather_kernel<float>, tokens, threads, 0, stream, ids, (const float*)table, out, width, vocab, err);
   else if (table_dtype == LS_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, width, vocab, err);
+    ls_launch(embed_gather_kernel<__nv_bfloat16>, tokens, threads, 0, stream, ids, (const __nv_bfloat16*)table, out, width, vocab, err);
   else
     return LS_E_DTYPE;
   return ls_launch_status();
@@ -49,6 +50,7 @@ __global__ void __launch_bounds__(128)
 rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
                const TG* __restrict__ gain, TO* __restrict__ y, int rows, int width, int src_rows,
                float eps, int* err) {
+  ls_dependency_sync();
   constexpr int KEEP = 64;                    // floats a lane keeps: 16 float4
   const int lane = threadIdx.x & 31;
   const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -114,7 +116,7 @@ LS_API int ls_rmsnorm(const float* x, const int* row_index, const void* gain, in
   const int warps = rows >= 1024 ? 4 : 1;
   const int blocks = (rows + warps - 1) / warps;
 #define LS_RMS(TO, TG)                                                                          \
-  rmsnorm_kernel<TO, TG><<<blocks, warps * 32, 0, stream>>>(x, row_index, (const TG*)gain, (TO*)y, \
+  ls_launch(rmsnorm_kernel<TO, TG>, blocks, warps * 32, 0, stream, x, row_index, (const TG*)gain, (TO*)y, \
                                                             rows, width, src_rows, eps, err)
   if (y_dtype == LS_F32 && gain_dtype == LS_F32) LS_RMS(float, float);
   else if (y_dtype == LS_F32 && gain_dtype == LS_BF16) LS_RMS(float, __nv_bfloat16);
@@ -143,6 +145,7 @@ __global__ void qk_norm_rope_store_kernel(
     const int* __restrict__ block_table, int table_stride, int tokens, int nq, int nkv, int d,
     int rot_dim, int page_size, int num_pages, int max_positions, float eps, int write_cache,
     int* err) {
+  ls_dependency_sync();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int head = blockIdx.y * warps_per_block + (threadIdx.x >> 5);
@@ -225,7 +228,7 @@ LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int 
   const int warps = 4;
   dim3 grid(tokens, (heads + warps - 1) / warps);
 #define LS_QK(T, TG)                                                                          \
-  qk_norm_rope_store_kernel<T, TG><<<grid, warps * 32, 0, stream>>>(                          \
+  ls_launch(qk_norm_rope_store_kernel<T, TG>, grid, warps * 32, 0, stream,                           \
       (const T*)qkv, (T*)q_out, (T*)pages, (const TG*)q_gain, (const TG*)k_gain, cos_table,   \
       sin_table, positions, token_req, block_table, table_stride, tokens, nq, nkv, d, rot_dim, \
       page_size, num_pages, max_positions, eps, write_cache, err)
@@ -245,6 +248,7 @@ LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t rows,
                                 int width) {
+  ls_dependency_sync();
   const int64_t n = rows * width;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (int64_t)gridDim.x * blockDim.x) {
@@ -262,10 +266,13 @@ LS_API int ls_silu_mul(const void* gate_up, void* out, int dtype, int rows, int 
   const int64_t n = (int64_t)rows * width;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   if (dtype == LS_F32)
-    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, rows, width);
+    ls_launch(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, rows, width);
   else if (dtype == LS_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, width);
+    ls_launch(silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, width);
   else
     return LS_E_DTYPE;
   return ls_launch_status();
 }
+
+// Switches programmatic dependent launch of this library's kernels on or off.
+LS_API void ls_set_dependent_launch_core(int on) { ls_dependent_launch = on ? 1 : 0; }

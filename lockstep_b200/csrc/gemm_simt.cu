@@ -21,6 +21,7 @@ template <typename TA, typename TW, typename TC, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_nt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C, int M,
                int N, int K, int64_t lda, int64_t ldw, int64_t ldc) {
+  ls_dependency_sync();
   __shared__ float As[BK][BM + PAD];
   __shared__ float Ws[BK][BN + PAD];
   __shared__ float Us[EPI == 2 ? BK : 1][BN + PAD];
@@ -97,13 +98,13 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t l
   if (grid.y > 65535) return LS_E_SIZE;
   switch (epilogue) {
     case 0:
-      gemm_nt_kernel<TA, TW, TC, 0><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+      ls_launch(gemm_nt_kernel<TA, TW, TC, 0>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
       break;
     case 1:
-      gemm_nt_kernel<TA, TW, TC, 1><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+      ls_launch(gemm_nt_kernel<TA, TW, TC, 1>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
       break;
     case 2:
-      gemm_nt_kernel<TA, TW, TC, 2><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+      ls_launch(gemm_nt_kernel<TA, TW, TC, 2>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
       break;
     default:
       return LS_E_SIZE;

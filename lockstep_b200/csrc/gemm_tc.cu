@@ -198,6 +198,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share, int shares,
                int in_cluster, int* err) {
   using S = Shape<BN, EPI>;
+  ls_dependency_trigger();                      // barriers and tensor memory are set up while the
+                                                // previous kernel drains; memory is touched after the wait
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -240,6 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  ls_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -455,6 +458,7 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   using S = Shape<BN, EPI>;
   constexpr int COLS = S::REGION_COLS;           // at most 128: the running sum fits in registers
   static_assert(COLS <= 128 && COLS % 16 == 0, "token tile too wide for register sums");
+  ls_dependency_trigger();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -493,6 +497,7 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  ls_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -717,7 +722,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, 
       }
       const int tiles_n = (N + BM - 1) / BM, tiles_t = (T + BN - 1) / BN;
       const int tiles = tiles_n * tiles_t;
-      gemm_tc_walk_kernel<BN, EPI, TC><<<tiles < sms ? tiles : sms, 192, S::SMEM, stream>>>(
+      ls_launch(gemm_tc_walk_kernel<BN, EPI, TC>, tiles < sms ? tiles : sms, 192, S::SMEM, stream, 
           mw, mx, (TC*)C, T, N, K, ldc, plan.kb_per_share, plan.shares, tiles_n, tiles, err);
       return ls_launch_status();
     } else {
@@ -729,13 +734,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, 
   cfg.blockDim = dim3(192);
   cfg.dynamicSmemBytes = S::SMEM;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = plan.shares;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = ls_dependent_launch ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC>, mw, mx, (TC*)C, T, N, K, ldc,
                                      plan.kb_per_share, plan.shares, 1, err);
   if (e != cudaSuccess) return (int)e;
@@ -756,6 +763,8 @@ int dispatch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int c_dtype,
 }
 
 }  // namespace
+
+LS_API void ls_set_dependent_launch_tc(int on) { ls_dependent_launch = on ? 1 : 0; }
 
 // The token tile for T tokens of a product with an (N, K) weight (it does not change any sum).
 LS_API int ls_gemm_tc_token_tile(int T, int N, int K, int epilogue) {

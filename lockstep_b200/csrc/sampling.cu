@@ -71,6 +71,7 @@ __device__ ArgMax block_argmax(const float* row, int vocab, float* sval, int* si
 }
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+  ls_dependency_sync();
   __shared__ float sval[32];
   __shared__ int sidx[32];
   const ArgMax r = block_argmax(logits + (int64_t)blockIdx.x * vocab, vocab, sval, sidx);
@@ -167,6 +168,7 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ probs,
               const float* __restrict__ temperature, const float* __restrict__ top_p,
               const uint32_t* __restrict__ keys, const uint32_t* __restrict__ positions,
               int* __restrict__ out, int vocab) {
+  ls_dependency_sync();
   __shared__ float scratch[32];
   __shared__ int sidx[32];
   __shared__ int iscratch[SAMPLE_THREADS];
@@ -213,6 +215,7 @@ constexpr int ARGMAX_CHUNKS = 64;
 
 __global__ void argmax_chunk_kernel(const float* __restrict__ logits, float* __restrict__ cval,
                                     int* __restrict__ cidx, int vocab) {
+  ls_dependency_sync();
   __shared__ float sval[32];
   __shared__ int sidx[32];
   const int r = blockIdx.x, c = blockIdx.y;
@@ -234,6 +237,7 @@ __global__ void argmax_chunk_kernel(const float* __restrict__ logits, float* __r
 
 __global__ void argmax_final_kernel(const float* __restrict__ cval, const int* __restrict__ cidx,
                                     int* __restrict__ out) {
+  ls_dependency_sync();
   const int r = blockIdx.x;
   ArgMax best{cval[r * ARGMAX_CHUNKS + threadIdx.x], cidx[r * ARGMAX_CHUNKS + threadIdx.x]};
   // 64 candidates: two per lane of one warp
@@ -256,13 +260,13 @@ LS_API int ls_argmax(const float* logits, int* out, void* scratch, int rows, int
                      cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (scratch == nullptr || vocab < 4 * ARGMAX_CHUNKS) {
-    argmax_kernel<<<rows, 512, 0, stream>>>(logits, out, vocab);
+    ls_launch(argmax_kernel, rows, 512, 0, stream, logits, out, vocab);
     return ls_launch_status();
   }
   float* cval = (float*)scratch;
   int* cidx = (int*)(cval + (size_t)rows * ARGMAX_CHUNKS);
-  argmax_chunk_kernel<<<dim3(rows, ARGMAX_CHUNKS), 256, 0, stream>>>(logits, cval, cidx, vocab);
-  argmax_final_kernel<<<rows, 32, 0, stream>>>(cval, cidx, out);
+  ls_launch(argmax_chunk_kernel, dim3(rows, ARGMAX_CHUNKS), 256, 0, stream, logits, cval, cidx, vocab);
+  ls_launch(argmax_final_kernel, rows, 32, 0, stream, cval, cidx, out);
   return ls_launch_status();
 }
 
@@ -271,7 +275,7 @@ LS_API int ls_sample(const float* logits, float* probs, const float* temperature
                      const float* top_p, const uint32_t* keys, const uint32_t* positions, int* out,
                      int rows, int vocab, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, probs, temperature, top_p, keys,
+  ls_launch(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, probs, temperature, top_p, keys,
                                                      positions, out, vocab);
   return ls_launch_status();
 }

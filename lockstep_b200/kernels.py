@@ -96,6 +96,15 @@ def library(name: str = "core") -> ctypes.CDLL:
     return lib
 
 
+def set_dependent_launch(on: bool) -> None:
+    """Programmatic dependent launch of all kernels (on by default): a kernel is
+    scheduled while its predecessor drains and waits for it before it touches memory."""
+    for name in ("core", "tc"):
+        fn = getattr(library(name), f"ls_set_dependent_launch_{name}")
+        fn.argtypes, fn.restype = [c_int], None
+        fn(1 if on else 0)
+
+
 def require_cuda() -> None:
     if not torch.cuda.is_available():
         raise KernelError(
