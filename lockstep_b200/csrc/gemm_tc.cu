@@ -62,6 +62,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -189,38 +193,70 @@ constexpr int MAX_SHARES = 8;
 // K is cut into `shares` shares of kb_per_share 64-element blocks.  An output
 // element is  ((0 + p_0) + p_1) + ... + p_{shares-1}  with p_r the float32
 // accumulation of share r in ascending k.  The shares of a tile run either in
-// the `shares` blocks of a cluster (in_cluster: few tokens, many blocks wanted)
-// or one after the other in one block, each into an accumulator of its own in
-// tensor memory, summed in the epilogue; both give the same bits.
-template <int BN, int EPI, typename TC>
+// the `shares` blocks of a cluster (this kernel: few tokens, many blocks wanted)
+// or one after the other in one persistent block (gemm_tc_walk_kernel); both
+// give the same bits.
+//
+// NORM: the token operand is not read by TMA but made here from float32 rows:
+// x[t, :] = h[row(t), :] * rsqrt(mean(h^2) + eps) * gain, rounded to bfloat16,
+// with exactly the arithmetic of rmsnorm_kernel (a warp per row, lane l sums
+// the float4 groups l, l + 32, ... in order, lanes by an xor tree), so that
+// the fused and the separate form give the same bits.  The epilogue warps do it
+// while the first weight tiles are in flight.
+constexpr int NORM_X_BYTES = 64 * 1024;        // most shared memory the normed token operand may take
+
+template <int BN, int EPI, bool NORM>
+struct ClusterShape {
+  static constexpr int A_TILES = EPI == 2 ? 2 : 1;
+  static constexpr int B_BYTES = NORM ? 0 : BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
+  static constexpr int RING = (NORM ? 136 : 200) * 1024;
+  static constexpr int STAGES_FIT = RING / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
+  static constexpr int REGION_COLS = A_TILES * BN;
+  static constexpr int X_BYTES = NORM ? NORM_X_BYTES : 0;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + X_BYTES + 1024 + 256;
+  static_assert((size_t)STAGES * STAGE_BYTES >= (size_t)REGION_COLS * BM * 4, "no room to stage the partial tile");
+};
+
+struct NormArgs {
+  const float* h;          // [src_rows, K] float32
+  const int* row_index;    // rows of h to take, or null for rows 0 .. T-1
+  const void* gain;        // [K]
+  int gain_bf16;           // element type of gain: 1 bfloat16, 0 float32
+  int src_rows;
+  float eps;
+};
+
+template <int BN, int EPI, typename TC, bool NORM>
 __global__ void __launch_bounds__(192, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share, int shares,
-               int in_cluster, int* err) {
-  using S = Shape<BN, EPI>;
-  ls_dependency_trigger();                      // barriers and tensor memory are set up while the
-                                                // previous kernel drains; memory is touched after the wait
+gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                       const NormArgs norm, TC* __restrict__ C, int T, int N, int K, int64_t ldc,
+                       int kb_per_share, int shares, int* err) {
+  using S = ClusterShape<BN, EPI, NORM>;
+  ls_dependency_trigger();                      // set-up and (NORM) the weight loads run while the previous
+                                                // kernel drains; its results are touched after the wait
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)S::STAGES * S::STAGE_BYTES);
+  const uint32_t x_base = base + (uint32_t)S::STAGES * S::STAGE_BYTES;      // NORM: [kb][BN rows][128 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)S::STAGES * S::STAGE_BYTES + S::X_BYTES);
   uint64_t* full = bars;                        // [STAGES] operands landed
   uint64_t* empty = bars + S::STAGES;           // [STAGES] MMAs have read the stage
-  uint64_t* acc_full = bars + 2 * S::STAGES;    // [1] every accumulator of this block is complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_full = bars + 2 * S::STAGES;    // [1] the accumulator is complete
+  uint64_t* x_ready = acc_full + 1;             // [1] NORM: the token operand is in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(x_ready + 1);
   volatile uint32_t* failed = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM;
   const int t0 = blockIdx.y * BN;
   const int total_kb = (K + BK - 1) / BK;
-  const int first_share = in_cluster ? (int)blockIdx.z : 0;
-  const int my_shares = in_cluster ? 1 : shares;
-  const int kb_begin = first_share * kb_per_share;
-  int kb_end = (first_share + my_shares) * kb_per_share;
+  const int kb_begin = (int)blockIdx.z * kb_per_share;          // this block's share of K
+  int kb_end = kb_begin + kb_per_share;
   if (kb_end > total_kb) kb_end = total_kb;
   const int num_kb = kb_end - kb_begin;
-  const uint32_t acc_cols = (uint32_t)tmem_cols(my_shares * S::REGION_COLS);
+  constexpr uint32_t ACC_COLS = (uint32_t)tmem_cols(S::REGION_COLS);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
@@ -228,13 +264,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(&empty[s], 1);
     }
     mbar_init(acc_full, 1);
+    mbar_init(x_ready, 4);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    if (!NORM) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
   }
   if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"(acc_cols)
+                 "r"(ACC_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -242,10 +281,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  ls_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {
+      // the weights do not depend on the previous kernel; the token operand read by TMA does
+      if (!NORM) ls_dependency_wait();
       int issued = 0;
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % S::STAGES;
@@ -260,7 +300,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int kx = (kb_begin + kb) * BK;
         tma_load_2d(stage, &map_w, kx, n0, &full[s]);
         if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kx, N + n0, &full[s]);
-        tma_load_2d(stage + S::A_TILES * A_BYTES, &map_x, kx, t0, &full[s]);
+        if (!NORM) tma_load_2d(stage + S::A_TILES * A_BYTES, &map_x, kx, t0, &full[s]);
         issued = kb + 1;
       }
       if (*failed) {
@@ -274,42 +314,97 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BM, BN);
       bool ok = true;
-      int kb = 0;
-      for (int r = 0; r < my_shares && ok; ++r) {
-        const uint32_t acc_addr = tmem_base + (uint32_t)(r * S::REGION_COLS);
-        int share_end = (r + 1) * kb_per_share;
-        if (share_end > num_kb) share_end = num_kb;
-        for (bool first = true; kb < share_end; ++kb) {
-          const int s = kb % S::STAGES;
-          const uint32_t phase = (uint32_t)(kb / S::STAGES) & 1u;
-          if (*failed || !mbar_wait(&full[s], phase)) {
-            *failed = 1;
-            ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 200 + s);
-            ok = false;
-            break;
-          }
-          fence_after_sync();
-          const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t bdesc = smem_desc(stage + S::A_TILES * A_BYTES + k * UMMA_K * 2);
-            const uint32_t acc = (first && k == 0) ? 0u : 1u;
-            umma(acc_addr, smem_desc(stage + k * UMMA_K * 2), bdesc, idesc, acc);
-            if (EPI == 2) umma(acc_addr + BN, smem_desc(stage + A_BYTES + k * UMMA_K * 2), bdesc, idesc, acc);
-          }
-          first = false;
-          umma_commit(&empty[s]);
+      if (NORM && !mbar_wait(x_ready, 0)) {
+        *failed = 1;
+        ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 260);
+        ok = false;
+      }
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % S::STAGES;
+        const uint32_t phase = (uint32_t)(kb / S::STAGES) & 1u;
+        if (*failed || !mbar_wait(&full[s], phase)) {
+          *failed = 1;
+          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 200 + s);
+          ok = false;
+          break;
         }
+        fence_after_sync();
+        const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+        const uint32_t xs = NORM ? x_base + (uint32_t)(kb * BN * 128) : stage + S::A_TILES * A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint64_t bdesc = smem_desc(xs + k * UMMA_K * 2);
+          const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
+          umma(tmem_base, smem_desc(stage + k * UMMA_K * 2), bdesc, idesc, acc);
+          if (EPI == 2) umma(tmem_base + BN, smem_desc(stage + A_BYTES + k * UMMA_K * 2), bdesc, idesc, acc);
+        }
+        umma_commit(&empty[s]);
       }
       if (ok) umma_commit(acc_full);
     }
   } else {
-    // epilogue: warp w may touch tensor-memory lanes 32*(w%4) .. +32
+    // epilogue warps: warp w may touch tensor-memory lanes 32*(w%4) .. +32
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
-    const int n = n0 + row;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
-
+    ls_dependency_wait();
+    if (NORM) {
+      typedef __nv_bfloat16 bf16;
+      const int k_lo = kb_begin * BK;
+      const int k_hi = kb_end * BK < K ? kb_end * BK : K;
+      const int groups = K >> 2;
+      for (int t = warp - 2; t < BN; t += 4) {
+        uint8_t* xrow = aligned + (x_base - base) + t * 128;       // row t of k-block 0
+        if (t0 + t < T) {
+          int src = norm.row_index ? norm.row_index[t0 + t] : t0 + t;
+          if (src < 0 || src >= norm.src_rows) {
+            if (lane == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, t0 + t);
+            src = 0;
+          }
+          const float* xr = norm.h + (int64_t)src * K;
+          float ss = 0.f;
+          for (int g = lane; g < groups; g += 32) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + 4 * g);
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+          }
+          ss = ls_warp_sum(ss);
+          const float rstd = 1.0f / sqrtf(ss / (float)K + norm.eps);
+          for (int g = (k_lo >> 2) + lane; g < (k_hi >> 2); g += 32) {
+            const float4 v = *reinterpret_cast<const float4*>(xr + 4 * g);
+            float gn[4];
+            if (norm.gain_bf16) {
+              const bf16* gp = reinterpret_cast<const bf16*>(norm.gain) + 4 * g;
+              gn[0] = __bfloat162float(gp[0]); gn[1] = __bfloat162float(gp[1]);
+              gn[2] = __bfloat162float(gp[2]); gn[3] = __bfloat162float(gp[3]);
+            } else {
+              const float4 gv = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(norm.gain) + 4 * g);
+              gn[0] = gv.x; gn[1] = gv.y; gn[2] = gv.z; gn[3] = gv.w;
+            }
+            const int k = 4 * g - k_lo;                         // column within the share
+            const int kb = k >> 6, kk = k & 63;
+            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * rstd * gn[0], v.y * rstd * gn[1]);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * rstd * gn[2], v.w * rstd * gn[3]);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(xrow + kb * (BN * 128) + (((kk >> 3) ^ (t & 7)) << 4) + (kk & 7) * 2) = packed;
+          }
+          // columns of the last k-block past K
+          for (int k = k_hi - k_lo + 4 * lane; k < num_kb * BK; k += 128) {
+            const int kb = k >> 6, kk = k & 63;
+            *reinterpret_cast<uint2*>(xrow + kb * (BN * 128) + (((kk >> 3) ^ (t & 7)) << 4) + (kk & 7) * 2) = make_uint2(0u, 0u);
+          }
+        } else {
+          for (int k = 4 * lane; k < num_kb * BK; k += 128) {
+            const int kb = k >> 6, kk = k & 63;
+            *reinterpret_cast<uint2*>(xrow + kb * (BN * 128) + (((kk >> 3) ^ (t & 7)) << 4) + (kk & 7) * 2) = make_uint2(0u, 0u);
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x_ready);
+    }
     bool ok = mbar_wait(acc_full, 0);
     if (!ok) {
       *failed = 1;
@@ -317,7 +412,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     ok = __all_sync(0xffffffffu, ok);
     fence_after_sync();
-    if (ok && in_cluster) {
+    if (ok) {
       // leave this share's partial tile in shared memory: part[column][row], float32
       float* part = reinterpret_cast<float*>(aligned);
 #pragma unroll 1
@@ -328,99 +423,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 16; ++j) part[(c0 + j) * BM + row] = __uint_as_float(g[j]);
       }
-    } else if (ok) {
-      // sum the shares' accumulators in ascending order, eight columns at a time
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 8) {
-        if (t0 + c0 >= T) break;          // uniform across the warp
-        uint32_t g[S::MAX_WALKED < MAX_SHARES ? S::MAX_WALKED : MAX_SHARES][8];
-        uint32_t u[EPI == 2 ? (S::MAX_WALKED < MAX_SHARES ? S::MAX_WALKED : MAX_SHARES) : 1][8];
-#pragma unroll
-        for (int r = 0; r < MAX_SHARES; ++r) {
-          if (r < S::MAX_WALKED && r < my_shares) {
-            tmem_ld8(lane_base + (uint32_t)(r * S::REGION_COLS + c0), g[r]);
-            if (EPI == 2) tmem_ld8(lane_base + (uint32_t)(r * S::REGION_COLS + BN + c0), u[r]);
-          }
-        }
-        tmem_ld_wait();
-        float sg[8], su[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) sg[j] = su[j] = 0.f;
-#pragma unroll
-        for (int r = 0; r < MAX_SHARES; ++r) {
-          if (r < S::MAX_WALKED && r < my_shares) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              sg[j] += __uint_as_float(g[r][j]);
-              if (EPI == 2) su[j] += __uint_as_float(u[r][j]);
-            }
-          }
-        }
-        if (n < N) {
-          float old[8];
-          if (EPI == 1) {
-            // the residual rows are fetched together before any is written back
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              old[j] = (t0 + c0 + j < T) ? ls_to_float<TC>(C[(int64_t)(t0 + c0 + j) * ldc + n]) : 0.f;
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int t = t0 + c0 + j;
-            if (t < T) {
-              TC* c = C + (int64_t)t * ldc + n;
-              if (EPI == 0) *c = ls_from_float<TC>(sg[j]);
-              else if (EPI == 1) *c = ls_from_float<TC>(old[j] + sg[j]);
-              else *c = ls_from_float<TC>(sg[j] / (1.0f + expf(-sg[j])) * su[j]);
-            }
-          }
-        }
-      }
     }
   }
-  if (in_cluster) {
-    // all shares have left their partials; each block folds the columns c with
-    // c % shares == its rank, reading every share in ascending order
-    __syncwarp();
-    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    if (warp >= 2 && !*failed) {
-      const int quad = warp & 3;
-      const int row = quad * 32 + lane;
-      const int n = n0 + row;
-      uint32_t peer[MAX_SHARES];
+  // all shares have left their partials; each block folds the columns c with
+  // c % shares == its rank, reading every share in ascending order
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (warp >= 2 && !*failed) {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int n = n0 + row;
+    uint32_t peer[MAX_SHARES];
 #pragma unroll
-      for (int r = 0; r < MAX_SHARES; ++r)
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[r]) : "r"(base), "r"(r < shares ? r : 0));
-      for (int c = (int)blockIdx.z; c < BN; c += shares) {
-        const int t = t0 + c;
-        if (t >= T) break;
-        const uint32_t off_g = (uint32_t)((c * BM + row) * 4), off_u = (uint32_t)(((BN + c) * BM + row) * 4);
-        float vg[MAX_SHARES], vu[MAX_SHARES];
+    for (int r = 0; r < MAX_SHARES; ++r)
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[r]) : "r"(base), "r"(r < shares ? r : 0));
+    for (int c = (int)blockIdx.z; c < BN; c += shares) {
+      const int t = t0 + c;
+      if (t >= T) break;
+      const uint32_t off_g = (uint32_t)((c * BM + row) * 4), off_u = (uint32_t)(((BN + c) * BM + row) * 4);
+      float vg[MAX_SHARES], vu[MAX_SHARES];
 #pragma unroll
-        for (int r = 0; r < MAX_SHARES; ++r) {
-          vg[r] = r < shares ? ld_cluster_f32(peer[r] + off_g) : 0.f;
-          if (EPI == 2) vu[r] = r < shares ? ld_cluster_f32(peer[r] + off_u) : 0.f;
-        }
-        float g = 0.f, u = 0.f;
-#pragma unroll
-        for (int r = 0; r < MAX_SHARES; ++r) {
-          if (r < shares) {
-            g += vg[r];
-            if (EPI == 2) u += vu[r];
-          }
-        }
-        if (n < N) epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, g, u);
+      for (int r = 0; r < MAX_SHARES; ++r) {
+        vg[r] = r < shares ? ld_cluster_f32(peer[r] + off_g) : 0.f;
+        if (EPI == 2) vu[r] = r < shares ? ld_cluster_f32(peer[r] + off_u) : 0.f;
       }
+      float g = 0.f, u = 0.f;
+#pragma unroll
+      for (int r = 0; r < MAX_SHARES; ++r) {
+        if (r < shares) {
+          g += vg[r];
+          if (EPI == 2) u += vu[r];
+        }
+      }
+      if (n < N) epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, g, u);
     }
-    // no block may leave while a peer still reads its partial
-    __syncwarp();
-    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
+  // no block may leave while a peer still reads its partial
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
   fence_before_sync();
   __syncthreads();
   if (warp == 2) {
     fence_after_sync();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(acc_cols)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ACC_COLS)
                  : "memory");
   }
 }
@@ -433,10 +478,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // (((0 + p_0) + p_1) + ...), and after a tile's last share they write it out,
 // all while the next tile's products already run.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -694,40 +735,26 @@ Plan make_plan(int T, int N, int K, int epilogue) {
   return p;
 }
 
-template <int BN, int EPI, typename TC>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int64_t ldc,
-           const Plan& plan, int* err, cudaStream_t stream) {
-  using S = Shape<BN, EPI>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)S::SMEM) != cudaSuccess)
-      return LS_E_SMEM;
-    configured = true;
-  }
+int sm_count() {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   }
-  if (!plan.in_cluster) {
-    if constexpr (S::REGION_COLS <= 128) {
-      static bool walk_configured = false;
-      if (!walk_configured) {
-        if (cudaFuncSetAttribute(gemm_tc_walk_kernel<BN, EPI, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)S::SMEM) != cudaSuccess)
-          return LS_E_SMEM;
-        walk_configured = true;
-      }
-      const int tiles_n = (N + BM - 1) / BM, tiles_t = (T + BN - 1) / BN;
-      const int tiles = tiles_n * tiles_t;
-      ls_launch(gemm_tc_walk_kernel<BN, EPI, TC>, tiles < sms ? tiles : sms, 192, S::SMEM, stream, 
-          mw, mx, (TC*)C, T, N, K, ldc, plan.kb_per_share, plan.shares, tiles_n, tiles, err);
-      return ls_launch_status();
-    } else {
-      return LS_E_SIZE;
-    }
+  return sms;
+}
+
+template <int BN, int EPI, typename TC, bool NORM>
+int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs& norm, void* C, int T, int N,
+                   int K, int64_t ldc, const Plan& plan, int* err, cudaStream_t stream) {
+  using S = ClusterShape<BN, EPI, NORM>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_cluster_kernel<BN, EPI, TC, NORM>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM) != cudaSuccess)
+      return LS_E_SMEM;
+    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((N + BM - 1) / BM, (T + BN - 1) / BN, plan.shares);
@@ -743,23 +770,92 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ls_dependent_launch ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI, TC>, mw, mx, (TC*)C, T, N, K, ldc,
-                                     plan.kb_per_share, plan.shares, 1, err);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<BN, EPI, TC, NORM>, mw, mx, norm, (TC*)C, T,
+                                     N, K, ldc, plan.kb_per_share, plan.shares, err);
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }
 
+template <int BN, int EPI, typename TC>
+int launch_walk(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int64_t ldc,
+                const Plan& plan, int* err, cudaStream_t stream) {
+  using S = Shape<BN, EPI>;
+  if constexpr (S::REGION_COLS <= 128) {
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(gemm_tc_walk_kernel<BN, EPI, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)S::SMEM) != cudaSuccess)
+        return LS_E_SMEM;
+      configured = true;
+    }
+    const int tiles_n = (N + BM - 1) / BM, tiles_t = (T + BN - 1) / BN;
+    const int tiles = tiles_n * tiles_t;
+    const int sms = sm_count();
+    ls_launch(gemm_tc_walk_kernel<BN, EPI, TC>, tiles < sms ? tiles : sms, 192, S::SMEM, stream, mw, mx,
+              (TC*)C, T, N, K, ldc, plan.kb_per_share, plan.shares, tiles_n, tiles, err);
+    return ls_launch_status();
+  } else {
+    return LS_E_SIZE;
+  }
+}
+
+// norm == nullptr: the token operand is read through `mx`
+template <int BN, int EPI, typename TC>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs* norm, void* C, int T, int N, int K,
+           int64_t ldc, const Plan& plan, int* err, cudaStream_t stream) {
+  if (!plan.in_cluster) return launch_walk<BN, EPI, TC>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+  if constexpr (BN <= 128) {
+    if (norm != nullptr) return launch_cluster<BN, EPI, TC, true>(mw, mx, *norm, C, T, N, K, ldc, plan, err, stream);
+    NormArgs none = {};
+    return launch_cluster<BN, EPI, TC, false>(mw, mx, none, C, T, N, K, ldc, plan, err, stream);
+  } else {
+    return LS_E_SIZE;
+  }
+}
+
 template <int BN>
-int dispatch(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int c_dtype, int T, int N, int K,
-             int64_t ldc, int epilogue, const Plan& plan, int* err, cudaStream_t stream) {
+int dispatch(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs* norm, void* C, int c_dtype, int T,
+             int N, int K, int64_t ldc, int epilogue, const Plan& plan, int* err, cudaStream_t stream) {
   typedef __nv_bfloat16 bf16;
-  if (epilogue == 0 && c_dtype == LS_BF16) return launch<BN, 0, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream);
-  if (epilogue == 0 && c_dtype == LS_F32) return launch<BN, 0, float>(mw, mx, C, T, N, K, ldc, plan, err, stream);
-  if (epilogue == 1 && c_dtype == LS_F32) return launch<BN, 1, float>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+  if (epilogue == 0 && c_dtype == LS_BF16) return launch<BN, 0, bf16>(mw, mx, norm, C, T, N, K, ldc, plan, err, stream);
+  if (epilogue == 0 && c_dtype == LS_F32) return launch<BN, 0, float>(mw, mx, norm, C, T, N, K, ldc, plan, err, stream);
+  if (epilogue == 1 && c_dtype == LS_F32) return launch<BN, 1, float>(mw, mx, norm, C, T, N, K, ldc, plan, err, stream);
   if (epilogue == 2 && c_dtype == LS_BF16) {
-    if constexpr (BN <= 128) return launch<BN, 2, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+    if constexpr (BN <= 128) return launch<BN, 2, bf16>(mw, mx, norm, C, T, N, K, ldc, plan, err, stream);
   }
   return LS_E_DTYPE;
+}
+
+int run(const void* X, const NormArgs* norm, const void* W, void* C, int c_dtype, int T, int N, int K,
+        int64_t ldx, int64_t ldw, int64_t ldc, int epilogue, int* err, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (K <= 0 || epilogue < 0 || epilogue > 2) return LS_E_SIZE;
+  if ((K % 8) || (ldw % 8)) return LS_E_ALIGN;     // 16-byte row pitch
+  if ((uintptr_t)W & 15) return LS_E_ALIGN;
+  if ((N + BM - 1) / BM > 2147483647 / 2 || (T + 15) / 16 > 65535) return LS_E_SIZE;
+  const Plan plan = make_plan(T, N, K, epilogue);
+  const int bn = plan.bn;
+  const int w_rows = epilogue == 2 ? 2 * N : N;
+  CUtensorMap mw, mx;
+  if (!make_map(&mw, W, w_rows, K, ldw, BM)) return LS_E_SIZE;
+  if (norm == nullptr) {
+    if ((ldx % 8) || ((uintptr_t)X & 15)) return LS_E_ALIGN;
+    if (!make_map(&mx, X, T, K, ldx, bn)) return LS_E_SIZE;
+  } else {
+    // the fused form serves the cluster kernel only, up to 32 tokens (every block of the
+    // cluster norms all rows again, which pays only while they are few), and only while
+    // the normed rows of one share fit their shared-memory budget
+    if (!plan.in_cluster || bn > 32 || plan.kb_per_share * bn * 128 > NORM_X_BYTES) return LS_E_SIZE;
+    if ((K % 4) || ((uintptr_t)norm->h & 15) || ((uintptr_t)norm->gain & 15)) return LS_E_ALIGN;
+    mx = mw;
+  }
+  switch (bn) {
+    case 16: return dispatch<16>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 32: return dispatch<32>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 64: return dispatch<64>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 128: return dispatch<128>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+  }
+  return LS_E_SIZE;
 }
 
 }  // namespace
@@ -777,23 +873,25 @@ LS_API int ls_gemm_tc_token_tile(int T, int N, int K, int epilogue) {
 LS_API int ls_gemm_nt_tc(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
                          int64_t ldx, int64_t ldw, int64_t ldc, int epilogue, int* err,
                          cudaStream_t stream) {
-  if (T <= 0 || N <= 0) return 0;
-  if (K <= 0 || epilogue < 0 || epilogue > 2) return LS_E_SIZE;
-  if ((K % 8) || (ldx % 8) || (ldw % 8)) return LS_E_ALIGN;     // 16-byte row pitch
-  if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return LS_E_ALIGN;
-  if ((N + BM - 1) / BM > 2147483647 / 2 || (T + 15) / 16 > 65535) return LS_E_SIZE;
-  const Plan plan = make_plan(T, N, K, epilogue);
-  const int bn = plan.bn;
-  const int w_rows = epilogue == 2 ? 2 * N : N;
-  CUtensorMap mw, mx;
-  if (!make_map(&mw, W, w_rows, K, ldw, BM)) return LS_E_SIZE;
-  if (!make_map(&mx, X, T, K, ldx, bn)) return LS_E_SIZE;
-  switch (bn) {
-    case 16: return dispatch<16>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
-    case 32: return dispatch<32>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
-    case 64: return dispatch<64>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
-    case 128: return dispatch<128>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
-    case 256: return dispatch<256>(mw, mx, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
-  }
-  return LS_E_SIZE;
+  return run(X, nullptr, W, C, c_dtype, T, N, K, ldx, ldw, ldc, epilogue, err, stream);
+}
+
+// The same product with the token operand made in the kernel:
+// X[t, :] = rmsnorm(h[row_index ? row_index[t] : t, :]) with `gain` and `eps`, bit for bit
+// what ls_rmsnorm writes.  h [src_rows, K] float32.  Serves few tokens (the cluster form);
+// returns LS_E_SIZE or LS_E_ALIGN, having launched nothing, where it does not apply, and
+// the caller then runs ls_rmsnorm and ls_gemm_nt_tc.
+LS_API int ls_gemm_nt_tc_rmsnorm(const float* h, const int* row_index, int src_rows, const void* gain,
+                                 int gain_dtype, float eps, const void* W, void* C, int c_dtype, int T,
+                                 int N, int K, int64_t ldw, int64_t ldc, int epilogue, int* err,
+                                 cudaStream_t stream) {
+  if (gain_dtype != LS_F32 && gain_dtype != LS_BF16) return LS_E_DTYPE;
+  NormArgs norm;
+  norm.h = h;
+  norm.row_index = row_index;
+  norm.gain = gain;
+  norm.gain_bf16 = gain_dtype == LS_BF16 ? 1 : 0;
+  norm.src_rows = src_rows;
+  norm.eps = eps;
+  return run(nullptr, &norm, W, C, c_dtype, T, N, K, 0, ldw, ldc, epilogue, err, stream);
 }

@@ -14,6 +14,8 @@ Only models whose parts are all ``graph_safe`` are recorded.
 
 from __future__ import annotations
 
+import gc
+
 import numpy as np
 import torch
 
@@ -121,8 +123,17 @@ class DecodeGraphs:
         from .. import kernels as K
 
         before = K.LAUNCHES[0]
-        with torch.cuda.graph(graph, pool=self.pool):
-            logits = r.forward(ctx)
+        # No object may be collected while the stream is capturing: the destructor of
+        # another runner's graph calls into CUDA and would invalidate the capture.
+        collecting = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, pool=self.pool):
+                logits = r.forward(ctx)
+        finally:
+            if collecting:
+                gc.enable()
         recorded = K.LAUNCHES[0] - before
         K.LAUNCHES[0] = before               # recording launches nothing
         self.graphs[key] = (graph, ctx, logits, recorded)

@@ -76,6 +76,8 @@ _SIGNATURES["tc"] = {
     "ls_attention_prefill_tile_tokens": [],
     "ls_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    "ls_gemm_nt_tc_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
+                              c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p],
     "ls_gemm_nt_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                       c_int, c_void_p, c_void_p],
 }
@@ -356,6 +358,31 @@ def gemm_nt_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int,
     if status == -3:
         return False
     _check(status, "gemm_nt_tc")
+    return True
+
+
+def gemm_nt_tc_rmsnorm(h: torch.Tensor, gain: torch.Tensor, eps: float, w: torch.Tensor, c: torch.Tensor,
+                       epilogue: int, err: torch.Tensor, row_index: torch.Tensor | None = None) -> bool:
+    """c = rmsnorm(h)[rows] @ w.T with the norm made inside the product's kernel, bit for bit
+    what ``rmsnorm`` followed by ``gemm_nt_tc`` gives.  h [rows, k] float32, w bfloat16.
+    Returns False, having launched nothing, where the fused form does not apply (many
+    tokens, a weight whose depth is not shared out, unaligned rows)."""
+    if not USE_TENSOR_CORES[0] or w.dtype != torch.bfloat16:
+        return False
+    k = h.shape[1]
+    m, n = c.shape
+    rows_w = 2 * n if epilogue == EPILOGUE_SILU_MUL else n
+    if w.shape != (rows_w, k) or gain.numel() != k:
+        raise KernelError("gemm_nt_tc_rmsnorm: shapes do not agree")
+    if row_index is None and h.shape[0] != m:
+        raise KernelError("gemm_nt_tc_rmsnorm: row counts do not agree")
+    status = library("tc").ls_gemm_nt_tc_rmsnorm(
+        _dev(h, "h", torch.float32), _opt(row_index, "row_index", torch.int32), h.shape[0],
+        _dev(gain, "gain"), _code(gain), float(eps), _dev(w, "w"), _dev(c, "c"), _code(c), m, n, k, k, n,
+        epilogue, _dev(err, "err", torch.int32), _stream())
+    if status in (-2, -3):
+        return False
+    _check(status, "gemm_nt_tc_rmsnorm")
     return True
 
 

@@ -14,10 +14,12 @@ import torch
 
 from .. import kernels as K
 from .base import CacheNeed, Mixer, PositionEncoding, Runtime, WeightSpec, register_part
+from .norm import NormedRows
 
 
 class GQAttention(Mixer):
     graph_safe = True
+    accepts_normed_rows = True
 
     def __init__(self, hidden_size, num_heads, num_kv_heads, head_dim, scale, window, qk_norm_eps,
                  position: PositionEncoding, runtime: Runtime):
@@ -61,11 +63,14 @@ class GQAttention(Mixer):
             self.q_gain, self.k_gain = tensors["q_norm.weight"], tensors["k_norm.weight"]
 
     def forward(self, x, ctx, cache, residual):
-        t = x.shape[0]
         nq, nkv, d = self.nq, self.nkv, self.d
-        dev, dt = x.device, x.dtype
+        dev, dt = residual.device, self.rt.dtype
+        t = residual.shape[0]
         qkv = torch.empty((t, (nq + 2 * nkv) * d), dtype=dt, device=dev)
-        K.gemm_nt(x, self.w_qkv, qkv, err=self.rt.err)
+        if isinstance(x, NormedRows):
+            x.linear(self.w_qkv, qkv, K.EPILOGUE_STORE, self.rt.err)
+        else:
+            K.gemm_nt(x, self.w_qkv, qkv, err=self.rt.err)
         q = torch.empty((t, nq * d), dtype=dt, device=dev)
         rot = self.position.rotary()
         cos, sin, rot_dim = rot if rot is not None else (None, None, 0)

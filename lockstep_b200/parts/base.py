@@ -74,6 +74,11 @@ class Part:
     # context (``ctx.portions``) in ``forward`` must leave it False.
     graph_safe = False
 
+    # True for a mixer or feed-forward whose ``forward`` takes ``x`` either as a tensor or
+    # as a ``norm.NormedRows`` (rows still to be normalised), so that it can make the norm
+    # inside its first product.  Parts that leave it False always get a tensor.
+    accepts_normed_rows = False
+
     def attention_windows(self) -> set[int]:
         """Window sizes for which this part asks ``ctx.attention_plan``."""
         return set()

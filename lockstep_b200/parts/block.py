@@ -52,9 +52,16 @@ class PreNormBlock(Block):
             if own or part.weight_specs():
                 part.bind(own)
 
+    @staticmethod
+    def _normed(norm, consumer, h):
+        """Rows for ``consumer``: still to be normalised where it can fuse the norm, else the tensor."""
+        if consumer.accepts_normed_rows and hasattr(norm, "lazy"):
+            return norm.lazy(h)
+        return norm.forward(h)
+
     def forward(self, h, ctx, cache):
-        self.mixer.forward(self.mixer_norm.forward(h), ctx, cache, h)
-        self.feed_forward.forward(self.feed_forward_norm.forward(h), ctx, h)
+        self.mixer.forward(self._normed(self.mixer_norm, self.mixer, h), ctx, cache, h)
+        self.feed_forward.forward(self._normed(self.feed_forward_norm, self.feed_forward, h), ctx, h)
 
 
 @register_part("block", "pre_norm")

@@ -9,10 +9,12 @@ import torch
 
 from .. import kernels as K
 from .base import FeedForward, Runtime, WeightSpec, register_part
+from .norm import NormedRows
 
 
 class SwiGLU(FeedForward):
     graph_safe = True
+    accepts_normed_rows = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, runtime: Runtime):
         self.h, self.i, self.rt = int(hidden_size), int(intermediate_size), runtime
@@ -30,8 +32,11 @@ class SwiGLU(FeedForward):
         self.w_down = tensors["down_proj.weight"]
 
     def forward(self, x, ctx, residual):
-        act = torch.empty((x.shape[0], self.i), dtype=x.dtype, device=x.device)
-        K.gemm_nt(x, self.w_gate_up, act, K.EPILOGUE_SILU_MUL, err=self.rt.err)
+        act = torch.empty((residual.shape[0], self.i), dtype=self.rt.dtype, device=residual.device)
+        if isinstance(x, NormedRows):
+            x.linear(self.w_gate_up, act, K.EPILOGUE_SILU_MUL, self.rt.err)
+        else:
+            K.gemm_nt(x, self.w_gate_up, act, K.EPILOGUE_SILU_MUL, err=self.rt.err)
         K.gemm_nt(act, self.w_down, residual, K.EPILOGUE_RESIDUAL, err=self.rt.err)
 
 

@@ -103,3 +103,45 @@ def test_unaligned_depth_falls_back_to_the_cuda_cores():
     assert not K.gemm_nt_tc(x, w, c, K.EPILOGUE_STORE, err)
     K.gemm_nt(x, w, c, err=err)
     assert (c.cpu().double() - x.cpu().double() @ w.cpu().double().T).abs().max() < 1e-4
+
+
+@pytest.mark.parametrize("gain_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("t,n,k", [(1, 4096, 1024), (8, 1024, 2048), (16, 384, 1024), (27, 640, 1536), (32, 256, 1024)])
+def test_norm_made_inside_the_product_gives_the_same_bits(t, n, k, gain_dtype):
+    """rmsnorm then product, against the product that makes the norm itself, for all epilogues."""
+    from lockstep_b200 import kernels as K
+
+    g = torch.Generator().manual_seed(t + n)
+    h = (torch.randn(t + 3, k, generator=g) * 2).to(dev())
+    gain = (1 + 0.1 * torch.randn(k, generator=g)).to(gain_dtype).to(dev())
+    w = (torch.randn(2 * n, k, generator=g) * 0.1).to(torch.bfloat16).to(dev())
+    rows = torch.randperm(t + 3, generator=g)[:t].to(torch.int32).to(dev())
+    err = K.new_error_word(dev())
+    for row_index in (None, rows):
+        hh = h[:t].contiguous() if row_index is None else h
+        x = torch.empty(t, k, dtype=torch.bfloat16, device=dev())
+        K.rmsnorm(hh, gain, x, 1e-6, err, row_index)
+        for epilogue, wt, dtype in [(K.EPILOGUE_STORE, w[:n].contiguous(), torch.bfloat16),
+                                    (K.EPILOGUE_STORE, w[:n].contiguous(), torch.float32),
+                                    (K.EPILOGUE_RESIDUAL, w[:n].contiguous(), torch.float32),
+                                    (K.EPILOGUE_SILU_MUL, w, torch.bfloat16)]:
+            base = torch.randn(t, n, generator=g).to(dtype).to(dev())
+            want, got = base.clone(), base.clone()
+            assert K.gemm_nt_tc(x, wt, want, epilogue, err)
+            assert K.gemm_nt_tc_rmsnorm(hh, gain, 1e-6, wt, got, epilogue, err, row_index), (t, n, k, epilogue)
+            assert torch.equal(want, got), (epilogue, dtype, row_index is not None)
+    K.raise_on_fault(err)
+
+
+def test_norm_fusion_declines_where_it_does_not_apply():
+    from lockstep_b200 import kernels as K
+
+    err = K.new_error_word(dev())
+    h = torch.randn(300, 1024, device=dev())
+    gain = torch.ones(1024, dtype=torch.bfloat16, device=dev())
+    w = torch.randn(256, 1024, device=dev()).to(torch.bfloat16)
+    c = torch.empty(300, 256, dtype=torch.bfloat16, device=dev())
+    assert not K.gemm_nt_tc_rmsnorm(h, gain, 1e-6, w, c, K.EPILOGUE_STORE, err)          # many tokens
+    wide = torch.randn(151936 // 8, 1024, device=dev()).to(torch.bfloat16)
+    c2 = torch.empty(4, wide.shape[0], dtype=torch.float32, device=dev())
+    assert not K.gemm_nt_tc_rmsnorm(h[:4].contiguous(), gain, 1e-6, wide, c2, K.EPILOGUE_STORE, err)  # one share
