@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import torch
 
+from .. import kernels as K
 from ..sampling import Sampler
 from .batch import StepEntry
 from .policy import Policy
@@ -41,10 +42,13 @@ class Engine:
 
     # backend interface of the scheduler
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
-        return self.runner.step(entries)
+        # the device error word is read after sampling, in one wait for the whole step
+        return self.runner.step(entries, check=False, static_logits=True)
 
     def sample(self, logits, params) -> list[int]:
-        return self.sampler.sample(logits, params)
+        tokens = self.sampler.sample(logits, params)
+        K.raise_on_fault(self.runner.err)
+        return tokens
 
     # -- generation -------------------------------------------------------------
     def submit(self, request: Request) -> None:

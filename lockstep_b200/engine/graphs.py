@@ -48,6 +48,7 @@ class StaticStepContext:
                 combine_items=self.dev[off + capacity * 8:off + per_window].view(batch, 4),
                 n_combine=batch, n_slots=capacity)
             off += per_window
+        self._arange = np.arange(batch, dtype=np.int32)
         self.portions: list = []
         self.entries: list = []
         self.slots: list = []
@@ -67,18 +68,40 @@ class StaticStepContext:
             self.copied.synchronize()      # the last copy has read the pinned buffer
         b, h = self.batch, self.host_np
         self.entries, self.slots = entries, slots
-        self.portions = [(slot, i, e.start, 1) for i, (e, slot) in enumerate(zip(entries, slots))]
-        h[0:b] = [e.tokens[0] for e in entries]
-        h[b:2 * b] = [e.start for e in entries]
-        h[2 * b:3 * b] = slots
-        h[3 * b:4 * b] = np.arange(b, dtype=np.int32)
+        start = np.fromiter((e.start for e in entries), dtype=np.int64, count=b)
+        slot = np.asarray(slots, dtype=np.int64)
+        self.portions = list(zip(slots, range(b), start.tolist(), [1] * b))
+        h[0:b] = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=b)
+        h[b:2 * b] = start
+        h[2 * b:3 * b] = slot
+        h[3 * b:4 * b] = self._arange
         for w in self.windows:
-            _, split, combine, _ = plan_attention(self.portions, w, self.split_size)
+            # one item per (entry, split): splits lo // S .. start // S of each entry, in entry order
+            lo = np.maximum(0, start - w + 1) if w else np.zeros(b, dtype=np.int64)
+            first, last = lo // self.split_size, start // self.split_size
+            count = last - first + 1
+            total = int(count.sum())
+            if total > self.capacity:
+                raise ValueError("the attention work list outgrew the capacity this graph was recorded for")
+            base = np.cumsum(count) - count                       # first scratch slot of each entry
+            owner = np.repeat(np.arange(b), count)
+            split = np.arange(total) - np.repeat(base, count) + np.repeat(first, count)
             off = self._offsets[w]
-            n = split.size
-            h[off:off + n] = split.reshape(-1)
-            h[off + n:off + self.capacity * 8] = 0
-            h[off + self.capacity * 8:off + self.capacity * 8 + combine.size] = combine.reshape(-1)
+            items = h[off:off + self.capacity * 8].reshape(self.capacity, 8)
+            items[:total, 0] = slot[owner]
+            items[:total, 1] = owner
+            items[:total, 2] = 1
+            items[:total, 3] = start[owner]
+            items[:total, 4] = split
+            items[:total, 5] = split + 1
+            items[:total, 6] = np.arange(total)
+            items[:total, 7] = 0
+            items[total:] = 0
+            comb = h[off + self.capacity * 8:off + self.capacity * 8 + b * 4].reshape(b, 4)
+            comb[:, 0] = self._arange
+            comb[:, 1] = base
+            comb[:, 2] = 1
+            comb[:, 3] = count
         self.dev.copy_(self.host, non_blocking=True)
         self.copied.record()
         self._pending = True

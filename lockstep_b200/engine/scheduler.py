@@ -49,6 +49,15 @@ class Request:
     def total_tokens(self) -> int:
         return len(self.prompt) + len(self.generated)
 
+    def tokens(self, start: int, end: int) -> list[int]:
+        """context()[start:end] without building the whole context."""
+        n = len(self.prompt)
+        if end <= n:
+            return self.prompt[start:end]
+        if start >= n:
+            return self.generated[start - n:end - n]
+        return self.prompt[start:] + self.generated[:end - n]
+
 
 class OversizedRequest(ValueError):
     """A request that cannot fit even when the pool is empty."""
@@ -200,12 +209,12 @@ class Scheduler:
         # decoding requests first, then prompts, each group oldest first
         budget = self.max_step_tokens
         planned: list[tuple[Request, int]] = []
-        order = [r for r in self.running if len(r.context()) - r.kv_len == 1] + \
-                [r for r in self.running if len(r.context()) - r.kv_len > 1]
+        order = [r for r in self.running if r.total_tokens() - r.kv_len == 1] + \
+                [r for r in self.running if r.total_tokens() - r.kv_len > 1]
         for request in order:
             if request not in self.running or budget <= 0:
                 continue
-            remaining = len(request.context()) - request.kv_len
+            remaining = request.total_tokens() - request.kv_len
             take = self.policy.chunk_boundary(state, request.uid, remaining)
             if not 1 <= take <= remaining:
                 raise ValueError(f"policy {self.policy.name} returned a portion of {take} for "
@@ -223,10 +232,9 @@ class Scheduler:
 
         entries = []
         for request, take in planned:
-            context = request.context()
             start = request.kv_len
-            last = start + take == len(context)
-            entries.append(StepEntry(uid=request.uid, tokens=context[start:start + take], start=start,
+            last = start + take == request.total_tokens()
+            entries.append(StepEntry(uid=request.uid, tokens=request.tokens(start, start + take), start=start,
                                      want=[take - 1] if last else []))
             self._event("decode" if take == 1 and last else "chunk", request.uid, (start, take))
         kinds = {len(e.tokens) == 1 for e in entries}
@@ -244,10 +252,9 @@ class Scheduler:
                                              temperature=request.temperature, top_p=request.top_p,
                                              position=request.total_tokens() - 1))
                 owners.append(request)
-        if owners:
-            tokens = self.backend.sample(logits, params)
-            for request, token in zip(owners, tokens):
-                request.generated.append(int(token))
+        tokens = self.backend.sample(logits, params)     # also where the backend reports device faults
+        for request, token in zip(owners, tokens):
+            request.generated.append(int(token))
 
         if self.audit_enabled:
             self.cache.audit()
