@@ -166,8 +166,6 @@ struct Shape {
   static constexpr int STAGES_FIT = (200 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
   static constexpr int REGION_COLS = A_TILES * BN;      // one accumulator (gate and up for silu-mul)
-  // a block that walks several shares of K gives each share an accumulator of its own
-  static constexpr int MAX_WALKED = 512 / REGION_COLS;  // shares that fit in tensor memory
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
 };
 
