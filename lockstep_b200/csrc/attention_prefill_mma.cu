@@ -110,10 +110,12 @@ attention_prefill_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv
   uint64_t* full = bars;               // [STAGES] TMA bytes landed
   uint64_t* empty = bars + STAGES;     // [STAGES] all consumer warps are done with the stage
 
-  const int* w = work + (int64_t)blockIdx.x * 8;
+  // blocks are handed out head-fastest, so the tiles with the longest context (listed
+  // first) start first for every head and the short ones fill the tail
+  const int* w = work + (int64_t)blockIdx.y * 8;
   const int req_row = w[0], tok0 = w[1], ntok = w[2], pos0 = w[3];
   if (ntok == 0) return;
-  const int h = blockIdx.y;
+  const int h = blockIdx.x;
   const int kvh = h / (nq / nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int* table_row = block_table + (int64_t)req_row * table_stride;
@@ -369,7 +371,7 @@ int launch(const CUtensorMap& map, const void* q, void* out, const int* work, in
       return LS_E_SMEM;
     configured = true;
   }
-  dim3 grid(n_work, nq);
+  dim3 grid(nq, n_work);
   ls_launch(attention_prefill_mma_kernel<HALVES>, grid, (CONSUMERS + 1) * 32, smem, stream, 
       map, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, work, block_table, table_stride, nq, nkv,
       page_size, num_pages, window, scale * 1.4426950408889634f, err);
@@ -388,7 +390,7 @@ LS_API int ls_attention_prefill_mma(const void* q, const void* pages, void* out,
                                     int nkv, int d, int page_size, int num_pages, int window,
                                     float scale, int* err, cudaStream_t stream) {
   if (n_work <= 0) return 0;
-  if (nq <= 0 || nkv <= 0 || nq % nkv || nq > 65535) return LS_E_SIZE;
+  if (nq <= 0 || nkv <= 0 || nq % nkv || n_work > 65535) return LS_E_SIZE;
   if (d != 64 && d != 128) return LS_E_SIZE;
   if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return LS_E_SIZE;
   const int64_t rows = (int64_t)num_pages * 2 * nkv * page_size;
