@@ -20,6 +20,7 @@
 // split, first scratch slot (-1: serial, write `out`), unused.
 #include <math_constants.h>
 
+#include "attention_fold.cuh"
 #include "common.cuh"
 
 #define LS_SPLIT 256
@@ -29,23 +30,6 @@ namespace {
 constexpr int TILE_M = 16;   // query tokens of a tile kernel block
 constexpr int TILE_N = 32;   // keys per tile of the tile kernel
 constexpr int MAX_D = 256;
-
-struct Fold {
-  float m, l;
-};
-
-// acc_run, m_run, l_run <- fold of (acc_s, m_s, l_s), written with explicit
-// roundings so that every caller produces the same bits.
-__device__ __forceinline__ void ls_fold_scales(float m_run, float m_s, float& alpha, float& beta,
-                                               float& m_new) {
-  m_new = fmaxf(m_run, m_s);
-  alpha = (m_run == -CUDART_INF_F) ? 0.f : expf(m_run - m_new);
-  beta = (m_s == -CUDART_INF_F) ? 0.f : expf(m_s - m_new);
-}
-
-__device__ __forceinline__ float ls_fold_value(float run, float alpha, float part, float beta) {
-  return __fmaf_rn(part, beta, __fmul_rn(run, alpha));
-}
 
 template <typename T>
 __device__ __forceinline__ const T* page_ptr(const T* pages, const int* table_row, int key,
@@ -369,36 +353,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
   const int tok = it[0], first = it[1], stride = it[2], n = it[3];
   if (n == 0) return;                        // padding item of a recorded launch
   const int h = blockIdx.y;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    float acc = 0.f, m_run = -CUDART_INF_F, l_run = 0.f;
-    // the partials of eight splits are fetched together (independent loads), then
-    // folded one after the other in ascending order
-    for (int s0 = 0; s0 < n; s0 += 8) {
-      float m_s[8], l_s[8], a_s[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (s0 + j < n) {
-          const int64_t slot = (int64_t)first + (int64_t)(s0 + j) * stride;
-          m_s[j] = part_ml[(slot * nq + h) * 2 + 0];
-          l_s[j] = part_ml[(slot * nq + h) * 2 + 1];
-          a_s[j] = part_acc[(slot * nq + h) * d + c];
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (s0 + j < n) {
-          float alpha, beta, m_new;
-          ls_fold_scales(m_run, m_s[j], alpha, beta, m_new);
-          if (m_s[j] != -CUDART_INF_F) {
-            acc = ls_fold_value(acc, alpha, a_s[j], beta);
-            l_run = ls_fold_value(l_run, alpha, l_s[j], beta);
-            m_run = m_new;
-          }
-        }
-      }
-    }
-    out[((int64_t)tok * nq + h) * d + c] = ls_from_float<T>(l_run > 0.f ? __fdiv_rn(acc, l_run) : 0.f);
-  }
+  for (int c = threadIdx.x; c < d; c += blockDim.x)
+    out[((int64_t)tok * nq + h) * d + c] = ls_from_float<T>(ls_fold_row(part_acc, part_ml, first, stride, n, nq, h, d, c));
 }
 
 size_t tile_smem_bytes(int d) {

@@ -4,6 +4,7 @@
 // All reductions run in float32 in an order fixed by the row's own width, so
 // a row's result does not depend on what else is in the batch.
 #include "common.cuh"
+#include "rope.cuh"
 
 // --------------------------------------------------------------------------
 // embedding: out[t, :] = table[ids[t], :]   (out is the float32 residual stream)
@@ -179,39 +180,13 @@ __global__ void qk_norm_rope_store_kernel(
   }
 
   const TG* gain = is_q ? q_gain : k_gain;
-  float rstd = 1.f;
-  if (gain != nullptr) {
-    float ss = 0.f;
-    for (int i = lane; i < d; i += 32) {
-      const float v = ls_to_float<T>(src[i]);
-      ss = fmaf(v, v, ss);
-    }
-    ss = ls_warp_sum(ss);
-    rstd = 1.0f / sqrtf(ss / (float)d + eps);
-  }
   const int half = rot_dim >> 1;
   if (half > 0 && (pos < 0 || pos >= max_positions)) {
     if (lane == 0) ls_record_fault(err, LS_DEV_POSITION_RANGE, t);
     return;
   }
-  const float* cs = cos_table + (int64_t)pos * half;
-  const float* sn = sin_table + (int64_t)pos * half;
-  for (int i = lane; i < half; i += 32) {
-    float lo = ls_to_float<T>(src[i]) * rstd;
-    float hi = ls_to_float<T>(src[i + half]) * rstd;
-    if (gain != nullptr) {
-      lo *= ls_to_float<TG>(gain[i]);
-      hi *= ls_to_float<TG>(gain[i + half]);
-    }
-    const float c = cs[i], s = sn[i];
-    dst[i] = ls_from_float<T>(lo * c - hi * s);
-    dst[i + half] = ls_from_float<T>(hi * c + lo * s);
-  }
-  for (int i = rot_dim + lane; i < d; i += 32) {  // dims past the rotary part
-    float v = ls_to_float<T>(src[i]) * rstd;
-    if (gain != nullptr) v *= ls_to_float<TG>(gain[i]);
-    dst[i] = ls_from_float<T>(v);
-  }
+  ls_norm_rope_head<T, TG>(src, gain, cos_table + (int64_t)pos * half, sin_table + (int64_t)pos * half, d,
+                           rot_dim, eps, lane, [&](int i, float v) { dst[i] = ls_from_float<T>(v); });
 }
 
 LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int dtype,
