@@ -75,7 +75,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
         self.thread = threading.Thread(target=self._read, daemon=True)
@@ -194,9 +194,14 @@ def time_e2e(engine, batch, context, steps, warmup):
     for r in list(sched.running):
         sched.running.remove(r)
         engine.runner.close(r.uid)
-    # per step: token ids, positions, slots, wanted rows and attention work in; sampled ids out
-    h2d = batch * 4 * 4 + batch * (context // 256 + 1) * 8 * 4 + batch * 16
-    return batch * steps / dt, h2d, batch * 4
+    # per step: one pinned buffer in (token ids, positions, slots, wanted rows, attention work
+    # lists: the recorded step's whole input), sampled ids and the error word out
+    graphs = engine.runner.graphs
+    if graphs is not None and graphs.graphs:
+        h2d = max(ctx.size for _, ctx, _, _ in graphs.graphs.values()) * 4
+    else:
+        h2d = batch * 4 * 4 + batch * (context // 256 + 1) * 8 * 4 + batch * 16
+    return batch * steps / dt, h2d, batch * 4 + 8
 
 
 def time_prefill(runner, tokens, repeats=3):
