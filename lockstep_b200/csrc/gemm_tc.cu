@@ -482,14 +482,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 
-template <int BN, int EPI, typename TC>
-__global__ void __launch_bounds__(192, 1)
+// EW epilogue warps: 4 (192 threads; token tiles up to 128 columns of sums per thread) or 8
+// (320 threads; the two groups of four epilogue warps split the token columns, so a tile of
+// 256 tokens fits, which halves the weight bytes read per output).
+template <int BN, int EPI, typename TC, int EW>
+__global__ void __launch_bounds__(EW == 8 ? 320 : 192, 1)
 gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share, int shares,
                     int tiles_n, int tiles_total, int* err) {
   using S = Shape<BN, EPI>;
-  constexpr int COLS = S::REGION_COLS;           // at most 128: the running sum fits in registers
-  static_assert(COLS <= 128 && COLS % 16 == 0, "token tile too wide for register sums");
+  constexpr int COLS = S::REGION_COLS;           // columns of one accumulator region
+  constexpr int GROUPS = EW / 4;                 // epilogue warpgroups: each takes BN / GROUPS tokens
+  constexpr int TOK = BN / GROUPS;               // tokens per epilogue thread
+  constexpr int SUMS = S::A_TILES * TOK;         // running sums per epilogue thread
+  constexpr int EPI_FIRST = 2;                   // first epilogue warp
+  static_assert(SUMS <= 128 && TOK % 16 == 0 && 2 * COLS <= 512, "token tile too wide for register sums");
   ls_dependency_trigger();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -513,7 +520,7 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     for (int r = 0; r < 2; ++r) {
       mbar_init(&acc_full[r], 1);
-      mbar_init(&acc_empty[r], 4);
+      mbar_init(&acc_empty[r], EW);
     }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -602,12 +609,13 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
     }
-  } else {
+  } else if (warp >= EPI_FIRST) {
     // epilogue: warp w may touch tensor-memory lanes 32*(w%4) .. +32
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
+    const int tok_first = ((warp - EPI_FIRST) >> 2) * TOK;      // this warpgroup's tokens of the tile
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
-    float sum[COLS];
+    float sum[SUMS];
     int sc = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
@@ -623,17 +631,22 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (!ok) break;
         fence_after_sync();
 #pragma unroll
-        for (int c0 = 0; c0 < COLS; c0 += 32) {
-          uint32_t g[32];
-          if (COLS - c0 >= 32) {
-            tmem_ld32(lane_base + (uint32_t)(region * COLS + c0), g);
-          } else {
-            tmem_ld16(lane_base + (uint32_t)(region * COLS + c0), g);
-          }
-          tmem_ld_wait();
+        for (int part = 0; part < S::A_TILES; ++part) {          // gate, then (silu-mul) up
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (c0 + j < COLS) sum[c0 + j] = (r == 0 ? 0.f : sum[c0 + j]) + __uint_as_float(g[j]);
+          for (int c0 = 0; c0 < TOK; c0 += 32) {
+            uint32_t g[32];
+            const uint32_t col = (uint32_t)(region * COLS + part * BN + tok_first + c0);
+            if (TOK - c0 >= 32) {
+              tmem_ld32(lane_base + col, g);
+            } else {
+              tmem_ld16(lane_base + col, g);
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j < TOK)
+                sum[part * TOK + c0 + j] = (r == 0 ? 0.f : sum[part * TOK + c0 + j]) + __uint_as_float(g[j]);
+          }
         }
         fence_before_sync();
         __syncwarp();
@@ -641,24 +654,25 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
       if (ok && n < N) {
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 8) {
-          if (t0 + c0 < T) {
+        for (int c0 = 0; c0 < TOK; c0 += 8) {
+          const int tb = t0 + tok_first + c0;
+          if (tb < T) {
             float old[8];
             if (EPI == 1) {
               // the residual rows are fetched together before any is written back
 #pragma unroll
               for (int j = 0; j < 8; ++j)
-                old[j] = (t0 + c0 + j < T) ? ls_to_float<TC>(C[(int64_t)(t0 + c0 + j) * ldc + n]) : 0.f;
+                old[j] = (tb + j < T) ? ls_to_float<TC>(C[(int64_t)(tb + j) * ldc + n]) : 0.f;
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const int t = t0 + c0 + j;
+              const int t = tb + j;
               if (t < T) {
                 TC* c = C + (int64_t)t * ldc + n;
                 const float a = sum[c0 + j];
                 if (EPI == 0) *c = ls_from_float<TC>(a);
                 else if (EPI == 1) *c = ls_from_float<TC>(old[j] + a);
-                else *c = ls_from_float<TC>(a / (1.0f + expf(-a)) * sum[BN + c0 + j]);
+                else *c = ls_from_float<TC>(a / (1.0f + expf(-a)) * sum[TOK + c0 + j]);
               }
             }
           }
@@ -720,7 +734,8 @@ Plan make_plan(int T, int N, int K, int epilogue) {
   p.shares = (total_kb + p.kb_per_share - 1) / p.kb_per_share;    // every share has work
   p.in_cluster = p.shares > 1 && T <= 128;
   int cap = 128;                                    // cluster: the partial tile is staged in shared memory
-  if (!p.in_cluster) cap = epilogue == 2 ? 64 : 128;   // walked: the running sum lives in registers
+  if (!p.in_cluster) cap = epilogue == 2 ? 128 : 256;   // walked: running sums in registers, over one or
+                                                        // two epilogue warpgroups
   p.bn = 16;
   while (p.bn < T && p.bn < cap) p.bn *= 2;
   return p;
@@ -771,10 +786,11 @@ template <int BN, int EPI, typename TC>
 int launch_walk(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int64_t ldc,
                 const Plan& plan, int* err, cudaStream_t stream) {
   using S = Shape<BN, EPI>;
-  if constexpr (S::REGION_COLS <= 128) {
+  constexpr int EW = S::REGION_COLS > 128 ? 8 : 4;       // wide tiles need two epilogue warpgroups
+  if constexpr (S::REGION_COLS <= 256) {
     static bool configured = false;
     if (!configured) {
-      if (cudaFuncSetAttribute(gemm_tc_walk_kernel<BN, EPI, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      if (cudaFuncSetAttribute(gemm_tc_walk_kernel<BN, EPI, TC, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)S::SMEM) != cudaSuccess)
         return LS_E_SMEM;
       configured = true;
@@ -782,8 +798,8 @@ int launch_walk(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, in
     const int tiles_n = (N + BM - 1) / BM, tiles_t = (T + BN - 1) / BN;
     const int tiles = tiles_n * tiles_t;
     const int sms = sm_count();
-    ls_launch(gemm_tc_walk_kernel<BN, EPI, TC>, tiles < sms ? tiles : sms, 192, S::SMEM, stream, mw, mx,
-              (TC*)C, T, N, K, ldc, plan.kb_per_share, plan.shares, tiles_n, tiles, err);
+    ls_launch(gemm_tc_walk_kernel<BN, EPI, TC, EW>, tiles < sms ? tiles : sms, EW == 8 ? 320 : 192, S::SMEM,
+              stream, mw, mx, (TC*)C, T, N, K, ldc, plan.kb_per_share, plan.shares, tiles_n, tiles, err);
     return ls_launch_status();
   } else {
     return LS_E_SIZE;
@@ -845,6 +861,7 @@ int run(const void* X, const NormArgs* norm, const void* W, void* C, int c_dtype
     case 32: return dispatch<32>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
     case 64: return dispatch<64>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
     case 128: return dispatch<128>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 256: return dispatch<256>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
   }
   return LS_E_SIZE;
 }
