@@ -273,12 +273,27 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  float first_old = 0.f;        // residual epilogue: the old value of the first column this block folds
   if (warp == 0) {
     if (lane == 0) {
-      // the weights do not depend on the previous kernel; the token operand read by TMA does
-      if (!NORM) ls_dependency_wait();
-      int issued = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      // the weights do not depend on the previous kernel; the token operand read by TMA does:
+      // the first round of the ring takes its weights before the wait and its tokens after
+      const int first_round = num_kb < S::STAGES ? num_kb : S::STAGES;
+      for (int kb = 0; kb < first_round; ++kb) {
+        const uint32_t stage = base + (uint32_t)kb * S::STAGE_BYTES;
+        mbar_expect_tx(&full[kb], S::STAGE_BYTES);
+        const int kx = (kb_begin + kb) * BK;
+        tma_load_2d(stage, &map_w, kx, n0, &full[kb]);
+        if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kx, N + n0, &full[kb]);
+      }
+      if (!NORM) {
+        ls_dependency_wait();
+        for (int kb = 0; kb < first_round; ++kb)
+          tma_load_2d(base + (uint32_t)kb * S::STAGE_BYTES + S::A_TILES * A_BYTES, &map_x, (kb_begin + kb) * BK, t0,
+                      &full[kb]);
+      }
+      int issued = first_round;
+      for (int kb = first_round; kb < num_kb; ++kb) {
         const int s = kb % S::STAGES;
         const uint32_t phase = (uint32_t)(kb / S::STAGES) & 1u;
         if (*failed || !mbar_wait(&empty[s], phase ^ 1u)) {
@@ -329,7 +344,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
           umma(tmem_base, smem_desc(stage + k * UMMA_K * 2), bdesc, idesc, acc);
           if (EPI == 2) umma(tmem_base + BN, smem_desc(stage + A_BYTES + k * UMMA_K * 2), bdesc, idesc, acc);
         }
-        umma_commit(&empty[s]);
+        if (kb + S::STAGES < num_kb) umma_commit(&empty[s]);     // only a stage that is filled again
       }
       if (ok) umma_commit(acc_full);
     }
@@ -339,6 +354,8 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
     ls_dependency_wait();
+    if (EPI == 1 && (int)blockIdx.z < BN && t0 + (int)blockIdx.z < T && n0 + row < N)
+      first_old = ls_to_float<TC>(C[(int64_t)(t0 + (int)blockIdx.z) * ldc + n0 + row]);   // in flight during the products
     if (NORM) {
       typedef __nv_bfloat16 bf16;
       const int k_lo = kb_begin * BK;
@@ -446,7 +463,15 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
           if (EPI == 2) u += vu[r];
         }
       }
-      if (n < N) epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, g, u);
+      if (n < N) {
+        if (EPI == 1) {
+          TC* cp = C + (int64_t)t * ldc + n;
+          const float before = c == (int)blockIdx.z ? first_old : ls_to_float<TC>(*cp);
+          *cp = ls_from_float<TC>(before + g);
+        } else {
+          epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, g, u);
+        }
+      }
     }
   }
   // no block may leave while a peer still reads its partial
