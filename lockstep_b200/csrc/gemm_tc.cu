@@ -8,7 +8,8 @@
 // the weight gives too few tiles to occupy the device (few rows of tiles, deep
 // K), K is cut into shares run by the blocks of one thread-block cluster, and
 // the shares' partial tiles are summed in ascending share order through
-// distributed shared memory.  The number of shares is a function of the
+// distributed shared memory (pushed with st.async for few tokens, read after a
+// cluster barrier for more).  The number of shares is a function of the
 // weight's shape alone (ls_gemm_tc_k_shares), so an output element is the same
 // sum whatever the batch.
 //
@@ -183,30 +184,26 @@ constexpr int MAX_SHARES = 8;
 
 // K is cut into `shares` shares of kb_per_share 64-element blocks.  An output
 // element is  ((0 + p_0) + p_1) + ... + p_{shares-1}  with p_r the float32
-// accumulation of share r in ascending k.  The shares of a tile run either in
-// the `shares` blocks of a cluster (this kernel: few tokens, many blocks wanted)
-// or one after the other in one persistent block (gemm_tc_walk_kernel); both
-// give the same bits.
+// accumulation of share r in ascending k.  The shares of a tile run in the
+// `shares` blocks of a cluster (gemm_tc_few_kernel for a tile of 16 or 32 tokens,
+// this kernel for 64 or 128) or one after the other in one persistent block
+// (gemm_tc_walk_kernel); all three give the same bits.
 //
-// NORM: the token operand is not read by TMA but made here from float32 rows:
-// x[t, :] = h[row(t), :] * rsqrt(mean(h^2) + eps) * gain, rounded to bfloat16,
-// with exactly the arithmetic of rmsnorm_kernel (a warp per row, lane l sums
-// the float4 groups l, l + 32, ... in order, lanes by an xor tree), so that
-// the fused and the separate form give the same bits.  The epilogue warps do it
-// while the first weight tiles are in flight.
-constexpr int NORM_X_BYTES = 64 * 1024;        // most shared memory the normed token operand may take
+// This kernel: every block leaves its partial tile in its own shared memory, the
+// cluster meets at a barrier, and block r folds the columns c with c % shares == r,
+// reading all shares through distributed shared memory.
+constexpr int NORM_X_BYTES = 64 * 1024;        // most shared memory a normed token operand may take
 
-template <int BN, int EPI, bool NORM>
+template <int BN, int EPI>
 struct ClusterShape {
   static constexpr int A_TILES = EPI == 2 ? 2 : 1;
-  static constexpr int B_BYTES = NORM ? 0 : BN * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
-  static constexpr int RING = (NORM ? 136 : 200) * 1024;
+  static constexpr int RING = 200 * 1024;
   static constexpr int STAGES_FIT = RING / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
   static constexpr int REGION_COLS = A_TILES * BN;
-  static constexpr int X_BYTES = NORM ? NORM_X_BYTES : 0;
-  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + X_BYTES + 1024 + 256;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
   static_assert((size_t)STAGES * STAGE_BYTES >= (size_t)REGION_COLS * BM * 4, "no room to stage the partial tile");
 };
 
@@ -219,24 +216,22 @@ struct NormArgs {
   float eps;
 };
 
-template <int BN, int EPI, typename TC, bool NORM>
+template <int BN, int EPI, typename TC>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                       const NormArgs norm, TC* __restrict__ C, int T, int N, int K, int64_t ldc,
+                       TC* __restrict__ C, int T, int N, int K, int64_t ldc,
                        int kb_per_share, int shares, int* err) {
-  using S = ClusterShape<BN, EPI, NORM>;
-  ls_dependency_trigger();                      // set-up and (NORM) the weight loads run while the previous
+  using S = ClusterShape<BN, EPI>;
+  ls_dependency_trigger();                      // set-up and the weight loads run while the previous
                                                 // kernel drains; its results are touched after the wait
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t x_base = base + (uint32_t)S::STAGES * S::STAGE_BYTES;      // NORM: [kb][BN rows][128 B]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)S::STAGES * S::STAGE_BYTES + S::X_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)S::STAGES * S::STAGE_BYTES);
   uint64_t* full = bars;                        // [STAGES] operands landed
   uint64_t* empty = bars + S::STAGES;           // [STAGES] MMAs have read the stage
   uint64_t* acc_full = bars + 2 * S::STAGES;    // [1] the accumulator is complete
-  uint64_t* x_ready = acc_full + 1;             // [1] NORM: the token operand is in shared memory
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(x_ready + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile uint32_t* failed = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -255,11 +250,10 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
       mbar_init(&empty[s], 1);
     }
     mbar_init(acc_full, 1);
-    mbar_init(x_ready, 4);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-    if (!NORM) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
   }
   if (warp == 2) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -286,12 +280,10 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         tma_load_2d(stage, &map_w, kx, n0, &full[kb]);
         if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kx, N + n0, &full[kb]);
       }
-      if (!NORM) {
-        ls_dependency_wait();
-        for (int kb = 0; kb < first_round; ++kb)
-          tma_load_2d(base + (uint32_t)kb * S::STAGE_BYTES + S::A_TILES * A_BYTES, &map_x, (kb_begin + kb) * BK, t0,
-                      &full[kb]);
-      }
+      ls_dependency_wait();
+      for (int kb = 0; kb < first_round; ++kb)
+        tma_load_2d(base + (uint32_t)kb * S::STAGE_BYTES + S::A_TILES * A_BYTES, &map_x, (kb_begin + kb) * BK, t0,
+                    &full[kb]);
       int issued = first_round;
       for (int kb = first_round; kb < num_kb; ++kb) {
         const int s = kb % S::STAGES;
@@ -306,7 +298,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         const int kx = (kb_begin + kb) * BK;
         tma_load_2d(stage, &map_w, kx, n0, &full[s]);
         if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kx, N + n0, &full[s]);
-        if (!NORM) tma_load_2d(stage + S::A_TILES * A_BYTES, &map_x, kx, t0, &full[s]);
+        tma_load_2d(stage + S::A_TILES * A_BYTES, &map_x, kx, t0, &full[s]);
         issued = kb + 1;
       }
       if (*failed) {
@@ -320,11 +312,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BM, BN);
       bool ok = true;
-      if (NORM && !mbar_wait(x_ready, 0)) {
-        *failed = 1;
-        ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 260);
-        ok = false;
-      }
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % S::STAGES;
         const uint32_t phase = (uint32_t)(kb / S::STAGES) & 1u;
@@ -336,7 +323,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         }
         fence_after_sync();
         const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
-        const uint32_t xs = NORM ? x_base + (uint32_t)(kb * BN * 128) : stage + S::A_TILES * A_BYTES;
+        const uint32_t xs = stage + S::A_TILES * A_BYTES;
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
           const uint64_t bdesc = smem_desc(xs + k * UMMA_K * 2);
@@ -356,63 +343,6 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     ls_dependency_wait();
     if (EPI == 1 && (int)blockIdx.z < BN && t0 + (int)blockIdx.z < T && n0 + row < N)
       first_old = ls_to_float<TC>(C[(int64_t)(t0 + (int)blockIdx.z) * ldc + n0 + row]);   // in flight during the products
-    if (NORM) {
-      typedef __nv_bfloat16 bf16;
-      const int k_lo = kb_begin * BK;
-      const int k_hi = kb_end * BK < K ? kb_end * BK : K;
-      const int groups = K >> 2;
-      for (int t = warp - 2; t < BN; t += 4) {
-        uint8_t* xrow = aligned + (x_base - base) + t * 128;       // row t of k-block 0
-        if (t0 + t < T) {
-          int src = norm.row_index ? norm.row_index[t0 + t] : t0 + t;
-          if (src < 0 || src >= norm.src_rows) {
-            if (lane == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, t0 + t);
-            src = 0;
-          }
-          const float* xr = norm.h + (int64_t)src * K;
-          float ss = 0.f;
-          for (int g = lane; g < groups; g += 32) {
-            const float4 v = *reinterpret_cast<const float4*>(xr + 4 * g);
-            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-          }
-          ss = ls_warp_sum(ss);
-          const float rstd = 1.0f / sqrtf(ss / (float)K + norm.eps);
-          for (int g = (k_lo >> 2) + lane; g < (k_hi >> 2); g += 32) {
-            const float4 v = *reinterpret_cast<const float4*>(xr + 4 * g);
-            float gn[4];
-            if (norm.gain_bf16) {
-              const bf16* gp = reinterpret_cast<const bf16*>(norm.gain) + 4 * g;
-              gn[0] = __bfloat162float(gp[0]); gn[1] = __bfloat162float(gp[1]);
-              gn[2] = __bfloat162float(gp[2]); gn[3] = __bfloat162float(gp[3]);
-            } else {
-              const float4 gv = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(norm.gain) + 4 * g);
-              gn[0] = gv.x; gn[1] = gv.y; gn[2] = gv.z; gn[3] = gv.w;
-            }
-            const int k = 4 * g - k_lo;                         // column within the share
-            const int kb = k >> 6, kk = k & 63;
-            __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * rstd * gn[0], v.y * rstd * gn[1]);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * rstd * gn[2], v.w * rstd * gn[3]);
-            uint2 packed;
-            packed.x = *reinterpret_cast<uint32_t*>(&lo);
-            packed.y = *reinterpret_cast<uint32_t*>(&hi);
-            *reinterpret_cast<uint2*>(xrow + kb * (BN * 128) + (((kk >> 3) ^ (t & 7)) << 4) + (kk & 7) * 2) = packed;
-          }
-          // columns of the last k-block past K
-          for (int k = k_hi - k_lo + 4 * lane; k < num_kb * BK; k += 128) {
-            const int kb = k >> 6, kk = k & 63;
-            *reinterpret_cast<uint2*>(xrow + kb * (BN * 128) + (((kk >> 3) ^ (t & 7)) << 4) + (kk & 7) * 2) = make_uint2(0u, 0u);
-          }
-        } else {
-          for (int k = 4 * lane; k < num_kb * BK; k += 128) {
-            const int kb = k >> 6, kk = k & 63;
-            *reinterpret_cast<uint2*>(xrow + kb * (BN * 128) + (((kk >> 3) ^ (t & 7)) << 4) + (kk & 7) * 2) = make_uint2(0u, 0u);
-          }
-        }
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(x_ready);
-    }
     bool ok = mbar_wait(acc_full, 0);
     if (!ok) {
       *failed = 1;
@@ -477,6 +407,424 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   // no block may leave while a peer still reads its partial
   __syncwarp();
   asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ACC_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Few tokens (a tile of 16 or 32): the decode step's products.  The same shares
+// in the blocks of a cluster, but nothing waits at a cluster barrier for the
+// sums.  A block that has its share's tile pushes every column straight from
+// registers into the shared memory of the block that folds that column (column
+// c belongs to rank c % shares) with stores that count their bytes on that
+// block's barrier (st.async); a block folds as soon as the bytes of all shares
+// have landed, a block with no column to fold does not wait at all, and either
+// may leave at
+// once, since nobody reads its memory.  The ring is as deep as the share (all
+// weights of a block are in flight before the previous kernel has ended), and
+// with NORM the token operand is not read by TMA but made here from float32 rows,
+// x[t, :] = h[row(t), :] * rsqrt(mean(h^2) + eps) * gain rounded to bfloat16, with
+// exactly the arithmetic of rmsnorm_kernel, so that the fused and the separate
+// form give the same bits; the epilogue warps do it, two rows of a warp at a time
+// with all their loads in flight together, the gain fetched before the wait on
+// the previous kernel.  Sums and their order are those of the other two kernels.
+// ---------------------------------------------------------------------------
+constexpr int MAX_STAGES = 12;
+
+struct FewLayout {
+  int stages;            // depth of the ring
+  int slots;             // columns one block folds: ceil(BN / shares)
+  uint32_t x_off;        // NORM: normed rows [kb][BN][128 B], from the aligned base
+  uint32_t recv_off;     // received partials [share][slot][part][128] float32
+  uint32_t bars_off;     // barriers and words
+  uint32_t smem;         // dynamic shared memory of the launch
+};
+
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, int rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+// A float32 into a peer's shared memory that counts itself (4 bytes) on the peer's barrier
+// when it has landed: no fence and no separate arrival follow the pushes.
+__device__ __forceinline__ void st_async_f32(uint32_t cluster_addr, float v, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(cluster_addr),
+               "r"(__float_as_uint(v)), "r"(cluster_bar)
+               : "memory");
+}
+// the limit is four times that of a block's own waits: a peer that ran into its own limit
+// is given up on later than that
+__device__ __forceinline__ bool mbar_wait_long(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < 4u * WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// The gain of a share's columns as one lane needs it (groups k_lo/4 + lane + 32 j), fetched
+// before the wait on the previous kernel: a weight, and the one access of the norm that
+// goes to device memory.
+constexpr int GAIN_KEEP = 4;      // float4 groups per lane kept in registers (a share of 512 columns)
+
+__device__ __forceinline__ float4 load_gain4(const NormArgs& norm, int g) {
+  typedef __nv_bfloat16 bf16;
+  if (norm.gain_bf16) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(norm.gain) + 4 * g);
+    const __nv_bfloat162 g01 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 g23 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__bfloat162float(g01.x), __bfloat162float(g01.y), __bfloat162float(g23.x),
+                       __bfloat162float(g23.y));
+  }
+  return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(norm.gain) + 4 * g);
+}
+
+// Rows t_a and t_b (t_b < 0: none) of the token tile, normed and rounded, written into the
+// swizzled operand layout: the arithmetic of rmsnorm_kernel (lane l sums the float4 groups
+// l, l + 32, ... in order, lanes by an xor tree), with the loads of both rows issued together.
+template <int BN>
+__device__ __forceinline__ void normed_rows_to_smem(const NormArgs& norm, const float4* gain_kept,
+                                                    uint8_t* x_region, int t_a, int t_b, int t0, int K,
+                                                    int k_lo, int k_hi, int num_kb, int lane, int* err) {
+  constexpr int U = 8;                               // float4 groups per lane and row in flight
+  const int groups = K >> 2;
+  const float* xr[2];
+  const int tt[2] = {t_a, t_b};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    int src = 0;
+    if (tt[i] >= 0) {
+      src = norm.row_index ? norm.row_index[t0 + tt[i]] : t0 + tt[i];
+      if (src < 0 || src >= norm.src_rows) {
+        if (lane == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, t0 + tt[i]);
+        src = 0;
+      }
+    }
+    xr[i] = norm.h + (int64_t)src * K;
+  }
+  float ss[2] = {0.f, 0.f};
+  for (int g0 = lane; g0 < groups; g0 += 32 * U) {
+    float4 v[2][U];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int g = g0 + 32 * u;
+        v[i][u] = (tt[i] >= 0 && g < groups) ? *reinterpret_cast<const float4*>(xr[i] + 4 * g)
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (g0 + 32 * u < groups) {
+          ss[i] = fmaf(v[i][u].x, v[i][u].x, ss[i]); ss[i] = fmaf(v[i][u].y, v[i][u].y, ss[i]);
+          ss[i] = fmaf(v[i][u].z, v[i][u].z, ss[i]); ss[i] = fmaf(v[i][u].w, v[i][u].w, ss[i]);
+        }
+      }
+  }
+  float rstd[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) rstd[i] = 1.0f / sqrtf(ls_warp_sum(ss[i]) / (float)K + norm.eps);
+  int j = 0;
+  for (int g = (k_lo >> 2) + lane; g < (k_hi >> 2); g += 32, ++j) {
+    float4 v[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      v[i] = tt[i] >= 0 ? *reinterpret_cast<const float4*>(xr[i] + 4 * g) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 gn;
+    if (j < GAIN_KEEP) {
+      gn = gain_kept[0];
+#pragma unroll
+      for (int q = 1; q < GAIN_KEEP; ++q)
+        if (j == q) gn = gain_kept[q];
+    } else {
+      gn = load_gain4(norm, g);
+    }
+    const int k = 4 * g - k_lo;                      // column within the share
+    const int kb = k >> 6, kk = k & 63;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (tt[i] < 0) continue;
+      const int t = tt[i];
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v[i].x * rstd[i] * gn.x, v[i].y * rstd[i] * gn.y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(v[i].z * rstd[i] * gn.z, v[i].w * rstd[i] * gn.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(x_region + t * 128 + kb * (BN * 128) + (((kk >> 3) ^ (t & 7)) << 4) + (kk & 7) * 2) =
+          packed;
+    }
+  }
+  // columns of the last k-block past K: the weight's are zero there, these must not be NaN
+  for (int k = k_hi - k_lo + 4 * lane; k < num_kb * BK; k += 128) {
+    const int kb = k >> 6, kk = k & 63;
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (tt[i] >= 0)
+        *reinterpret_cast<uint2*>(x_region + tt[i] * 128 + kb * (BN * 128) + (((kk >> 3) ^ (tt[i] & 7)) << 4) +
+                                  (kk & 7) * 2) = make_uint2(0u, 0u);
+  }
+}
+
+template <int BN, int EPI, typename TC, bool NORM>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   const NormArgs norm, TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share,
+                   int shares, const FewLayout lay, int* err) {
+  constexpr int A_TILES = EPI == 2 ? 2 : 1;
+  constexpr int STAGE_BYTES = A_TILES * A_BYTES + (NORM ? 0 : BN * BK * 2);
+  constexpr int REGION_COLS = A_TILES * BN;
+  constexpr uint32_t ACC_COLS = (uint32_t)tmem_cols(REGION_COLS);
+  ls_dependency_trigger();
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t x_base = base + lay.x_off;
+  float* recv = reinterpret_cast<float*>(aligned + lay.recv_off);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + lay.bars_off);
+  uint64_t* full = bars;                          // [stages] operands landed
+  uint64_t* empty = bars + MAX_STAGES;            // [stages] MMAs have read the stage
+  uint64_t* acc_full = bars + 2 * MAX_STAGES;     // the accumulator is complete
+  uint64_t* x_ready = acc_full + 1;               // NORM: the token operand is in shared memory
+  uint64_t* recv_bar = acc_full + 2;              // every share's columns for this block have arrived
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 3);
+  volatile uint32_t* failed = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = lay.stages;
+  const int rank = (int)blockIdx.z;               // the cluster is the z extent of the grid
+  const int n0 = blockIdx.x * BM;
+  const int t0 = blockIdx.y * BN;
+  const int total_kb = (K + BK - 1) / BK;
+  const int kb_begin = rank * kb_per_share;
+  int kb_end = kb_begin + kb_per_share;
+  if (kb_end > total_kb) kb_end = total_kb;
+  const int num_kb = kb_end - kb_begin;
+  const int valid = T - t0 < BN ? T - t0 : BN;    // token columns of this tile
+  const int my_cols = valid > rank ? (valid - rank + shares - 1) / shares : 0;   // columns rank, rank + shares, ...
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(x_ready, 4);
+    mbar_init(recv_bar, 1);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // every share sends A_TILES x 128 floats for each column this block folds
+    if (my_cols > 0) mbar_expect_tx(recv_bar, (uint32_t)(my_cols * shares * A_TILES * BM * 4));
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    if (!NORM) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(ACC_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  cluster_arrive();                               // this block's barriers exist; waited for before the first push
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // the weights do not depend on the previous kernel; the token operand read by TMA does:
+      // the first round of the ring takes its weights before the wait and its tokens after
+      const int first_round = num_kb < stages ? num_kb : stages;
+      for (int kb = 0; kb < first_round; ++kb) {
+        const uint32_t stage = base + (uint32_t)kb * STAGE_BYTES;
+        mbar_expect_tx(&full[kb], STAGE_BYTES);
+        const int kx = (kb_begin + kb) * BK;
+        tma_load_2d(stage, &map_w, kx, n0, &full[kb]);
+        if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kx, N + n0, &full[kb]);
+      }
+      if (!NORM) {
+        ls_dependency_wait();
+        for (int kb = 0; kb < first_round; ++kb)
+          tma_load_2d(base + (uint32_t)kb * STAGE_BYTES + A_TILES * A_BYTES, &map_x, (kb_begin + kb) * BK, t0,
+                      &full[kb]);
+      }
+      int issued = first_round;
+      int s = 0;                                  // kb % stages and the parity of kb / stages, without dividing
+      uint32_t phase = 1u;
+      for (int kb = first_round; kb < num_kb; ++kb) {
+        if (*failed || !mbar_wait(&empty[s], phase ^ 1u)) {
+          *failed = 1;
+          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 400 + s);
+          break;
+        }
+        const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        const int kx = (kb_begin + kb) * BK;
+        tma_load_2d(stage, &map_w, kx, n0, &full[s]);
+        if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kx, N + n0, &full[s]);
+        if (!NORM) tma_load_2d(stage + A_TILES * A_BYTES, &map_x, kx, t0, &full[s]);
+        issued = kb + 1;
+        if (++s == stages) {
+          s = 0;
+          phase ^= 1u;
+        }
+      }
+      if (*failed) {
+        // wait (bounded) for the copies still in flight before the block exits
+        const int first = issued > stages ? issued - stages : 0;
+        for (int kb = first; kb < issued; ++kb) mbar_wait(&full[kb % stages], (uint32_t)(kb / stages) & 1u);   // cold path
+      }
+    }
+    __syncwarp();
+    cluster_wait();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BM, BN);
+      bool ok = true;
+      if (NORM && !mbar_wait(x_ready, 0)) {
+        *failed = 1;
+        ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 560);
+        ok = false;
+      }
+      int s = 0;
+      uint32_t phase = 0u;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        if (!mbar_wait(&full[s], phase)) {           // runs out too when the producer gave up
+          *failed = 1;
+          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 500 + s);
+          ok = false;
+          break;
+        }
+        fence_after_sync();
+        const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
+        const uint32_t xs = NORM ? x_base + (uint32_t)(kb * BN * 128) : stage + A_TILES * A_BYTES;
+        // a step of 16 elements along K is 32 bytes: 2 in the descriptor's address field
+        const uint64_t adesc = smem_desc(stage), udesc = smem_desc(stage + A_BYTES), bdesc = smem_desc(xs);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
+          umma(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+          if (EPI == 2) umma(tmem_base + BN, udesc + 2 * k, bdesc + 2 * k, idesc, acc);
+        }
+        if (kb + stages < num_kb) umma_commit(&empty[s]);     // only a stage that is filled again
+        if (++s == stages) {
+          s = 0;
+          phase ^= 1u;
+        }
+      }
+      if (ok) umma_commit(acc_full);
+    }
+    __syncwarp();
+    cluster_wait();
+  } else {
+    // epilogue warps: warp w may touch tensor-memory lanes 32*(w%4) .. +32
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int n = n0 + row;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const int k_lo = kb_begin * BK;
+    const int k_hi = kb_end * BK < K ? kb_end * BK : K;
+    float4 gain_kept[GAIN_KEEP];
+    if (NORM) {
+#pragma unroll
+      for (int j = 0; j < GAIN_KEEP; ++j) {
+        const int g = (k_lo >> 2) + lane + 32 * j;
+        gain_kept[j] = g < (k_hi >> 2) ? load_gain4(norm, g) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    ls_dependency_wait();
+    float first_old = 0.f;      // residual epilogue: the old value of the first column this block folds
+    if (EPI == 1 && rank < valid && n < N) first_old = ls_to_float<TC>(C[(int64_t)(t0 + rank) * ldc + n]);
+    if (NORM) {
+      for (int t = warp - 2; t < valid; t += 8)
+        normed_rows_to_smem<BN>(norm, gain_kept, aligned + lay.x_off, t, t + 4 < valid ? t + 4 : -1, t0, K, k_lo, k_hi,
+                                num_kb, lane, err);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(x_ready);
+    }
+    cluster_wait();             // every block of the cluster has its barriers and may be written to
+    bool ok = mbar_wait(acc_full, 0);
+    if (!ok) {
+      *failed = 1;
+      if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 600 + quad);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    fence_after_sync();
+    const uint32_t recv_mine = smem_u32(recv) + (uint32_t)(rank * lay.slots * A_TILES * BM + row) * 4u;
+    const uint32_t recv_bar_addr = smem_u32(recv_bar);
+    if (ok) {
+      // column c of the tile goes to the block of rank c % shares, into its slot c / shares
+#pragma unroll
+      for (int part = 0; part < A_TILES; ++part) {
+        int dest = 0, slot = 0;
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t g[16];
+          tmem_ld16(lane_base + part * BN + c0, g);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (c0 + j < valid)
+              st_async_f32(map_to_rank(recv_mine + (uint32_t)((slot * A_TILES + part) * BM) * 4u, dest),
+                           __uint_as_float(g[j]), map_to_rank(recv_bar_addr, dest));
+            if (++dest == shares) {
+              dest = 0;
+              ++slot;
+            }
+          }
+        }
+      }
+    }
+    // a block that failed pushes nothing: its peers' waits run out and they record it too
+    bool got = true;
+    if (my_cols > 0) {
+      got = mbar_wait_long(recv_bar, 0);
+      if (!got) {
+        *failed = 1;
+        if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 700 + quad);
+      }
+    }
+    if (got && !*failed && n < N) {
+      for (int slot = 0; slot < lay.slots; ++slot) {
+        const int c = rank + slot * shares;
+        if (c >= valid) break;
+        const float* p = recv + (slot * A_TILES) * BM + row;
+        const int share_stride = lay.slots * A_TILES * BM;
+        float vg[MAX_SHARES], vu[MAX_SHARES];
+#pragma unroll
+        for (int r = 0; r < MAX_SHARES; ++r) {
+          vg[r] = r < shares ? p[r * share_stride] : 0.f;
+          if (EPI == 2) vu[r] = r < shares ? p[r * share_stride + BM] : 0.f;
+        }
+        float g = 0.f, u = 0.f;
+#pragma unroll
+        for (int r = 0; r < MAX_SHARES; ++r) {
+          if (r < shares) {
+            g += vg[r];
+            if (EPI == 2) u += vu[r];
+          }
+        }
+        TC* cp = C + (int64_t)(t0 + c) * ldc + n;
+        if (EPI == 1) {
+          const float before = slot == 0 ? first_old : ls_to_float<TC>(*cp);
+          *cp = ls_from_float<TC>(before + g);
+        } else {
+          epilogue_store<EPI, TC>(cp, g, u);
+        }
+      }
+    }
+  }
   fence_before_sync();
   __syncthreads();
   if (warp == 2) {
@@ -776,13 +1124,13 @@ int sm_count() {
   return sms;
 }
 
-template <int BN, int EPI, typename TC, bool NORM>
-int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs& norm, void* C, int T, int N,
+template <int BN, int EPI, typename TC>
+int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N,
                    int K, int64_t ldc, const Plan& plan, int* err, cudaStream_t stream) {
-  using S = ClusterShape<BN, EPI, NORM>;
+  using S = ClusterShape<BN, EPI>;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc_cluster_kernel<BN, EPI, TC, NORM>,
+    if (cudaFuncSetAttribute(gemm_tc_cluster_kernel<BN, EPI, TC>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM) != cudaSuccess)
       return LS_E_SMEM;
     configured = true;
@@ -801,8 +1149,57 @@ int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs&
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ls_dependent_launch ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<BN, EPI, TC, NORM>, mw, mx, norm, (TC*)C, T,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<BN, EPI, TC>, mw, mx, (TC*)C, T,
                                      N, K, ldc, plan.kb_per_share, plan.shares, err);
+  if (e != cudaSuccess) return (int)e;
+  return ls_launch_status();
+}
+
+constexpr int MAX_DYNAMIC_SMEM = 227 * 1024;
+
+template <int BN, int EPI, typename TC, bool NORM>
+int launch_few(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs& norm, void* C, int T, int N, int K,
+               int64_t ldc, const Plan& plan, int* err, cudaStream_t stream) {
+  constexpr int A_TILES = EPI == 2 ? 2 : 1;
+  constexpr int STAGE_BYTES = A_TILES * A_BYTES + (NORM ? 0 : BN * BK * 2);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_few_kernel<BN, EPI, TC, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             MAX_DYNAMIC_SMEM) != cudaSuccess)
+      return LS_E_SMEM;
+    configured = true;
+  }
+  FewLayout lay;
+  lay.slots = (BN + plan.shares - 1) / plan.shares;
+  const int x_bytes = NORM ? plan.kb_per_share * BN * 128 : 0;
+  const int recv_bytes = plan.shares * lay.slots * A_TILES * BM * 4;
+  const int bars_bytes = 256;
+  const int fit = (MAX_DYNAMIC_SMEM - 1024 - bars_bytes - x_bytes - recv_bytes) / STAGE_BYTES;
+  lay.stages = plan.kb_per_share < MAX_STAGES ? plan.kb_per_share : MAX_STAGES;
+  if (lay.stages > fit) lay.stages = fit;
+  if (lay.stages < 1) return LS_E_SIZE;
+  lay.x_off = (uint32_t)lay.stages * STAGE_BYTES;
+  lay.recv_off = lay.x_off + (uint32_t)x_bytes;
+  lay.bars_off = lay.recv_off + (uint32_t)recv_bytes;
+  // the whole SM is asked for although less is used: a block of this kernel, resident early,
+  // must not take room from the blocks of the kernel before it (measured: slower otherwise)
+  lay.smem = MAX_DYNAMIC_SMEM;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((N + BM - 1) / BM, (T + BN - 1) / BN, plan.shares);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = lay.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = plan.shares;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ls_dependent_launch ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_few_kernel<BN, EPI, TC, NORM>, mw, mx, norm, (TC*)C, T, N, K,
+                                     ldc, plan.kb_per_share, plan.shares, lay, err);
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }
@@ -836,10 +1233,13 @@ template <int BN, int EPI, typename TC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs* norm, void* C, int T, int N, int K,
            int64_t ldc, const Plan& plan, int* err, cudaStream_t stream) {
   if (!plan.in_cluster) return launch_walk<BN, EPI, TC>(mw, mx, C, T, N, K, ldc, plan, err, stream);
-  if constexpr (BN <= 128) {
-    if (norm != nullptr) return launch_cluster<BN, EPI, TC, true>(mw, mx, *norm, C, T, N, K, ldc, plan, err, stream);
+  if constexpr (BN <= 32) {
+    if (norm != nullptr) return launch_few<BN, EPI, TC, true>(mw, mx, *norm, C, T, N, K, ldc, plan, err, stream);
     NormArgs none = {};
-    return launch_cluster<BN, EPI, TC, false>(mw, mx, none, C, T, N, K, ldc, plan, err, stream);
+    return launch_few<BN, EPI, TC, false>(mw, mx, none, C, T, N, K, ldc, plan, err, stream);
+  } else if constexpr (BN <= 128) {
+    if (norm != nullptr) return LS_E_SIZE;
+    return launch_cluster<BN, EPI, TC>(mw, mx, C, T, N, K, ldc, plan, err, stream);
   } else {
     return LS_E_SIZE;
   }
