@@ -137,56 +137,16 @@ LS_API int ls_rmsnorm(const float* x, const int* row_index, const void* gain, in
 // pages: [num_pages, 2, nkv, page_size, d]   one layer of one cache group
 // The page of a token is block_table[req_row[token] * table_stride + pos / page_size].
 // --------------------------------------------------------------------------
-template <typename T, typename TG>
-__global__ void qk_norm_rope_store_kernel(
-    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ pages,
-    const TG* __restrict__ q_gain, const TG* __restrict__ k_gain,
-    const float* __restrict__ cos_table, const float* __restrict__ sin_table,
-    const int* __restrict__ positions, const int* __restrict__ token_req,
-    const int* __restrict__ block_table, int table_stride, int tokens, int nq, int nkv, int d,
-    int rot_dim, int page_size, int num_pages, int max_positions, float eps, int write_cache,
-    int* err) {
+template <typename T>
+__global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, const LsQkvStore args, int tokens, int* err) {
   ls_dependency_sync();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int head = blockIdx.y * warps_per_block + (threadIdx.x >> 5);
   const int t = blockIdx.x;
-  const int heads_total = nq + 2 * nkv;
+  const int heads_total = args.nq + 2 * args.nkv;
   if (head >= heads_total) return;
-  const bool is_q = head < nq;
-  const bool is_k = !is_q && head < nq + nkv;
-  if (!is_q && !write_cache) return;
-
-  const T* src = qkv + (int64_t)t * heads_total * d + (int64_t)head * d;
-  const int pos = positions[t];
-
-  T* dst;
-  if (is_q) {
-    dst = q_out + ((int64_t)t * nq + head) * d;
-  } else {
-    const int kvh = is_k ? head - nq : head - nq - nkv;
-    const int row = token_req[t];
-    const int page = block_table[(int64_t)row * table_stride + pos / page_size];
-    if (page < 0 || page >= num_pages) {
-      if (lane == 0) ls_record_fault(err, LS_DEV_PAGE_RANGE, t);
-      return;
-    }
-    dst = pages + ((((int64_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + (pos % page_size)) * d;
-  }
-
-  if (!is_q && !is_k) {  // v: copied as it is
-    for (int i = lane; i < d; i += 32) dst[i] = src[i];
-    return;
-  }
-
-  const TG* gain = is_q ? q_gain : k_gain;
-  const int half = rot_dim >> 1;
-  if (half > 0 && (pos < 0 || pos >= max_positions)) {
-    if (lane == 0) ls_record_fault(err, LS_DEV_POSITION_RANGE, t);
-    return;
-  }
-  ls_norm_rope_head<T, TG>(src, gain, cos_table + (int64_t)pos * half, sin_table + (int64_t)pos * half, d,
-                           rot_dim, eps, lane, [&](int i, float v) { dst[i] = ls_from_float<T>(v); });
+  ls_qkv_head_store<T>(args, qkv + ((int64_t)t * heads_total + head) * args.d, t, head, lane, err);
 }
 
 LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int dtype,
@@ -202,17 +162,35 @@ LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int 
   const int heads = nq + 2 * nkv;
   const int warps = 4;
   dim3 grid(tokens, (heads + warps - 1) / warps);
-#define LS_QK(T, TG)                                                                          \
-  ls_launch(qk_norm_rope_store_kernel<T, TG>, grid, warps * 32, 0, stream,                           \
-      (const T*)qkv, (T*)q_out, (T*)pages, (const TG*)q_gain, (const TG*)k_gain, cos_table,   \
-      sin_table, positions, token_req, block_table, table_stride, tokens, nq, nkv, d, rot_dim, \
-      page_size, num_pages, max_positions, eps, write_cache, err)
-  if (dtype == LS_F32 && gain_dtype == LS_F32) LS_QK(float, float);
-  else if (dtype == LS_F32 && gain_dtype == LS_BF16) LS_QK(float, __nv_bfloat16);
-  else if (dtype == LS_BF16 && gain_dtype == LS_F32) LS_QK(__nv_bfloat16, float);
-  else if (dtype == LS_BF16 && gain_dtype == LS_BF16) LS_QK(__nv_bfloat16, __nv_bfloat16);
-  else return LS_E_DTYPE;
-#undef LS_QK
+  if (gain_dtype != LS_F32 && gain_dtype != LS_BF16) return LS_E_DTYPE;
+  LsQkvStore args;
+  args.q_out = q_out;
+  args.pages = pages;
+  args.q_gain = q_gain;
+  args.k_gain = k_gain;
+  args.cos_table = cos_table;
+  args.sin_table = sin_table;
+  args.positions = positions;
+  args.token_req = token_req;
+  args.block_table = block_table;
+  args.gain_bf16 = gain_dtype == LS_BF16 ? 1 : 0;
+  args.table_stride = table_stride;
+  args.nq = nq;
+  args.nkv = nkv;
+  args.d = d;
+  args.rot_dim = rot_dim;
+  args.page_size = page_size;
+  args.num_pages = num_pages;
+  args.max_positions = max_positions;
+  args.write_cache = write_cache;
+  args.eps = eps;
+  if (dtype == LS_F32)
+    ls_launch(qk_norm_rope_store_kernel<float>, grid, warps * 32, 0, stream, (const float*)qkv, args, tokens, err);
+  else if (dtype == LS_BF16)
+    ls_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream, (const __nv_bfloat16*)qkv, args,
+              tokens, err);
+  else
+    return LS_E_DTYPE;
   return ls_launch_status();
 }
 

@@ -20,12 +20,17 @@
 //   1 residual  C[t, n] += acc                      (float32, in place)
 //   2 silu-mul  C[t, n]  = silu(acc_gate) * acc_up  (W holds gate rows [0, N)
 //                                                    and up rows [N, 2N))
+//   3 q/k/v     the rows of W are q, k and v heads: each head of a token is
+//               rounded to bfloat16 and goes where ls_qkv_head_store puts it (q
+//               normed and rotated, k normed and rotated into its cache page, v
+//               copied there); few tokens only
 // Every wait on a barrier is bounded; a wait that runs out records
 // LS_DEV_WAIT_TIMEOUT in the error word and the block winds down (waits for its
 // own copies in flight, frees its tensor memory, returns).
 #include <cuda.h>
 
 #include "common.cuh"
+#include "rope.cuh"
 
 // Into how many shares K is cut for a weight of N rows and depth K: a function
 // of the weight's shape alone.  One share unless the weight has fewer than 96
@@ -441,6 +446,7 @@ struct FewLayout {
   int slots;             // columns one block folds: ceil(BN / shares)
   uint32_t x_off;        // NORM: normed rows [kb][BN][128 B], from the aligned base
   uint32_t recv_off;     // received partials [share][slot][part][128] float32
+  uint32_t head_off;     // q/k/v epilogue: folded columns [slot][128] bfloat16
   uint32_t bars_off;     // barriers and words
   uint32_t smem;         // dynamic shared memory of the launch
 };
@@ -579,8 +585,8 @@ __device__ __forceinline__ void normed_rows_to_smem(const NormArgs& norm, const 
 template <int BN, int EPI, typename TC, bool NORM>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                   const NormArgs norm, TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share,
-                   int shares, const FewLayout lay, int* err) {
+                   const NormArgs norm, const LsQkvStore heads, TC* __restrict__ C, int T, int N, int K,
+                   int64_t ldc, int kb_per_share, int shares, const FewLayout lay, int* err) {
   constexpr int A_TILES = EPI == 2 ? 2 : 1;
   constexpr int STAGE_BYTES = A_TILES * A_BYTES + (NORM ? 0 : BN * BK * 2);
   constexpr int REGION_COLS = A_TILES * BN;
@@ -742,6 +748,19 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         gain_kept[j] = g < (k_hi >> 2) ? load_gain4(norm, g) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
+    // q/k/v epilogue: where this warp's first head goes depends on the step's inputs alone
+    LsHeadTarget first_target;
+    if constexpr (EPI == 3) {
+      if (quad < my_cols * (BM / heads.d)) {
+        const int per_tile = BM / heads.d;
+        const int slot = quad / per_tile, j = quad - slot * per_tile;
+        const int head = n0 / heads.d + j;
+        if (head < heads.nq + 2 * heads.nkv)
+          first_target = ls_qkv_head_target(heads, t0 + rank + slot * shares, head, 2, lane, err);
+        else
+          first_target.dst = nullptr;
+      }
+    }
     ls_dependency_wait();
     float first_old = 0.f;      // residual epilogue: the old value of the first column this block folds
     if (EPI == 1 && rank < valid && n < N) first_old = ls_to_float<TC>(C[(int64_t)(t0 + rank) * ldc + n]);
@@ -795,7 +814,38 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 700 + quad);
       }
     }
-    if (got && !*failed && n < N) {
+    if constexpr (EPI == 3) {
+      // the folded columns, rounded as a stored projection would be, then a warp per head
+      __nv_bfloat16* folded = reinterpret_cast<__nv_bfloat16*>(aligned + lay.head_off);
+      const bool fold_ok = got && !*failed;
+      if (fold_ok) {
+        for (int slot = 0; slot < my_cols; ++slot) {
+          const float* p = recv + slot * BM + row;
+          const int share_stride = lay.slots * BM;
+          float vg[MAX_SHARES];
+#pragma unroll
+          for (int r = 0; r < MAX_SHARES; ++r) vg[r] = r < shares ? p[r * share_stride] : 0.f;
+          float g = 0.f;
+#pragma unroll
+          for (int r = 0; r < MAX_SHARES; ++r)
+            if (r < shares) g += vg[r];
+          folded[slot * BM + row] = __float2bfloat16_rn(g);
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
+      if (fold_ok) {
+        const int per_tile = BM / heads.d;                 // heads of this tile of rows
+        for (int job = quad; job < my_cols * per_tile; job += 4) {
+          const int slot = job / per_tile, j = job - slot * per_tile;
+          const int head = n0 / heads.d + j;
+          if (head >= heads.nq + 2 * heads.nkv) continue;
+          const LsHeadTarget target =
+              job == quad ? first_target
+                          : ls_qkv_head_target(heads, t0 + rank + slot * shares, head, 2, lane, err);
+          ls_qkv_head_write<__nv_bfloat16>(heads, folded + slot * BM + j * heads.d, target, lane);
+        }
+      }
+    } else if (got && !*failed && n < N) {
       for (int slot = 0; slot < lay.slots; ++slot) {
         const int c = rank + slot * shares;
         if (c >= valid) break;
@@ -1158,8 +1208,8 @@ int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T,
 constexpr int MAX_DYNAMIC_SMEM = 227 * 1024;
 
 template <int BN, int EPI, typename TC, bool NORM>
-int launch_few(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs& norm, void* C, int T, int N, int K,
-               int64_t ldc, const Plan& plan, int* err, cudaStream_t stream) {
+int launch_few(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs& norm, const LsQkvStore& heads, void* C,
+               int T, int N, int K, int64_t ldc, const Plan& plan, int* err, cudaStream_t stream) {
   constexpr int A_TILES = EPI == 2 ? 2 : 1;
   constexpr int STAGE_BYTES = A_TILES * A_BYTES + (NORM ? 0 : BN * BK * 2);
   static bool configured = false;
@@ -1173,14 +1223,16 @@ int launch_few(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs& nor
   lay.slots = (BN + plan.shares - 1) / plan.shares;
   const int x_bytes = NORM ? plan.kb_per_share * BN * 128 : 0;
   const int recv_bytes = plan.shares * lay.slots * A_TILES * BM * 4;
+  const int head_bytes = EPI == 3 ? lay.slots * BM * 2 : 0;
   const int bars_bytes = 256;
-  const int fit = (MAX_DYNAMIC_SMEM - 1024 - bars_bytes - x_bytes - recv_bytes) / STAGE_BYTES;
+  const int fit = (MAX_DYNAMIC_SMEM - 1024 - bars_bytes - x_bytes - recv_bytes - head_bytes) / STAGE_BYTES;
   lay.stages = plan.kb_per_share < MAX_STAGES ? plan.kb_per_share : MAX_STAGES;
   if (lay.stages > fit) lay.stages = fit;
   if (lay.stages < 1) return LS_E_SIZE;
   lay.x_off = (uint32_t)lay.stages * STAGE_BYTES;
   lay.recv_off = lay.x_off + (uint32_t)x_bytes;
-  lay.bars_off = lay.recv_off + (uint32_t)recv_bytes;
+  lay.head_off = lay.recv_off + (uint32_t)recv_bytes;
+  lay.bars_off = lay.head_off + (uint32_t)head_bytes;
   // the whole SM is asked for although less is used: a block of this kernel, resident early,
   // must not take room from the blocks of the kernel before it (measured: slower otherwise)
   lay.smem = MAX_DYNAMIC_SMEM;
@@ -1198,8 +1250,8 @@ int launch_few(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs& nor
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ls_dependent_launch ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_few_kernel<BN, EPI, TC, NORM>, mw, mx, norm, (TC*)C, T, N, K,
-                                     ldc, plan.kb_per_share, plan.shares, lay, err);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_few_kernel<BN, EPI, TC, NORM>, mw, mx, norm, heads, (TC*)C, T, N,
+                                     K, ldc, plan.kb_per_share, plan.shares, lay, err);
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }
@@ -1228,45 +1280,65 @@ int launch_walk(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, in
   }
 }
 
-// norm == nullptr: the token operand is read through `mx`
+// norm == nullptr: the token operand is read through `mx`; heads: the q/k/v epilogue's targets
 template <int BN, int EPI, typename TC>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs* norm, void* C, int T, int N, int K,
-           int64_t ldc, const Plan& plan, int* err, cudaStream_t stream) {
-  if (!plan.in_cluster) return launch_walk<BN, EPI, TC>(mw, mx, C, T, N, K, ldc, plan, err, stream);
-  if constexpr (BN <= 32) {
-    if (norm != nullptr) return launch_few<BN, EPI, TC, true>(mw, mx, *norm, C, T, N, K, ldc, plan, err, stream);
-    NormArgs none = {};
-    return launch_few<BN, EPI, TC, false>(mw, mx, none, C, T, N, K, ldc, plan, err, stream);
-  } else if constexpr (BN <= 128) {
-    if (norm != nullptr) return LS_E_SIZE;
-    return launch_cluster<BN, EPI, TC>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs* norm, const LsQkvStore* heads, void* C, int T,
+           int N, int K, int64_t ldc, const Plan& plan, int* err, cudaStream_t stream) {
+  if constexpr (EPI == 3) {
+    if constexpr (BN <= 32) {
+      if (!plan.in_cluster || heads == nullptr) return LS_E_SIZE;
+      NormArgs none = {};
+      if (norm != nullptr) return launch_few<BN, 3, TC, true>(mw, mx, *norm, *heads, C, T, N, K, ldc, plan, err, stream);
+      return launch_few<BN, 3, TC, false>(mw, mx, none, *heads, C, T, N, K, ldc, plan, err, stream);
+    } else {
+      return LS_E_SIZE;
+    }
   } else {
-    return LS_E_SIZE;
+    if (!plan.in_cluster) return launch_walk<BN, EPI, TC>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+    if constexpr (BN <= 32) {
+      LsQkvStore no_heads = {};
+      if (norm != nullptr)
+        return launch_few<BN, EPI, TC, true>(mw, mx, *norm, no_heads, C, T, N, K, ldc, plan, err, stream);
+      NormArgs none = {};
+      return launch_few<BN, EPI, TC, false>(mw, mx, none, no_heads, C, T, N, K, ldc, plan, err, stream);
+    } else if constexpr (BN <= 128) {
+      if (norm != nullptr) return LS_E_SIZE;
+      return launch_cluster<BN, EPI, TC>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+    } else {
+      return LS_E_SIZE;
+    }
   }
 }
 
 template <int BN>
-int dispatch(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs* norm, void* C, int c_dtype, int T,
-             int N, int K, int64_t ldc, int epilogue, const Plan& plan, int* err, cudaStream_t stream) {
+int dispatch(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs* norm, const LsQkvStore* heads, void* C,
+             int c_dtype, int T, int N, int K, int64_t ldc, int epilogue, const Plan& plan, int* err,
+             cudaStream_t stream) {
   typedef __nv_bfloat16 bf16;
-  if (epilogue == 0 && c_dtype == LS_BF16) return launch<BN, 0, bf16>(mw, mx, norm, C, T, N, K, ldc, plan, err, stream);
-  if (epilogue == 0 && c_dtype == LS_F32) return launch<BN, 0, float>(mw, mx, norm, C, T, N, K, ldc, plan, err, stream);
-  if (epilogue == 1 && c_dtype == LS_F32) return launch<BN, 1, float>(mw, mx, norm, C, T, N, K, ldc, plan, err, stream);
+  if (epilogue == 0 && c_dtype == LS_BF16)
+    return launch<BN, 0, bf16>(mw, mx, norm, heads, C, T, N, K, ldc, plan, err, stream);
+  if (epilogue == 0 && c_dtype == LS_F32)
+    return launch<BN, 0, float>(mw, mx, norm, heads, C, T, N, K, ldc, plan, err, stream);
+  if (epilogue == 1 && c_dtype == LS_F32)
+    return launch<BN, 1, float>(mw, mx, norm, heads, C, T, N, K, ldc, plan, err, stream);
   if (epilogue == 2 && c_dtype == LS_BF16) {
-    if constexpr (BN <= 128) return launch<BN, 2, bf16>(mw, mx, norm, C, T, N, K, ldc, plan, err, stream);
+    if constexpr (BN <= 128) return launch<BN, 2, bf16>(mw, mx, norm, heads, C, T, N, K, ldc, plan, err, stream);
   }
+  if (epilogue == 3 && c_dtype == LS_BF16)
+    return launch<BN, 3, bf16>(mw, mx, norm, heads, C, T, N, K, ldc, plan, err, stream);
   return LS_E_DTYPE;
 }
 
-int run(const void* X, const NormArgs* norm, const void* W, void* C, int c_dtype, int T, int N, int K,
-        int64_t ldx, int64_t ldw, int64_t ldc, int epilogue, int* err, cudaStream_t stream) {
+int run(const void* X, const NormArgs* norm, const LsQkvStore* heads, const void* W, void* C, int c_dtype, int T,
+        int N, int K, int64_t ldx, int64_t ldw, int64_t ldc, int epilogue, int* err, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (K <= 0 || epilogue < 0 || epilogue > 2) return LS_E_SIZE;
+  if (K <= 0 || epilogue < 0 || epilogue > 3 || (epilogue == 3) != (heads != nullptr)) return LS_E_SIZE;
   if ((K % 8) || (ldw % 8)) return LS_E_ALIGN;     // 16-byte row pitch
   if ((uintptr_t)W & 15) return LS_E_ALIGN;
   if ((N + BM - 1) / BM > 2147483647 / 2 || (T + 15) / 16 > 65535) return LS_E_SIZE;
   const Plan plan = make_plan(T, N, K, epilogue);
   const int bn = plan.bn;
+  if (epilogue == 3 && (!plan.in_cluster || bn > 32)) return LS_E_SIZE;    // before any work is done
   const int w_rows = epilogue == 2 ? 2 * N : N;
   CUtensorMap mw, mx;
   if (!make_map(&mw, W, w_rows, K, ldw, BM)) return LS_E_SIZE;
@@ -1282,11 +1354,11 @@ int run(const void* X, const NormArgs* norm, const void* W, void* C, int c_dtype
     mx = mw;
   }
   switch (bn) {
-    case 16: return dispatch<16>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
-    case 32: return dispatch<32>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
-    case 64: return dispatch<64>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
-    case 128: return dispatch<128>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
-    case 256: return dispatch<256>(mw, mx, norm, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 16: return dispatch<16>(mw, mx, norm, heads, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 32: return dispatch<32>(mw, mx, norm, heads, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 64: return dispatch<64>(mw, mx, norm, heads, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 128: return dispatch<128>(mw, mx, norm, heads, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
+    case 256: return dispatch<256>(mw, mx, norm, heads, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
   }
   return LS_E_SIZE;
 }
@@ -1306,7 +1378,8 @@ LS_API int ls_gemm_tc_token_tile(int T, int N, int K, int epilogue) {
 LS_API int ls_gemm_nt_tc(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K,
                          int64_t ldx, int64_t ldw, int64_t ldc, int epilogue, int* err,
                          cudaStream_t stream) {
-  return run(X, nullptr, W, C, c_dtype, T, N, K, ldx, ldw, ldc, epilogue, err, stream);
+  if (epilogue == 3) return LS_E_SIZE;
+  return run(X, nullptr, nullptr, W, C, c_dtype, T, N, K, ldx, ldw, ldc, epilogue, err, stream);
 }
 
 // The same product with the token operand made in the kernel:
@@ -1326,5 +1399,57 @@ LS_API int ls_gemm_nt_tc_rmsnorm(const float* h, const int* row_index, int src_r
   norm.gain_bf16 = gain_dtype == LS_BF16 ? 1 : 0;
   norm.src_rows = src_rows;
   norm.eps = eps;
-  return run(nullptr, &norm, W, C, c_dtype, T, N, K, 0, ldw, ldc, epilogue, err, stream);
+  if (epilogue == 3) return LS_E_SIZE;
+  return run(nullptr, &norm, nullptr, W, C, c_dtype, T, N, K, 0, ldw, ldc, epilogue, err, stream);
+}
+
+// The q/k/v projection of few tokens with its heads finished in the epilogue: what
+// ls_gemm_nt_tc (or ls_gemm_nt_tc_rmsnorm when h is given instead of X) followed by
+// ls_qk_norm_rope_store writes, bit for bit, without the projection going through memory.
+// W [(nq + 2 nkv) * d, K]; the head size must divide 128.  Returns LS_E_SIZE or LS_E_ALIGN,
+// having launched nothing, where it does not apply (more than 32 tokens, a weight whose depth
+// is not shared out); the caller then runs the two kernels.
+LS_API int ls_gemm_nt_tc_qkv_heads(const void* X, int64_t ldx, const float* h, const int* row_index, int src_rows,
+                                   const void* gain, int gain_dtype, float eps, const void* W, int64_t ldw, int T,
+                                   int K, void* q_out, void* pages, const void* q_gain, const void* k_gain,
+                                   int head_gain_dtype, const float* cos_table, const float* sin_table,
+                                   const int* positions, const int* token_req, const int* block_table,
+                                   int table_stride, int nq, int nkv, int d, int rot_dim, int page_size,
+                                   int num_pages, int max_positions, float head_eps, int write_cache, int* err,
+                                   cudaStream_t stream) {
+  if (d <= 0 || BM % d || nq <= 0 || nkv <= 0) return LS_E_SIZE;
+  if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return LS_E_SIZE;
+  if (head_gain_dtype != LS_F32 && head_gain_dtype != LS_BF16) return LS_E_DTYPE;
+  LsQkvStore heads;
+  heads.q_out = q_out;
+  heads.pages = pages;
+  heads.q_gain = q_gain;
+  heads.k_gain = k_gain;
+  heads.cos_table = cos_table;
+  heads.sin_table = sin_table;
+  heads.positions = positions;
+  heads.token_req = token_req;
+  heads.block_table = block_table;
+  heads.gain_bf16 = head_gain_dtype == LS_BF16 ? 1 : 0;
+  heads.table_stride = table_stride;
+  heads.nq = nq;
+  heads.nkv = nkv;
+  heads.d = d;
+  heads.rot_dim = rot_dim;
+  heads.page_size = page_size;
+  heads.num_pages = num_pages;
+  heads.max_positions = max_positions;
+  heads.write_cache = write_cache;
+  heads.eps = head_eps;
+  const int N = (nq + 2 * nkv) * d;
+  if (h == nullptr) return run(X, nullptr, &heads, W, nullptr, LS_BF16, T, N, K, ldx, ldw, 0, 3, err, stream);
+  if (gain_dtype != LS_F32 && gain_dtype != LS_BF16) return LS_E_DTYPE;
+  NormArgs norm;
+  norm.h = h;
+  norm.row_index = row_index;
+  norm.gain = gain;
+  norm.gain_bf16 = gain_dtype == LS_BF16 ? 1 : 0;
+  norm.src_rows = src_rows;
+  norm.eps = eps;
+  return run(nullptr, &norm, &heads, W, nullptr, LS_BF16, T, N, K, 0, ldw, 0, 3, err, stream);
 }

@@ -20,6 +20,7 @@ F32, BF16 = 0, 1
 _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
 
 EPILOGUE_STORE, EPILOGUE_RESIDUAL, EPILOGUE_SILU_MUL = 0, 1, 2
+FEW_TOKENS = 32      # up to here a product runs in the few-token kernel, which can also finish q/k/v heads
 
 _REFUSALS = {
     -1: "unsupported element type combination",
@@ -76,6 +77,10 @@ _SIGNATURES["tc"] = {
     "ls_attention_prefill_tile_tokens": [],
     "ls_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    "ls_gemm_nt_tc_qkv_heads": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p,
+                                c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "ls_gemm_nt_tc_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int,
                               c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p],
     "ls_gemm_nt_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
@@ -383,6 +388,57 @@ def gemm_nt_tc_rmsnorm(h: torch.Tensor, gain: torch.Tensor, eps: float, w: torch
     if status in (-2, -3):
         return False
     _check(status, "gemm_nt_tc_rmsnorm")
+    return True
+
+
+def gemm_nt_tc_qkv_heads(x, w, q_out, pages, q_gain, k_gain, cos, sin, positions, token_req, block_table,
+                         nq: int, nkv: int, d: int, rot_dim: int, head_eps: float, write_cache: bool, err,
+                         normed=None) -> bool:
+    """The q/k/v projection of few tokens with the work of ``qk_norm_rope_store`` done in the
+    product's epilogue (same bits, one kernel).  ``x`` [tokens, k] bfloat16, or None with
+    ``normed`` = (h float32 [rows, k], gain, eps, row_index or None) to make the RMSNorm of the
+    rows inside the product as well.  Returns False, having launched nothing, where the fused
+    form does not apply; the caller then runs the product and ``qk_norm_rope_store``."""
+    if not USE_TENSOR_CORES[0] or w.dtype != torch.bfloat16 or q_out.dtype != torch.bfloat16:
+        return False
+    tokens = q_out.shape[0]
+    k = w.shape[1]
+    if w.shape[0] != (nq + 2 * nkv) * d or q_out.shape != (tokens, nq * d):
+        raise KernelError("gemm_nt_tc_qkv_heads: shapes do not agree")
+    if (q_gain is None) != (k_gain is None):
+        raise KernelError("gemm_nt_tc_qkv_heads: q and k gains come together")
+    if q_gain is not None and (q_gain.dtype != k_gain.dtype or q_gain.numel() != d or k_gain.numel() != d):
+        raise KernelError("gemm_nt_tc_qkv_heads: gains do not match the head size")
+    if write_cache:
+        if pages.dtype != torch.bfloat16 or pages.shape[1:3] != (2, nkv) or pages.shape[4] != d:
+            raise KernelError("gemm_nt_tc_qkv_heads: cache pages do not match the projections")
+        num_pages, page_size = pages.shape[0], pages.shape[3]
+    else:
+        num_pages, page_size = 0, 1
+    if rot_dim and (cos.shape != sin.shape or cos.shape[1] != rot_dim // 2):
+        raise KernelError("gemm_nt_tc_qkv_heads: rotary tables do not match rot_dim")
+    if normed is None:
+        if x.dtype != torch.bfloat16 or x.shape != (tokens, k):
+            raise KernelError("gemm_nt_tc_qkv_heads: the token operand does not match")
+        xp, ldx, hp, rows_p, src_rows, gain_p, gain_code, eps = _dev(x, "x"), k, None, None, 0, None, F32, 0.0
+    else:
+        h, gain, eps, row_index = normed
+        if h.shape[1] != k or gain.numel() != k or (row_index is None and h.shape[0] != tokens):
+            raise KernelError("gemm_nt_tc_qkv_heads: the rows to norm do not match")
+        xp, ldx, hp, rows_p = None, 0, _dev(h, "h", torch.float32), _opt(row_index, "row_index", torch.int32)
+        src_rows, gain_p, gain_code = h.shape[0], _dev(gain, "gain"), _code(gain)
+    status = library("tc").ls_gemm_nt_tc_qkv_heads(
+        xp, ldx, hp, rows_p, src_rows, gain_p, gain_code, float(eps), _dev(w, "w"), k, tokens, k,
+        _dev(q_out, "q_out"), _opt(pages if write_cache else None, "pages"), _opt(q_gain, "q_gain"),
+        _opt(k_gain, "k_gain"), _code(q_gain) if q_gain is not None else F32,
+        _opt(cos if rot_dim else None, "cos", torch.float32), _opt(sin if rot_dim else None, "sin", torch.float32),
+        _dev(positions, "positions", torch.int32), _dev(token_req, "token_req", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.shape[-1], nq, nkv, d, rot_dim, page_size,
+        num_pages, cos.shape[0] if rot_dim else 0, float(head_eps), 1 if write_cache else 0,
+        _dev(err, "err", torch.int32), _stream())
+    if status in (-2, -3):
+        return False
+    _check(status, "gemm_nt_tc_qkv_heads")
     return True
 
 

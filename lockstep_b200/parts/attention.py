@@ -66,17 +66,26 @@ class GQAttention(Mixer):
         nq, nkv, d = self.nq, self.nkv, self.d
         dev, dt = residual.device, self.rt.dtype
         t = residual.shape[0]
-        qkv = torch.empty((t, (nq + 2 * nkv) * d), dtype=dt, device=dev)
-        if isinstance(x, NormedRows):
-            x.linear(self.w_qkv, qkv, K.EPILOGUE_STORE, self.rt.err)
-        else:
-            K.gemm_nt(x, self.w_qkv, qkv, err=self.rt.err)
         q = torch.empty((t, nq * d), dtype=dt, device=dev)
         rot = self.position.rotary()
         cos, sin, rot_dim = rot if rot is not None else (None, None, 0)
-        K.qk_norm_rope_store(qkv, q, cache.pages, self.q_gain, self.k_gain, cos, sin, ctx.positions,
-                             ctx.token_slot, cache.block_table, nq, nkv, d, rot_dim,
-                             self.qk_norm_eps or 0.0, cache.writes, self.rt.err)
+        heads = (q, cache.pages, self.q_gain, self.k_gain, cos, sin, ctx.positions, ctx.token_slot,
+                 cache.block_table, nq, nkv, d, rot_dim, self.qk_norm_eps or 0.0, cache.writes, self.rt.err)
+        # few tokens: the product finishes its heads itself (norm, rotation, cache write); else
+        # the projection goes through memory and a second kernel does that
+        fused = False
+        if t <= K.FEW_TOKENS and not self.exact:
+            pending = isinstance(x, NormedRows) and x.pending()
+            fused = K.gemm_nt_tc_qkv_heads(None if pending else (x.materialize() if isinstance(x, NormedRows) else x),
+                                           self.w_qkv, *heads,
+                                           normed=(x.h, x.gain, x.eps, x.row_index) if pending else None)
+        if not fused:
+            qkv = torch.empty((t, (nq + 2 * nkv) * d), dtype=dt, device=dev)
+            if isinstance(x, NormedRows):
+                x.linear(self.w_qkv, qkv, K.EPILOGUE_STORE, self.rt.err)
+            else:
+                K.gemm_nt(x, self.w_qkv, qkv, err=self.rt.err)
+            K.qk_norm_rope_store(qkv, *heads)
         attn = torch.empty((t, nq * d), dtype=dt, device=dev)
         plan, done = None, False
         if not self.exact and d in (64, 128):

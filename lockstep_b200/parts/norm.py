@@ -19,6 +19,10 @@ class NormedRows:
         self.gain, self.eps = norm.gain, norm.eps
         self._out = None
 
+    def pending(self) -> bool:
+        """True while nobody has asked for the normalised tensor (a product may still make it)."""
+        return self._out is None
+
     def materialize(self) -> torch.Tensor:
         if self._out is None:
             self._out = self.norm.forward(self.h, self.row_index)

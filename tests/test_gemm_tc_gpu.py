@@ -145,3 +145,72 @@ def test_norm_fusion_declines_where_it_does_not_apply():
     wide = torch.randn(151936 // 8, 1024, device=dev()).to(torch.bfloat16)
     c2 = torch.empty(4, wide.shape[0], dtype=torch.float32, device=dev())
     assert not K.gemm_nt_tc_rmsnorm(h[:4].contiguous(), gain, 1e-6, wide, c2, K.EPILOGUE_STORE, err)  # one share
+
+
+@pytest.mark.parametrize("gain_dtype", [torch.bfloat16, torch.float32, None])
+@pytest.mark.parametrize("t,nq,nkv,d,k,rot,page", [(8, 16, 8, 128, 1024, 128, 16), (1, 16, 8, 128, 1024, 128, 16),
+                                                   (5, 6, 3, 64, 512, 32, 8), (32, 4, 2, 32, 1024, 32, 32),
+                                                   (17, 3, 1, 128, 2056, 64, 16)])
+def test_qkv_heads_finished_in_the_product_give_the_same_bits(t, nq, nkv, d, k, rot, page, gain_dtype):
+    """product + qk_norm_rope_store against the product that finishes its heads, with the token
+    operand given and with the RMSNorm made inside as well; the cache is written or not."""
+    from lockstep_b200 import kernels as K
+
+    g = torch.Generator().manual_seed(t * 31 + d)
+    n = (nq + 2 * nkv) * d
+    h = (torch.randn(t, k, generator=g) * 2).to(dev())
+    norm_gain = (1 + 0.1 * torch.randn(k, generator=g)).to(torch.bfloat16).to(dev())
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(dev())
+    qg = kg = None
+    if gain_dtype is not None:
+        qg = (1 + 0.1 * torch.randn(d, generator=g)).to(gain_dtype).to(dev())
+        kg = (1 + 0.1 * torch.randn(d, generator=g)).to(gain_dtype).to(dev())
+    max_pos, num_pages = 300, 64
+    ang = torch.rand(max_pos, rot // 2, generator=g) * 6.28
+    cos, sin = ang.cos().to(dev()), ang.sin().to(dev())
+    positions = torch.randperm(max_pos, generator=g)[:t].to(torch.int32).to(dev())     # no two tokens in one place
+    token_req = torch.randint(0, 3, (t,), generator=g).to(torch.int32).to(dev())
+    table = torch.stack([torch.randperm(num_pages, generator=g)[:max_pos // page + 1] for _ in range(3)]).to(torch.int32).to(dev())
+    err = K.new_error_word(dev())
+    x = torch.empty(t, k, dtype=torch.bfloat16, device=dev())
+    K.rmsnorm(h, norm_gain, x, 1e-6, err)
+    for write in (True, False):
+        qkv = torch.empty(t, n, dtype=torch.bfloat16, device=dev())
+        assert K.gemm_nt_tc(x, w, qkv, K.EPILOGUE_STORE, err)
+        q_want = torch.zeros(t, nq * d, dtype=torch.bfloat16, device=dev())
+        pages_want = torch.zeros(num_pages, 2, nkv, page, d, dtype=torch.bfloat16, device=dev())
+        K.qk_norm_rope_store(qkv, q_want, pages_want, qg, kg, cos, sin, positions, token_req, table, nq, nkv, d, rot,
+                             1e-5, write, err)
+        for normed in (None, (h, norm_gain, 1e-6, None)):
+            q_got = torch.zeros_like(q_want)
+            pages_got = torch.zeros_like(pages_want)
+            assert K.gemm_nt_tc_qkv_heads(None if normed else x, w, q_got, pages_got, qg, kg, cos, sin, positions,
+                                          token_req, table, nq, nkv, d, rot, 1e-5, write, err, normed=normed)
+            K.raise_on_fault(err)
+            assert torch.equal(q_got, q_want)
+            assert torch.equal(pages_got, pages_want)
+            assert bool(pages_want.any()) == write
+
+
+def test_qkv_heads_in_the_product_decline_what_they_do_not_cover():
+    from lockstep_b200 import kernels as K
+
+    err = K.new_error_word(dev())
+    nq, nkv, d, k = 4, 2, 128, 1024
+    w = torch.zeros((nq + 2 * nkv) * d, k, dtype=torch.bfloat16, device=dev())
+    pages = torch.zeros(8, 2, nkv, 16, d, dtype=torch.bfloat16, device=dev())
+    table = torch.zeros(1, 4, dtype=torch.int32, device=dev())
+    cos = sin = torch.zeros(64, d // 2, device=dev())
+
+    def call(t, d_=d, w_=w):
+        x = torch.zeros(t, w_.shape[1], dtype=torch.bfloat16, device=dev())
+        q = torch.zeros(t, nq * d_, dtype=torch.bfloat16, device=dev())
+        z = torch.zeros(t, dtype=torch.int32, device=dev())
+        return K.gemm_nt_tc_qkv_heads(x, w_, q, pages, None, None, cos, sin, z, z, table, nq, nkv, d_, d_, 0.0, False, err)
+
+    assert call(8)
+    assert not call(33)                      # more tokens than the few-token kernel takes
+    # a weight with one share of K runs in the persistent kernel, which has no such epilogue
+    shallow = torch.zeros((nq + 2 * nkv) * d, 128, dtype=torch.bfloat16, device=dev())
+    assert K.library("tc").ls_gemm_tc_k_shares(shallow.shape[0], 128) == 1
+    assert not call(8, w_=shallow)
