@@ -92,7 +92,10 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
                             const int* __restrict__ work, const int* __restrict__ block_table,
                             int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
                             float scale, int* err) {
-  ls_dependency_sync();
+  // The work list, the block table and every key older than this step's token are there
+  // before the step's first kernel starts, so the first chunks are fetched while the kernel
+  // before this one (which writes the token's own key and value, and q) still runs.
+  ls_dependency_trigger();
   constexpr int D = HALVES * 64;
   constexpr int KSTEPS = D / 16;                 // k-steps of QK^T
   constexpr int DTILES = D / 8;                  // n-tiles of PV
@@ -129,18 +132,6 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
   }
   __syncwarp();
 
-  // rows of the MMA tile are the group's query heads (zero rows pad it to 16); the
-  // tile sits in shared memory with its 16-byte chunks swizzled by the row
-  {
-    const __nv_bfloat16* qb = q + ((int64_t)tok * nq + kvh * group) * D;
-    for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += WARPS * 32) {
-      const int row = idx / (D / 8), ch = idx % (D / 8);
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (row < group) v = *reinterpret_cast<const uint4*>(qb + row * D + ch * 8);
-      *reinterpret_cast<uint4*>(aligned + (q_smem - base) + row * (D * 2) + ((ch ^ (row & 7)) << 4)) = v;
-    }
-  }
-  __syncthreads();
   const int r0 = lane >> 2, cq = (lane & 3) * 2;   // this thread holds rows r0 and r0 + 8
 
   float acc[DTILES][4];
@@ -204,7 +195,24 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
 
   int it = 0;
   while (it < n_iter && !chunk_live(it)) ++it;
-  if (it < n_iter) issue(it, chunk_start(it), true, true);
+  // a chunk that holds the step's own token waits for the kernel that writes it
+  const bool first_early = it < n_iter && chunk_start(it) + CHUNK <= pos;
+  if (first_early) issue(it, chunk_start(it), true, true);
+  ls_dependency_wait();
+  if (it < n_iter && !first_early) issue(it, chunk_start(it), true, true);
+
+  // rows of the MMA tile are the group's query heads (zero rows pad it to 16); the
+  // tile sits in shared memory with its 16-byte chunks swizzled by the row
+  {
+    const __nv_bfloat16* qb = q + ((int64_t)tok * nq + kvh * group) * D;
+    for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += WARPS * 32) {
+      const int row = idx / (D / 8), ch = idx % (D / 8);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (row < group) v = *reinterpret_cast<const uint4*>(qb + row * D + ch * 8);
+      *reinterpret_cast<uint4*>(aligned + (q_smem - base) + row * (D * 2) + ((ch ^ (row & 7)) << 4)) = v;
+    }
+  }
+  __syncthreads();
 
   while (it < n_iter) {
     const int c0 = chunk_start(it);
