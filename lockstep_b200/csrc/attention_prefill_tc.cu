@@ -1,0 +1,563 @@
+// Attention of a portion of a prompt over the paged cache on the 5th-generation
+// tensor cores: bfloat16, head sizes 64 and 128.  A block takes 128 query tokens of
+// one request and one query head (a token is a row of the MMA tile, a lane of
+// tensor memory, and a thread of the softmax warps) and walks the keys in
+// ascending tiles of 128, whose edges lie at multiples of 128 keys whatever the
+// portion, so a row's arithmetic depends on its own position only.
+//
+//   S = Q K^T     tcgen05.mma, Q [128 x d] and the key tile [128 x d] K-major in
+//                 shared memory (TMA, 128-byte swizzle), S in tensor memory
+//   softmax       a thread per row reads its row of S with tcgen05.ld: maximum,
+//                 p = exp2(s * scale * log2 e - m), running m and l in registers; P
+//                 rounded to bfloat16 goes to shared memory in the K-major layout
+//   PV            tcgen05.mma, P [128 x 128] K-major, the value tile [128 keys x d]
+//                 as it lies in the cache (MN-major), into tensor memory, and the
+//                 threads add it to their running row  O = O * alpha + PV
+//
+// Six warps: warp 0 fetches Q once and key/value tiles into two stages each (the
+// pages of a tile are looked up by its lanes in parallel), warp 1 issues the MMAs
+// (S of the next tile before PV of this one, so the tensor cores work while the
+// softmax runs; S has two buffers in tensor memory, PV two), warps 2..5 are the
+// softmax.  Every wait is bounded; a wait that runs out records
+// LS_DEV_WAIT_TIMEOUT and the block winds down and frees its tensor memory.
+#include <cuda.h>
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr int BLOCK_M = 128;              // query tokens per block
+constexpr int BLOCK_N = 128;              // keys per tile
+constexpr int STAGES = 2;
+constexpr int UMMA_K = 16;
+constexpr int HALF_BYTES = 128 * 128;     // 128 rows of 64 elements
+constexpr uint32_t TMEM_COLS = 512;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// K-major operand: rows of 128 bytes with 128-byte swizzle, groups of 8 rows 1024 bytes apart
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// MN-major operand (the value tile as it lies in the cache: a key is a row of 128 bytes = 64
+// elements of d): blocks of 64 elements of d are `block_stride` bytes apart (leading offset),
+// groups of 8 keys 1024 bytes (stride offset); 128-byte swizzle
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr, uint32_t block_stride) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((block_stride >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// D float32, A and B bfloat16, A K-major, B K-major or MN-major, M x N
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before_sync() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_after_sync() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// 2^x on the special-function unit, one instruction (inputs here are <= 0 or -inf)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// HALVES = d / 64.  Shared memory: Q [HALVES][128 rows][128 B]; two stages of K and of V
+// [HALVES][128 keys][128 B]; P [2][128 rows][128 B] (keys 0..63, 64..127); barriers.
+template <int HALVES>
+__global__ void __launch_bounds__(192, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                            __nv_bfloat16* __restrict__ out, const int* __restrict__ work,
+                            const int* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size,
+                            int num_pages, int window, float scale_log2, int* err) {
+  ls_dependency_trigger();
+  constexpr int D = HALVES * 64;
+  constexpr int KV_BYTES = HALVES * HALF_BYTES;          // K (or V) of one tile; also Q
+  constexpr int P_BYTES = 2 * HALF_BYTES;
+  constexpr uint32_t S_COL = 0, O_COL = 2 * BLOCK_N;     // tensor memory: S buffers, then PV buffers
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base;
+  const uint32_t k_smem = q_smem + KV_BYTES;             // [STAGES]
+  const uint32_t v_smem = k_smem + STAGES * KV_BYTES;    // [STAGES]
+  const uint32_t p_smem = v_smem + STAGES * KV_BYTES;
+  uint8_t* p_ptr = aligned + (p_smem - base);
+  uint8_t* v_ptr = aligned + (v_smem - base);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (p_smem - base) + P_BYTES);
+  uint64_t* q_full = bars;             // Q landed
+  uint64_t* k_full = bars + 1;         // [2] keys of a tile landed
+  uint64_t* v_full = bars + 3;         // [2] values landed
+  uint64_t* k_free = bars + 5;         // [2] S = Q K^T has read the stage
+  uint64_t* v_free = bars + 7;         // [2] PV has read the stage
+  uint64_t* s_full = bars + 9;         // [2] S of a tile is in tensor memory
+  uint64_t* s_free = bars + 11;        // [2] the softmax warps have read it (4 arrivals)
+  uint64_t* p_full = bars + 13;        // P of a tile is in shared memory (4 arrivals)
+  uint64_t* o_full = bars + 14;        // [2] PV of a tile is in tensor memory (and P may be overwritten)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile uint32_t* failed = tmem_slot + 1;
+
+  // blocks are handed out head-fastest, so the tiles with the longest context (listed
+  // first) start first for every head and the short ones fill the tail
+  const int* w = work + (int64_t)blockIdx.y * 8;
+  const int req_row = w[0], tok0 = w[1], ntok = w[2], pos0 = w[3];
+  if (ntok == 0) return;
+  const int h = blockIdx.x;
+  const int kvh = h / (nq / nkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int* table_row = block_table + (int64_t)req_row * table_stride;
+
+  const int pos_last = pos0 + ntok - 1;
+  const int key_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;   // first key any row reads
+  const int tile_first = key_lo / BLOCK_N;
+  const int tile_end = pos_last / BLOCK_N + 1;
+  const int n_tiles = tile_end - tile_first;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&k_free[s], 1);
+      mbar_init(&v_free[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_free[s], 4);
+      mbar_init(&o_full[s], 1);
+    }
+    mbar_init(p_full, 4);
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  ls_dependency_wait();                 // q and this step's keys and values come from the kernel before
+
+  if (warp == 0) {
+    // ---- producer ----
+    if (lane == 0) {
+      mbar_expect_tx(q_full, KV_BYTES);
+#pragma unroll
+      for (int hh = 0; hh < HALVES; ++hh) tma_load_2d(q_smem + hh * HALF_BYTES, &map_q, h * D + hh * 64, tok0, q_full);
+    }
+    const int rows_per_box = page_size < BLOCK_N ? page_size : BLOCK_N;
+    const int boxes = BLOCK_N / rows_per_box;            // at most 16
+    for (int it = 0; it < n_tiles; ++it) {
+      const int s = it & 1;
+      const uint32_t phase = (uint32_t)(it >> 1) & 1u;
+      const int c0 = (tile_first + it) * BLOCK_N;
+      int page = 0;
+      if (lane < boxes) {
+        int key = c0 + lane * rows_per_box;
+        if (key > pos_last) key = pos_last;              // past the last key: any page that exists
+        if (key < key_lo) key = key_lo;                  // behind the window: pages may have been given back
+        page = table_row[key / page_size];
+        if (page < 0 || page >= num_pages) {
+          ls_record_fault(err, LS_DEV_PAGE_RANGE, key);
+          page = 0;
+        }
+      }
+      bool ok = *failed == 0 && mbar_wait(&k_free[s], phase ^ 1u) && mbar_wait(&v_free[s], phase ^ 1u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        *failed = 1;
+        if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 800 + s);
+        break;
+      }
+      if (lane == 0) {
+        mbar_expect_tx(&k_full[s], KV_BYTES);
+        mbar_expect_tx(&v_full[s], KV_BYTES);
+      }
+      for (int b = 0; b < boxes; ++b) {
+        const int pg = __shfl_sync(0xffffffffu, page, b);
+        if (lane == 0) {
+          const int in_page = ((c0 + b * rows_per_box) % page_size) / rows_per_box * rows_per_box;
+          const int y_k = ((pg * 2 + 0) * nkv + kvh) * page_size + in_page;
+          const int y_v = ((pg * 2 + 1) * nkv + kvh) * page_size + in_page;
+#pragma unroll
+          for (int hh = 0; hh < HALVES; ++hh) {
+            const uint32_t off = (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + b * rows_per_box * 128);
+            tma_load_2d(k_smem + off, &map_kv, hh * 64, y_k, &k_full[s]);
+            tma_load_2d(v_smem + off, &map_kv, hh * 64, y_v, &v_full[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue ----
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = instr_desc(BLOCK_M, BLOCK_N, false);
+      constexpr uint32_t idesc_o = instr_desc(BLOCK_M, D, true);
+      bool ok = mbar_wait(q_full, 0);
+      auto issue_s = [&](int it) {       // S(it) = Q K(it)^T into S buffer it & 1
+        const int s = it & 1;
+        const uint32_t phase = (uint32_t)(it >> 1) & 1u;
+        if (!mbar_wait(&k_full[s], phase)) return false;
+        if (it >= 2 && !mbar_wait(&s_free[s], (uint32_t)((it >> 1) - 1) & 1u)) return false;
+        fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < D / UMMA_K; ++k) {
+          const uint32_t koff = (uint32_t)((k >> 2) * HALF_BYTES + (k & 3) * UMMA_K * 2);
+          umma(tmem_base + S_COL + s * BLOCK_N, desc_k_major(q_smem + koff),
+               desc_k_major(k_smem + s * KV_BYTES + koff), idesc_s, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[s]);
+        umma_commit(&k_free[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int it = 0; it < n_tiles && ok; ++it) {
+        const int s = it & 1;
+        const uint32_t phase = (uint32_t)(it >> 1) & 1u;
+        if (it + 1 < n_tiles) ok = issue_s(it + 1);
+        if (!ok) break;
+        if (!mbar_wait(p_full, (uint32_t)it & 1u) || !mbar_wait(&v_full[s], phase)) {
+          ok = false;
+          break;
+        }
+        fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < BLOCK_N / UMMA_K; ++k) {
+          // P: 16 keys are 32 bytes of a row; V: 16 keys are 16 rows of 128 bytes
+          const uint64_t a = desc_k_major(p_smem + (k >> 2) * HALF_BYTES + (k & 3) * UMMA_K * 2);
+          const uint64_t b = desc_mn_major(v_smem + s * KV_BYTES + k * UMMA_K * 128, HALF_BYTES);
+          umma(tmem_base + O_COL + s * D, a, b, idesc_o, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&o_full[s]);
+        umma_commit(&v_free[s]);
+      }
+      if (!ok) {
+        *failed = 1;
+        ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 820);
+      }
+    }
+  } else {
+    // ---- softmax: this thread owns row `row` of the tile (a token), lane `row` of tensor memory ----
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const int pos = pos0 + row;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
+    float o[D];
+#pragma unroll
+    for (int c = 0; c < D; ++c) o[c] = 0.f;
+    float m_run = -CUDART_INF_F, l_run = 0.f, alpha_pending = 1.f;
+    bool ok = true;
+
+    // O = O * alpha + PV of tile `it` (its scale alpha was fixed when its P was made)
+    auto take_pv = [&](int it) {
+      const int s = it & 1;
+      if (!mbar_wait(&o_full[s], (uint32_t)(it >> 1) & 1u)) return false;
+      fence_after_sync();
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t g[32];
+        tmem_ld32(lane_base + O_COL + s * D + c0, g);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[c0 + j] = fmaf(o[c0 + j], alpha_pending, __uint_as_float(g[j]));
+      }
+      return true;
+    };
+
+    for (int it = 0; it < n_tiles && ok; ++it) {
+      const int s = it & 1;
+      const int c0 = (tile_first + it) * BLOCK_N;
+      if (!mbar_wait(&s_full[s], (uint32_t)(it >> 1) & 1u)) {
+        ok = false;
+        break;
+      }
+      fence_after_sync();
+      // every key of the tile is seen by every row: no masks (uniform over the block)
+      const bool full_tile = c0 + BLOCK_N - 1 <= pos0 && c0 >= lo_last;
+      // pass 1: the row's maximum over the tile (four running maxima: no long chain)
+      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int n0 = 0; n0 < BLOCK_N; n0 += 32) {
+        uint32_t g[32];
+        tmem_ld32(lane_base + S_COL + s * BLOCK_N + n0, g);
+        tmem_ld_wait();
+        if (full_tile) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(g[j]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = c0 + n0 + j;
+            if (key <= pos && key >= lo) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(g[j]));
+          }
+        }
+      }
+      const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const float m_new = fmaxf(m_run, tile_max * scale_log2);
+      const float alpha = (m_run == -CUDART_INF_F) ? 0.f : ex2(m_run - m_new);       // m_new >= m_run
+      // the tile before this one must be through PV before its P is overwritten; its PV is taken
+      // after this tile's P has gone out, while the tensor cores work on it
+      if (it > 0 && !mbar_wait(&o_full[(it - 1) & 1], (uint32_t)((it - 1) >> 1) & 1u)) {
+        ok = false;
+        break;
+      }
+      // pass 2: p = exp2(s * scale - m), rounded to bfloat16 into the K-major tile of P; the row sum
+      // in four running sums, folded in a fixed order
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+      const bool dead = m_new == -CUDART_INF_F;          // nothing seen yet by this row
+      const float neg_m = dead ? 0.f : -m_new;
+#pragma unroll
+      for (int n0 = 0; n0 < BLOCK_N; n0 += 32) {
+        uint32_t g[32];
+        tmem_ld32(lane_base + S_COL + s * BLOCK_N + n0, g);
+        tmem_ld_wait();
+        float p[32];
+        if (full_tile) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) p[j] = ex2(fmaf(__uint_as_float(g[j]), scale_log2, neg_m));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = c0 + n0 + j;
+            const bool keep = key <= pos && key >= lo && !dead;
+            p[j] = keep ? ex2(fmaf(__uint_as_float(g[j]), scale_log2, neg_m)) : 0.f;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) ps[j & 3] += p[j];
+        // 32 keys are 64 bytes: four 16-byte chunks of the row's 128-byte line of this half
+        uint8_t* line = p_ptr + (n0 >> 6) * HALF_BYTES + row * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = ((n0 & 63) >> 3) + q4;
+          *reinterpret_cast<uint4*>(line + ((chunk ^ (row & 7)) << 4)) =
+              make_uint4(pack_bf16(p[q4 * 8], p[q4 * 8 + 1]), pack_bf16(p[q4 * 8 + 2], p[q4 * 8 + 3]),
+                         pack_bf16(p[q4 * 8 + 4], p[q4 * 8 + 5]), pack_bf16(p[q4 * 8 + 6], p[q4 * 8 + 7]));
+        }
+      }
+      const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[s]);
+      // value rows of keys past the last position were never written: they must not be NaN,
+      // since P is zero there and the MMA multiplies all the same
+      if (c0 + BLOCK_N - 1 > pos_last) {
+        if (!mbar_wait(&v_full[s], (uint32_t)(it >> 1) & 1u)) {
+          ok = false;
+          break;
+        }
+        if (c0 + row > pos_last) {
+#pragma unroll
+          for (int hh = 0; hh < HALVES; ++hh) {
+            uint4* vrow = reinterpret_cast<uint4*>(v_ptr + s * KV_BYTES + hh * HALF_BYTES + row * 128);
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) vrow[q8] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      // the tile before: its PV into the running row, with the scale its own P was made with
+      if (it > 0) {
+        if (!take_pv(it - 1)) {
+          ok = false;
+          break;
+        }
+      }
+      l_run = fmaf(l_run, alpha, psum);
+      alpha_pending = alpha;
+      m_run = m_new;
+    }
+    if (ok && n_tiles > 0) ok = take_pv(n_tiles - 1);
+    if (!ok) {
+      *failed = 1;
+      if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 840 + quad);
+    } else if (row < ntok) {
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      __nv_bfloat16* dst = out + ((int64_t)(tok0 + row) * nq + h) * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 8) {
+        uint4 v;
+        v.x = pack_bf16(o[c] * inv, o[c + 1] * inv);
+        v.y = pack_bf16(o[c + 2] * inv, o[c + 3] * inv);
+        v.z = pack_bf16(o[c + 4] * inv, o[c + 5] * inv);
+        v.w = pack_bf16(o[c + 6] * inv, o[c + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + c) = v;
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)p;
+  }
+  return fn;
+}
+
+bool encode(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint32_t box_rows) {
+  EncodeTiled enc = encode_fn();
+  if (enc == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)inner * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int HALVES>
+int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const int* work, int n_work,
+           const int* block_table, int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
+           float scale, int* err, cudaStream_t stream) {
+  constexpr int KV_BYTES = HALVES * HALF_BYTES;
+  const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 2 * HALF_BYTES + 256 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return LS_E_SMEM;
+    configured = true;
+  }
+  dim3 grid(nq, n_work);
+  ls_launch(attention_prefill_tc_kernel<HALVES>, grid, 192, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work,
+            block_table, table_stride, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
+  return ls_launch_status();
+}
+
+}  // namespace
+
+LS_API int ls_attention_prefill_tc_tile_tokens() { return BLOCK_M; }
+
+// q, out: [tokens, nq * d] bfloat16; pages [num_pages, 2, nkv, page_size, d]; d 64 or 128; page
+// sizes 8, 16, 32, 64, 128.  Work items as for ls_attention_tile with up to 128 tokens each
+// (splits and slots are not used).  Returns LS_E_SIZE or LS_E_ALIGN for anything else, having
+// launched nothing.
+LS_API int ls_attention_prefill_tc(const void* q, const void* pages, void* out, int tokens, const int* work,
+                                   int n_work, const int* block_table, int table_stride, int nq, int nkv, int d,
+                                   int page_size, int num_pages, int window, float scale, int* err,
+                                   cudaStream_t stream) {
+  if (n_work <= 0 || tokens <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv || n_work > 65535) return LS_E_SIZE;
+  if (d != 64 && d != 128) return LS_E_SIZE;
+  if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return LS_E_SIZE;
+  const int64_t rows = (int64_t)num_pages * 2 * nkv * page_size;
+  if (rows > 2147483647LL) return LS_E_SIZE;
+  if (((uintptr_t)pages & 127) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return LS_E_ALIGN;
+  CUtensorMap map_q, map_kv;
+  if (!encode(&map_q, q, (uint64_t)nq * d, (uint64_t)tokens, BLOCK_M)) return LS_E_SIZE;
+  if (!encode(&map_kv, pages, (uint64_t)d, (uint64_t)rows, page_size < BLOCK_N ? page_size : BLOCK_N)) return LS_E_SIZE;
+  if (d == 64)
+    return launch<1>(map_q, map_kv, out, work, n_work, block_table, table_stride, nq, nkv, page_size, num_pages,
+                     window, scale, err, stream);
+  return launch<2>(map_q, map_kv, out, work, n_work, block_table, table_stride, nq, nkv, page_size, num_pages,
+                   window, scale, err, stream);
+}

@@ -75,6 +75,9 @@ _SIGNATURES["tc"] = {
     "ls_attention_decode_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "ls_attention_prefill_tile_tokens": [],
+    "ls_attention_prefill_tc_tile_tokens": [],
+    "ls_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "ls_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                  c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "ls_gemm_nt_tc_qkv_heads": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p,
@@ -318,6 +321,27 @@ def attention_prefill_mma(q, pages, out, work, n_work, block_table, nq, nkv, d, 
     if status == -2:
         return False
     _check(status, "attention_prefill_mma")
+    return True
+
+
+def attention_prefill_tc_tile_tokens() -> int:
+    return int(library("tc").ls_attention_prefill_tc_tile_tokens())
+
+
+def attention_prefill_tc(q, pages, out, work, n_work, block_table, nq, nkv, d, window, scale, err) -> bool:
+    """Attention of prompt portions on tcgen05 (csrc/attention_prefill_tc.cu): bfloat16, head
+    size 64 or 128, work items of up to 128 tokens.  Returns False (nothing launched) for
+    anything else."""
+    if q.dtype != torch.bfloat16 or not USE_TENSOR_CORES[0]:
+        return False
+    status = library("tc").ls_attention_prefill_tc(
+        _dev(q, "q"), _dev(pages, "pages", q.dtype), _dev(out, "out", q.dtype), q.shape[0],
+        _dev(work, "work", torch.int32), n_work, _dev(block_table, "block_table", torch.int32),
+        block_table.shape[-1], nq, nkv, d, pages.shape[3], pages.shape[0], int(window), float(scale),
+        _dev(err, "err", torch.int32), _stream())
+    if status in (-2, -3):
+        return False
+    _check(status, "attention_prefill_tc")
     return True
 
 
