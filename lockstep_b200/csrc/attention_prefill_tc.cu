@@ -7,18 +7,20 @@
 //
 //   S = Q K^T     tcgen05.mma, Q [128 x d] and the key tile [128 x d] K-major in
 //                 shared memory (TMA, 128-byte swizzle), S in tensor memory
-//   softmax       a thread per row reads its row of S with tcgen05.ld: maximum,
+//   softmax       the threads of a row read it from S with tcgen05.ld: maximum,
 //                 p = exp2(s * scale * log2 e - m), running m and l in registers; P
 //                 rounded to bfloat16 goes to shared memory in the K-major layout
 //   PV            tcgen05.mma, P [128 x 128] K-major, the value tile [128 keys x d]
 //                 as it lies in the cache (MN-major), into tensor memory, and the
 //                 threads add it to their running row  O = O * alpha + PV
 //
-// Six warps: warp 0 fetches Q once and key/value tiles into two stages each (the
+// Ten warps: warp 0 fetches Q once and key/value tiles into two stages each (the
 // pages of a tile are looked up by its lanes in parallel), warp 1 issues the MMAs
 // (S of the next tile before PV of this one, so the tensor cores work while the
-// softmax runs; S has two buffers in tensor memory, PV two), warps 2..5 are the
-// softmax.  Every wait is bounded; a wait that runs out records
+// softmax runs; S has two buffers in tensor memory, PV two), warps 2..9 are the
+// softmax, two threads per row: one has the first 64 keys of a tile and the first
+// half of the head's dimensions, the other the rest; they share the row's maximum
+// through shared memory.  Every wait is bounded; a wait that runs out records
 // LS_DEV_WAIT_TIMEOUT and the block winds down and frees its tensor memory.
 #include <cuda.h>
 #include <math_constants.h>
@@ -147,7 +149,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // HALVES = d / 64.  Shared memory: Q [HALVES][128 rows][128 B]; two stages of K and of V
 // [HALVES][128 keys][128 B]; P [2][128 rows][128 B] (keys 0..63, 64..127); barriers.
 template <int HALVES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             __nv_bfloat16* __restrict__ out, const int* __restrict__ work,
                             const int* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size,
@@ -174,11 +176,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint64_t* k_free = bars + 5;         // [2] S = Q K^T has read the stage
   uint64_t* v_free = bars + 7;         // [2] PV has read the stage
   uint64_t* s_full = bars + 9;         // [2] S of a tile is in tensor memory
-  uint64_t* s_free = bars + 11;        // [2] the softmax warps have read it (4 arrivals)
-  uint64_t* p_full = bars + 13;        // P of a tile is in shared memory (4 arrivals)
+  uint64_t* s_free = bars + 11;        // [2] the softmax warps have read it (8 arrivals)
+  uint64_t* p_full = bars + 13;        // P of a tile is in shared memory (8 arrivals)
   uint64_t* o_full = bars + 14;        // [2] PV of a tile is in tensor memory (and P may be overwritten)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile uint32_t* failed = tmem_slot + 1;
+  float* row_max = reinterpret_cast<float*>(bars + 32);   // [2 tiles][2 groups][128 rows], then reused for l
 
   // blocks are handed out head-fastest, so the tiles with the longest context (listed
   // first) start first for every head and the short ones fill the tail
@@ -204,10 +207,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&k_free[s], 1);
       mbar_init(&v_free[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_free[s], 4);
+      mbar_init(&s_free[s], 8);
       mbar_init(&o_full[s], 1);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -233,14 +236,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int hh = 0; hh < HALVES; ++hh) tma_load_2d(q_smem + hh * HALF_BYTES, &map_q, h * D + hh * 64, tok0, q_full);
     }
     const int rows_per_box = page_size < BLOCK_N ? page_size : BLOCK_N;
-    const int boxes = BLOCK_N / rows_per_box;            // at most 16
-    for (int it = 0; it < n_tiles; ++it) {
-      const int s = it & 1;
-      const uint32_t phase = (uint32_t)(it >> 1) & 1u;
-      const int c0 = (tile_first + it) * BLOCK_N;
+    const int boxes = BLOCK_N / rows_per_box;            // at most 16: lane b fetches box b of a tile
+    // the page of this lane's box of tile `it`, looked up one tile ahead
+    auto lookup = [&](int it) {
       int page = 0;
-      if (lane < boxes) {
-        int key = c0 + lane * rows_per_box;
+      if (it < n_tiles && lane < boxes) {
+        int key = (tile_first + it) * BLOCK_N + lane * rows_per_box;
         if (key > pos_last) key = pos_last;              // past the last key: any page that exists
         if (key < key_lo) key = key_lo;                  // behind the window: pages may have been given back
         page = table_row[key / page_size];
@@ -249,31 +250,47 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           page = 0;
         }
       }
-      bool ok = *failed == 0 && mbar_wait(&k_free[s], phase ^ 1u) && mbar_wait(&v_free[s], phase ^ 1u);
+      return page;
+    };
+    int page = lookup(0);
+    for (int it = 0; it < n_tiles; ++it) {
+      const int s = it & 1;
+      const uint32_t phase = (uint32_t)(it >> 1) & 1u;
+      const int c0 = (tile_first + it) * BLOCK_N;
+      const int page_next = lookup(it + 1);
+      // keys of the stage first: they are free (S of two tiles ago) before the values (its PV)
+      bool ok = *failed == 0 && mbar_wait(&k_free[s], phase ^ 1u);
       ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        if (lane == 0) mbar_expect_tx(&k_full[s], KV_BYTES);
+        __syncwarp();
+        if (lane < boxes) {
+          const int in_page = ((c0 + lane * rows_per_box) % page_size) / rows_per_box * rows_per_box;
+          const int y_k = ((page * 2 + 0) * nkv + kvh) * page_size + in_page;
+#pragma unroll
+          for (int hh = 0; hh < HALVES; ++hh)
+            tma_load_2d(k_smem + (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + lane * rows_per_box * 128), &map_kv,
+                        hh * 64, y_k, &k_full[s]);
+        }
+        ok = mbar_wait(&v_free[s], phase ^ 1u);
+        ok = __all_sync(0xffffffffu, ok);
+      }
       if (!ok) {
         *failed = 1;
         if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 800 + s);
         break;
       }
-      if (lane == 0) {
-        mbar_expect_tx(&k_full[s], KV_BYTES);
-        mbar_expect_tx(&v_full[s], KV_BYTES);
-      }
-      for (int b = 0; b < boxes; ++b) {
-        const int pg = __shfl_sync(0xffffffffu, page, b);
-        if (lane == 0) {
-          const int in_page = ((c0 + b * rows_per_box) % page_size) / rows_per_box * rows_per_box;
-          const int y_k = ((pg * 2 + 0) * nkv + kvh) * page_size + in_page;
-          const int y_v = ((pg * 2 + 1) * nkv + kvh) * page_size + in_page;
+      if (lane == 0) mbar_expect_tx(&v_full[s], KV_BYTES);
+      __syncwarp();
+      if (lane < boxes) {
+        const int in_page = ((c0 + lane * rows_per_box) % page_size) / rows_per_box * rows_per_box;
+        const int y_v = ((page * 2 + 1) * nkv + kvh) * page_size + in_page;
 #pragma unroll
-          for (int hh = 0; hh < HALVES; ++hh) {
-            const uint32_t off = (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + b * rows_per_box * 128);
-            tma_load_2d(k_smem + off, &map_kv, hh * 64, y_k, &k_full[s]);
-            tma_load_2d(v_smem + off, &map_kv, hh * 64, y_v, &v_full[s]);
-          }
-        }
+        for (int hh = 0; hh < HALVES; ++hh)
+          tma_load_2d(v_smem + (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + lane * rows_per_box * 128), &map_kv,
+                      hh * 64, y_v, &v_full[s]);
       }
+      page = page_next;
     }
   } else if (warp == 1) {
     // ---- MMA issue ----
@@ -324,16 +341,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
     }
   } else {
-    // ---- softmax: this thread owns row `row` of the tile (a token), lane `row` of tensor memory ----
+    // ---- softmax: two threads per row (a token, lane `row` of tensor memory): the thread of
+    // group 0 (warps 2..5) has keys 0..63 of a tile and the first half of the head's
+    // dimensions, the thread of group 1 (warps 6..9) keys 64..127 and the second half ----
+    constexpr int HC = BLOCK_N / 2;               // keys of a tile per thread
+    constexpr int HD = D / 2;                     // output dimensions per thread
     const int quad = warp & 3;
+    const int group = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
     const int pos = pos0 + row;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
-    float o[D];
+    float o[HD];
 #pragma unroll
-    for (int c = 0; c < D; ++c) o[c] = 0.f;
+    for (int c = 0; c < HD; ++c) o[c] = 0.f;
     float m_run = -CUDART_INF_F, l_run = 0.f, alpha_pending = 1.f;
     bool ok = true;
 
@@ -342,131 +364,116 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int s = it & 1;
       if (!mbar_wait(&o_full[s], (uint32_t)(it >> 1) & 1u)) return false;
       fence_after_sync();
+      uint32_t g[HD];
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t g[32];
-        tmem_ld32(lane_base + O_COL + s * D + c0, g);
-        tmem_ld_wait();
+      for (int c0 = 0; c0 < HD; c0 += 32) tmem_ld32(lane_base + O_COL + s * D + group * HD + c0, g + c0);
+      tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[c0 + j] = fmaf(o[c0 + j], alpha_pending, __uint_as_float(g[j]));
-      }
+      for (int c = 0; c < HD; ++c) o[c] = fmaf(o[c], alpha_pending, __uint_as_float(g[c]));
       return true;
     };
 
-    for (int it = 0; it < n_tiles && ok; ++it) {
+    // A wait that runs out clears `ok`; the loop still runs to its end, skipping the work, so
+    // that every thread meets the named barrier of every tile.
+    for (int it = 0; it < n_tiles; ++it) {
       const int s = it & 1;
-      const int c0 = (tile_first + it) * BLOCK_N;
-      if (!mbar_wait(&s_full[s], (uint32_t)(it >> 1) & 1u)) {
-        ok = false;
-        break;
-      }
+      const int c0 = (tile_first + it) * BLOCK_N + group * HC;     // first key of this thread
+      if (ok && !mbar_wait(&s_full[s], (uint32_t)(it >> 1) & 1u)) ok = false;
       fence_after_sync();
+      // this thread's 64 scores into registers; the buffer is free once all have theirs
+      uint32_t g[HC];
+      tmem_ld32(lane_base + S_COL + s * BLOCK_N + group * HC, g);
+      tmem_ld32(lane_base + S_COL + s * BLOCK_N + group * HC + 32, g + 32);
+      tmem_ld_wait();
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[s]);
       // every key of the tile is seen by every row: no masks (uniform over the block)
-      const bool full_tile = c0 + BLOCK_N - 1 <= pos0 && c0 >= lo_last;
-      // pass 1: the row's maximum over the tile (four running maxima: no long chain)
+      const bool full_tile = (tile_first + it) * BLOCK_N + BLOCK_N - 1 <= pos0 && (tile_first + it) * BLOCK_N >= lo_last;
       float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+      if (full_tile) {
 #pragma unroll
-      for (int n0 = 0; n0 < BLOCK_N; n0 += 32) {
-        uint32_t g[32];
-        tmem_ld32(lane_base + S_COL + s * BLOCK_N + n0, g);
-        tmem_ld_wait();
-        if (full_tile) {
+        for (int j = 0; j < HC; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(g[j]));
+      } else {
+        // selects, not branches: a masked score counts as -inf
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(g[j]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = c0 + n0 + j;
-            if (key <= pos && key >= lo) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(g[j]));
-          }
+        for (int j = 0; j < HC; ++j) {
+          const bool keep = (c0 + j <= pos) & (c0 + j >= lo);
+          mx[j & 3] = fmaxf(mx[j & 3], keep ? __uint_as_float(g[j]) : -CUDART_INF_F);
         }
       }
-      const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      // the row's maximum is that of its two threads
+      float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      row_max[(it & 1) * 256 + group * 128 + row] = tile_max;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      tile_max = fmaxf(tile_max, row_max[(it & 1) * 256 + (group ^ 1) * 128 + row]);
       const float m_new = fmaxf(m_run, tile_max * scale_log2);
       const float alpha = (m_run == -CUDART_INF_F) ? 0.f : ex2(m_run - m_new);       // m_new >= m_run
       // the tile before this one must be through PV before its P is overwritten; its PV is taken
       // after this tile's P has gone out, while the tensor cores work on it
-      if (it > 0 && !mbar_wait(&o_full[(it - 1) & 1], (uint32_t)((it - 1) >> 1) & 1u)) {
-        ok = false;
-        break;
-      }
-      // pass 2: p = exp2(s * scale - m), rounded to bfloat16 into the K-major tile of P; the row sum
-      // in four running sums, folded in a fixed order
+      if (ok && it > 0 && !mbar_wait(&o_full[(it - 1) & 1], (uint32_t)((it - 1) >> 1) & 1u)) ok = false;
+      // p = exp2(s * scale - m), rounded to bfloat16 into this thread's 128-byte line of P
+      // (K-major, keys 64 * group ..); the sum in four running sums, folded in a fixed order
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
       const bool dead = m_new == -CUDART_INF_F;          // nothing seen yet by this row
       const float neg_m = dead ? 0.f : -m_new;
+      uint8_t* line = p_ptr + group * HALF_BYTES + row * 128;
+      if (ok) {
+        const bool plain = full_tile & !dead;             // uniform over the block but for `dead`
 #pragma unroll
-      for (int n0 = 0; n0 < BLOCK_N; n0 += 32) {
-        uint32_t g[32];
-        tmem_ld32(lane_base + S_COL + s * BLOCK_N + n0, g);
-        tmem_ld_wait();
-        float p[32];
-        if (full_tile) {
+        for (int n0 = 0; n0 < HC; n0 += 8) {
+          float p[8];
+          if (plain) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) p[j] = ex2(fmaf(__uint_as_float(g[j]), scale_log2, neg_m));
-        } else {
+            for (int j = 0; j < 8; ++j) p[j] = ex2(fmaf(__uint_as_float(g[n0 + j]), scale_log2, neg_m));
+          } else {
+            // every exponential is taken, masked ones of -inf (which is 0): selects, not branches
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = c0 + n0 + j;
-            const bool keep = key <= pos && key >= lo && !dead;
-            p[j] = keep ? ex2(fmaf(__uint_as_float(g[j]), scale_log2, neg_m)) : 0.f;
+            for (int j = 0; j < 8; ++j) {
+              const int key = c0 + n0 + j;
+              const bool keep = (key <= pos) & (key >= lo) & !dead;
+              p[j] = ex2(keep ? fmaf(__uint_as_float(g[n0 + j]), scale_log2, neg_m) : -CUDART_INF_F);
+            }
           }
-        }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) ps[j & 3] += p[j];
-        // 32 keys are 64 bytes: four 16-byte chunks of the row's 128-byte line of this half
-        uint8_t* line = p_ptr + (n0 >> 6) * HALF_BYTES + row * 128;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = ((n0 & 63) >> 3) + q4;
-          *reinterpret_cast<uint4*>(line + ((chunk ^ (row & 7)) << 4)) =
-              make_uint4(pack_bf16(p[q4 * 8], p[q4 * 8 + 1]), pack_bf16(p[q4 * 8 + 2], p[q4 * 8 + 3]),
-                         pack_bf16(p[q4 * 8 + 4], p[q4 * 8 + 5]), pack_bf16(p[q4 * 8 + 6], p[q4 * 8 + 7]));
+          for (int j = 0; j < 8; ++j) ps[j & 3] += p[j];
+          *reinterpret_cast<uint4*>(line + (((n0 >> 3) ^ (row & 7)) << 4)) =
+              make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
         }
       }
       const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[s]);
       // value rows of keys past the last position were never written: they must not be NaN,
       // since P is zero there and the MMA multiplies all the same
-      if (c0 + BLOCK_N - 1 > pos_last) {
-        if (!mbar_wait(&v_full[s], (uint32_t)(it >> 1) & 1u)) {
-          ok = false;
-          break;
-        }
-        if (c0 + row > pos_last) {
+      if ((tile_first + it) * BLOCK_N + BLOCK_N - 1 > pos_last) {
+        if (ok && !mbar_wait(&v_full[s], (uint32_t)(it >> 1) & 1u)) ok = false;
+        if (ok && group < HALVES && (tile_first + it) * BLOCK_N + row > pos_last) {
+          uint4* vrow = reinterpret_cast<uint4*>(v_ptr + s * KV_BYTES + group * HALF_BYTES + row * 128);
 #pragma unroll
-          for (int hh = 0; hh < HALVES; ++hh) {
-            uint4* vrow = reinterpret_cast<uint4*>(v_ptr + s * KV_BYTES + hh * HALF_BYTES + row * 128);
-#pragma unroll
-            for (int q8 = 0; q8 < 8; ++q8) vrow[q8] = make_uint4(0u, 0u, 0u, 0u);
-          }
+          for (int q8 = 0; q8 < 8; ++q8) vrow[q8] = make_uint4(0u, 0u, 0u, 0u);
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0 && ok) mbar_arrive(p_full);
       // the tile before: its PV into the running row, with the scale its own P was made with
-      if (it > 0) {
-        if (!take_pv(it - 1)) {
-          ok = false;
-          break;
-        }
-      }
+      if (ok && it > 0 && !take_pv(it - 1)) ok = false;
       l_run = fmaf(l_run, alpha, psum);
       alpha_pending = alpha;
       m_run = m_new;
     }
     if (ok && n_tiles > 0) ok = take_pv(n_tiles - 1);
+    // the row's sum is that of its two threads
+    row_max[group * 128 + row] = l_run;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const float l_row = group == 0 ? l_run + row_max[128 + row] : row_max[row] + l_run;
     if (!ok) {
       *failed = 1;
       if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 840 + quad);
     } else if (row < ntok) {
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      __nv_bfloat16* dst = out + ((int64_t)(tok0 + row) * nq + h) * D;
+      const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+      __nv_bfloat16* dst = out + ((int64_t)(tok0 + row) * nq + h) * D + group * HD;
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
+      for (int c = 0; c < HD; c += 8) {
         uint4 v;
         v.x = pack_bf16(o[c] * inv, o[c + 1] * inv);
         v.y = pack_bf16(o[c + 2] * inv, o[c + 3] * inv);
@@ -519,7 +526,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
            const int* block_table, int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
            float scale, int* err, cudaStream_t stream) {
   constexpr int KV_BYTES = HALVES * HALF_BYTES;
-  const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 2 * HALF_BYTES + 256 + 1024;
+  const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 2 * HALF_BYTES + 256 + 2048 + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -528,7 +535,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
     configured = true;
   }
   dim3 grid(nq, n_work);
-  ls_launch(attention_prefill_tc_kernel<HALVES>, grid, 192, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work,
+  ls_launch(attention_prefill_tc_kernel<HALVES>, grid, 320, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work,
             block_table, table_stride, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
   return ls_launch_status();
 }
