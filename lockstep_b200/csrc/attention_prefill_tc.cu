@@ -14,8 +14,8 @@
 //                 as it lies in the cache (MN-major), into tensor memory, and the
 //                 threads add it to their running row  O = O * alpha + PV
 //
-// Ten warps: warp 0 fetches Q once and key/value tiles into two stages each (the
-// pages of a tile are looked up by its lanes in parallel), warp 1 issues the MMAs
+// Eleven warps: warp 0 fetches Q once and the key tiles, warp 10 the value tiles, into
+// two stages each (a lane per page of a tile: look-up and TMA box), warp 1 issues the MMAs
 // (S of the next tile before PV of this one, so the tensor cores work while the
 // softmax runs; S has two buffers in tensor memory, PV two), warps 2..9 are the
 // softmax, two threads per row: one has the first 64 keys of a tile and the first
@@ -149,7 +149,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // HALVES = d / 64.  Shared memory: Q [HALVES][128 rows][128 B]; two stages of K and of V
 // [HALVES][128 keys][128 B]; P [2][128 rows][128 B] (keys 0..63, 64..127); barriers.
 template <int HALVES>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(352, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             __nv_bfloat16* __restrict__ out, const int* __restrict__ work,
                             const int* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size,
@@ -228,9 +228,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t tmem_base = *tmem_slot;
   ls_dependency_wait();                 // q and this step's keys and values come from the kernel before
 
-  if (warp == 0) {
-    // ---- producer ----
-    if (lane == 0) {
+  if (warp == 0 || warp == 10) {
+    // ---- producers ----
+    if (warp == 0 && lane == 0) {
       mbar_expect_tx(q_full, KV_BYTES);
 #pragma unroll
       for (int hh = 0; hh < HALVES; ++hh) tma_load_2d(q_smem + hh * HALF_BYTES, &map_q, h * D + hh * 64, tok0, q_full);
@@ -252,43 +252,34 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       return page;
     };
+    // warp 0 fetches the key tiles, warp 10 the value tiles: a key stage is free two tiles
+    // before the value stage of the same tile, and neither waits for the other's
+    const bool keys = warp == 0;
+    uint64_t* free_bar = keys ? k_free : v_free;
+    uint64_t* full_bar = keys ? k_full : v_full;
+    const uint32_t dst_base = keys ? k_smem : v_smem;
     int page = lookup(0);
     for (int it = 0; it < n_tiles; ++it) {
       const int s = it & 1;
       const uint32_t phase = (uint32_t)(it >> 1) & 1u;
       const int c0 = (tile_first + it) * BLOCK_N;
       const int page_next = lookup(it + 1);
-      // keys of the stage first: they are free (S of two tiles ago) before the values (its PV)
-      bool ok = *failed == 0 && mbar_wait(&k_free[s], phase ^ 1u);
+      bool ok = *failed == 0 && mbar_wait(&free_bar[s], phase ^ 1u);
       ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
-        if (lane == 0) mbar_expect_tx(&k_full[s], KV_BYTES);
-        __syncwarp();
-        if (lane < boxes) {
-          const int in_page = ((c0 + lane * rows_per_box) % page_size) / rows_per_box * rows_per_box;
-          const int y_k = ((page * 2 + 0) * nkv + kvh) * page_size + in_page;
-#pragma unroll
-          for (int hh = 0; hh < HALVES; ++hh)
-            tma_load_2d(k_smem + (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + lane * rows_per_box * 128), &map_kv,
-                        hh * 64, y_k, &k_full[s]);
-        }
-        ok = mbar_wait(&v_free[s], phase ^ 1u);
-        ok = __all_sync(0xffffffffu, ok);
-      }
       if (!ok) {
         *failed = 1;
         if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 800 + s);
         break;
       }
-      if (lane == 0) mbar_expect_tx(&v_full[s], KV_BYTES);
+      if (lane == 0) mbar_expect_tx(&full_bar[s], KV_BYTES);
       __syncwarp();
       if (lane < boxes) {
         const int in_page = ((c0 + lane * rows_per_box) % page_size) / rows_per_box * rows_per_box;
-        const int y_v = ((page * 2 + 1) * nkv + kvh) * page_size + in_page;
+        const int y = ((page * 2 + (keys ? 0 : 1)) * nkv + kvh) * page_size + in_page;
 #pragma unroll
         for (int hh = 0; hh < HALVES; ++hh)
-          tma_load_2d(v_smem + (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + lane * rows_per_box * 128), &map_kv,
-                      hh * 64, y_v, &v_full[s]);
+          tma_load_2d(dst_base + (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + lane * rows_per_box * 128), &map_kv,
+                      hh * 64, y, &full_bar[s]);
       }
       page = page_next;
     }
@@ -340,7 +331,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 820);
       }
     }
-  } else {
+  } else if (warp < 10) {
     // ---- softmax: two threads per row (a token, lane `row` of tensor memory): the thread of
     // group 0 (warps 2..5) has keys 0..63 of a tile and the first half of the head's
     // dimensions, the thread of group 1 (warps 6..9) keys 64..127 and the second half ----
@@ -535,7 +526,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
     configured = true;
   }
   dim3 grid(nq, n_work);
-  ls_launch(attention_prefill_tc_kernel<HALVES>, grid, 320, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work,
+  ls_launch(attention_prefill_tc_kernel<HALVES>, grid, 352, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work,
             block_table, table_stride, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
   return ls_launch_status();
 }
