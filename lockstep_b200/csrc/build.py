@@ -32,7 +32,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 # others hold the tensor-core kernels for the sizes they are specialised for.
 LIBRARIES: dict[str, list[str]] = {
     "core": ["elementwise.cu", "gemm_simt.cu", "attention_simt.cu", "sampling.cu"],
-    "tc": ["gemm_tc.cu", "attention_decode_mma.cu", "attention_prefill_mma.cu", "attention_prefill_tc.cu"],
+    "tc": ["gemm_tc.cu", "attention_decode_mma.cu", "attention_prefill_tc.cu"],
 }
 
 _HEADERS = ["common.cuh", "no_alloc.h", "rope.cuh", "attention_fold.cuh"]

@@ -74,12 +74,9 @@ _SIGNATURES["tc"] = {
     "ls_gemm_tc_k_shares": [c_int, c_int],
     "ls_attention_decode_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
-    "ls_attention_prefill_tile_tokens": [],
     "ls_attention_prefill_tc_tile_tokens": [],
     "ls_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                 c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
-    "ls_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                 c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "ls_gemm_nt_tc_qkv_heads": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int, c_float, c_void_p,
                                 c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -300,27 +297,6 @@ def attention_decode_mma(q, pages, part_acc, part_ml, work, n_work, block_table,
     if status == -2:
         return False
     _check(status, "attention_decode_mma")
-    return True
-
-
-def attention_prefill_tile_tokens() -> int:
-    return int(library("tc").ls_attention_prefill_tile_tokens())
-
-
-def attention_prefill_mma(q, pages, out, work, n_work, block_table, nq, nkv, d, window, scale, err) -> bool:
-    """Attention of prompt portions on mma.sync with TMA-fed pages
-    (csrc/attention_prefill_mma.cu): bfloat16, head size 64 or 128, work items of up to
-    64 tokens.  Returns False (nothing launched) for anything else."""
-    if q.dtype != torch.bfloat16 or not USE_TENSOR_CORES[0]:
-        return False
-    status = library("tc").ls_attention_prefill_mma(
-        _dev(q, "q"), _dev(pages, "pages", q.dtype), _dev(out, "out", q.dtype),
-        _dev(work, "work", torch.int32), n_work, _dev(block_table, "block_table", torch.int32),
-        block_table.shape[-1], nq, nkv, d, pages.shape[3], pages.shape[0], int(window), float(scale),
-        _dev(err, "err", torch.int32), _stream())
-    if status == -2:
-        return False
-    _check(status, "attention_prefill_mma")
     return True
 
 

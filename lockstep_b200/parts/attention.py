@@ -88,15 +88,9 @@ class GQAttention(Mixer):
             K.qk_norm_rope_store(qkv, *heads)
         attn = torch.empty((t, nq * d), dtype=dt, device=dev)
         plan, done = None, False
-        import os
-        if not self.exact and d in (64, 128) and os.environ.get("LS_PREFILL", "tc") == "tc":
+        if not self.exact and d in (64, 128):
             plan = ctx.attention_plan(self.window, K.attention_prefill_tc_tile_tokens())
             done = not plan.n_tile or K.attention_prefill_tc(
-                q, cache.pages, attn, plan.tile_work, plan.n_tile, cache.block_table, nq, nkv, d,
-                self.window, self.scale, self.rt.err)
-        if not done and not self.exact and d in (64, 128):
-            plan = ctx.attention_plan(self.window, K.attention_prefill_tile_tokens())
-            done = not plan.n_tile or K.attention_prefill_mma(
                 q, cache.pages, attn, plan.tile_work, plan.n_tile, cache.block_table, nq, nkv, d,
                 self.window, self.scale, self.rt.err)
         if not done:

@@ -166,19 +166,16 @@ def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel):
     split = k.attention_split_size()
     table = torch.full((2, 256), -1, dtype=torch.int32)
     table[1, :len(table_row)] = torch.tensor(table_row, dtype=torch.int32)
-    prefill_mma = decode_kernel in ("prefill_mma", "prefill_tc")
-    tile_tokens = {"prefill_mma": 64, "prefill_tc": 128}.get(decode_kernel, 16)
+    prefill_tc = decode_kernel == "prefill_tc"
+    tile_tokens = 128 if prefill_tc else 16
     tile, sp, comb, n_slots = plan_attention([(1, 0, start, n)], window, split, tile_tokens)
     D = dev()
     err = k.new_error_word(D)
     qd, pd, td = q.reshape(n, nq * d).contiguous().to(D), pages.to(D), table.to(D)
     out = torch.empty(n, nq * d, dtype=q.dtype, device=D)
-    if len(tile) and decode_kernel == "prefill_tc":
+    if len(tile) and prefill_tc:
         assert k.attention_prefill_tc(qd, pd, out, torch.from_numpy(tile).to(D), len(tile), td, nq, nkv, d,
                                       window, scale, err)
-    elif len(tile) and prefill_mma:
-        assert k.attention_prefill_mma(qd, pd, out, torch.from_numpy(tile).to(D), len(tile), td, nq, nkv, d,
-                                       window, scale, err)
     elif len(tile):
         k.attention_tile(qd, pd, out, None, None, torch.from_numpy(tile).to(D), len(tile), td, nq, nkv, d,
                          window, scale, err)
@@ -190,7 +187,7 @@ def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel):
         if decode_kernel == "mma":
             done = k.attention_decode_mma(qd, pd, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err)
             assert done
-        elif decode_kernel and not prefill_mma:
+        elif decode_kernel and not prefill_tc:
             done = k.attention_decode(qd, pd, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err)
             assert done
         if not done:
@@ -222,8 +219,8 @@ def test_attention_prefix_portion_and_decode(dtype, nq, nkv, d, page, window):
     assert (got - want[550:]).abs().max() <= bound
     if dtype == torch.bfloat16 and d in (64, 128):
         # the tensor-core kernel: a whole prompt, a ragged tail, two tokens at a tile's edge
-        # (one on mma.sync with 64-token tiles, one on tcgen05 with 128-token tiles)
-        for kernel in ("prefill_mma", "prefill_tc"):
+        # (tcgen05, 128-token tiles)
+        for kernel in ("prefill_tc",):
             for lo, hi in [(0, 700), (550, 700), (0, 1), (63, 65), (640, 642), (100, 229), (127, 130), (0, 129)]:
                 got = run_attention(k, q[lo:hi], pages, ids, lo, window, scale, kernel)
                 assert (got - want[lo:hi]).abs().max() <= bound, (kernel, lo, hi)
