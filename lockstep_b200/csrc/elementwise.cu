@@ -130,7 +130,7 @@ LS_API int ls_rmsnorm(const float* x, const int* row_index, const void* gain, in
 
 // --------------------------------------------------------------------------
 // Per-head RMSNorm (optional) + rotary position encoding (optional) of q and k,
-// and the write of k and v into the paged cache.  One warp per (token, head).
+// and the write of k and v into the paged cache.  A block per token, its warps over the heads.
 //
 // qkv:   [tokens, (nq + 2*nkv) * d]   projections of this step's tokens
 // q_out: [tokens, nq * d]
@@ -140,13 +140,24 @@ LS_API int ls_rmsnorm(const float* x, const int* row_index, const void* gain, in
 template <typename T>
 __global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, const LsQkvStore args, int tokens, int* err) {
   ls_dependency_sync();
-  const int warps_per_block = blockDim.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const int head = blockIdx.y * warps_per_block + (threadIdx.x >> 5);
+  // the token's projections come into shared memory in 16-byte pieces; then a warp per head
+  extern __shared__ uint4 row_smem[];
   const int t = blockIdx.x;
   const int heads_total = args.nq + 2 * args.nkv;
-  if (head >= heads_total) return;
-  ls_qkv_head_store<T>(args, qkv + ((int64_t)t * heads_total + head) * args.d, t, head, lane, err);
+  const int row_elems = heads_total * args.d;
+  const T* row = qkv + (int64_t)t * row_elems;
+  constexpr int PER = 16 / (int)sizeof(T);
+  if ((row_elems % PER) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    for (int i = threadIdx.x; i < row_elems / PER; i += blockDim.x)
+      row_smem[i] = reinterpret_cast<const uint4*>(row)[i];
+  } else {
+    T* dst = reinterpret_cast<T*>(row_smem);
+    for (int i = threadIdx.x; i < row_elems; i += blockDim.x) dst[i] = row[i];
+  }
+  __syncthreads();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int head = warp; head < heads_total; head += warps)
+    ls_qkv_head_store<T>(args, reinterpret_cast<const T*>(row_smem) + head * args.d, t, head, lane, err);
 }
 
 LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int dtype,
@@ -160,8 +171,23 @@ LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int 
   if (tokens <= 0) return 0;
   if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return LS_E_SIZE;
   const int heads = nq + 2 * nkv;
-  const int warps = 4;
-  dim3 grid(tokens, (heads + warps - 1) / warps);
+  const int warps = heads < 8 ? heads : 8;
+  const size_t smem = (size_t)heads * d * (dtype == LS_F32 ? 4 : 2);
+  if (smem > 200 * 1024) return LS_E_SIZE;          // a token's projections must fit shared memory
+  if (smem > 48 * 1024) {
+    static size_t allowed_f32 = 0, allowed_bf16 = 0;
+    size_t& allowed = dtype == LS_F32 ? allowed_f32 : allowed_bf16;
+    if (smem > allowed) {
+      cudaError_t e = dtype == LS_F32
+                          ? cudaFuncSetAttribute(qk_norm_rope_store_kernel<float>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                          : cudaFuncSetAttribute(qk_norm_rope_store_kernel<__nv_bfloat16>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return LS_E_SMEM;
+      allowed = smem;
+    }
+  }
+  dim3 grid(tokens);
   if (gain_dtype != LS_F32 && gain_dtype != LS_BF16) return LS_E_DTYPE;
   LsQkvStore args;
   args.q_out = q_out;
@@ -185,9 +211,9 @@ LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int 
   args.write_cache = write_cache;
   args.eps = eps;
   if (dtype == LS_F32)
-    ls_launch(qk_norm_rope_store_kernel<float>, grid, warps * 32, 0, stream, (const float*)qkv, args, tokens, err);
+    ls_launch(qk_norm_rope_store_kernel<float>, grid, warps * 32, smem, stream, (const float*)qkv, args, tokens, err);
   else if (dtype == LS_BF16)
-    ls_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream, (const __nv_bfloat16*)qkv, args,
+    ls_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, warps * 32, smem, stream, (const __nv_bfloat16*)qkv, args,
               tokens, err);
   else
     return LS_E_DTYPE;
