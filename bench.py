@@ -191,6 +191,7 @@ def time_e2e(engine, batch, context, steps, warmup):
     dt = time.perf_counter() - t0
     produced = sum(len(r.generated) for r in reqs)
     assert produced == batch * (steps + warmup), produced
+    sched.drain()              # a step the scheduler launched ahead of its last collect
     for r in list(sched.running):
         sched.running.remove(r)
         engine.runner.close(r.uid)

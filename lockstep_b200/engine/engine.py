@@ -31,6 +31,10 @@ class Engine:
         self.runner = ModelRunner(model_dir, dtype=dtype, device=device, num_pages=num_pages,
                                   page_size=page_size, max_live=max_running, max_seq_len=max_seq_len)
         self.sampler = Sampler(self.runner.device)
+        # two pinned buffers in turn (a step may be launched before the last one is collected):
+        # sampled ids, then the two words of the device error word
+        self._pinned = [torch.zeros(max_running + 2, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._pinned_turn = 0
         self.cache = self.runner.cache
         self.config = self.runner.config
         self._options = dict(max_step_tokens=max_step_tokens, policy=policy, eos_token_ids=eos_token_ids,
@@ -49,6 +53,36 @@ class Engine:
         tokens = self.sampler.sample(logits, params)
         K.raise_on_fault(self.runner.err)
         return tokens
+
+    # run-ahead: the sampled tokens and the error word go to pinned memory by a copy that the
+    # host waits for later, and the next decode step may take the tokens on the device
+    supports_run_ahead = True
+
+    def sample_async(self, logits, params) -> dict:
+        tokens = self.sampler.sample_device(logits, params)
+        n = tokens.numel()
+        host = self._pinned[self._pinned_turn]
+        self._pinned_turn ^= 1
+        if n:
+            host[:n].copy_(tokens, non_blocking=True)
+        host[-2:].copy_(self.runner.err, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return {"tokens": tokens, "host": host, "n": n, "done": done}
+
+    def collect(self, pending) -> list[int]:
+        pending["done"].synchronize()
+        host = pending["host"]
+        code, detail = host[-2:].tolist()
+        if code != 0:
+            K.raise_on_fault(self.runner.err)
+        return host[:pending["n"]].tolist()
+
+    def can_step_ahead(self, entries) -> bool:
+        return self.runner.can_step_ahead(entries)
+
+    def step_ahead(self, entries, pending) -> torch.Tensor:
+        return self.runner.step(entries, check=False, static_logits=True, tokens_device=pending["tokens"])
 
     # -- generation -------------------------------------------------------------
     def submit(self, request: Request) -> None:

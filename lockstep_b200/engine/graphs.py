@@ -161,11 +161,16 @@ class DecodeGraphs:
         K.LAUNCHES[0] = before               # recording launches nothing
         self.graphs[key] = (graph, ctx, logits, recorded)
 
-    def replay(self, key, entries, slots) -> torch.Tensor:
+    def replay(self, key, entries, slots, tokens_device=None) -> torch.Tensor:
+        """``tokens_device`` (int32, one per entry, on the device): the step's token ids, in
+        place of the entries' own: they are copied into the graph's buffer on the stream,
+        after the host's values and before the replay."""
         from .. import kernels as K
 
         graph, ctx, logits, recorded = self.graphs[key]
         ctx.fill(entries, slots)
+        if tokens_device is not None:
+            ctx.token_ids.copy_(tokens_device, non_blocking=True)
         graph.replay()
         K.LAUNCHES[0] += recorded
         self.replays += 1

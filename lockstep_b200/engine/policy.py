@@ -20,6 +20,9 @@ class SchedulerState:
 
 class Policy:
     name = "base"
+    # True if the policy's answers for a step of decoding requests do not depend on the
+    # tokens of the step before: the scheduler may then launch that step before it has them
+    allows_run_ahead = False
 
     def admit(self, state: SchedulerState, uid: str, blocks_needed: int) -> bool:
         raise NotImplementedError
@@ -44,6 +47,7 @@ class DefaultPolicy(Policy):
     budget of the step cuts it)."""
 
     name = "default"
+    allows_run_ahead = True
 
     def __init__(self, max_running: int = 32):
         self.max_running = max_running
@@ -69,6 +73,8 @@ class FixedChunkPolicy(DefaultPolicy):
 
 class ScriptedPolicy(DefaultPolicy):
     """Portions from a cyclic plan, preemption of named requests at named steps."""
+
+    allows_run_ahead = False          # it preempts at steps it names: every step is planned
 
     def __init__(self, chunk_plan=(), preempt_at=(), max_running: int = 32):
         super().__init__(max_running)

@@ -109,13 +109,24 @@ class ModelRunner:
         return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
 
     @torch.no_grad()
-    def step(self, entries: list[StepEntry], check: bool = True, static_logits: bool = False) -> torch.Tensor:
+    def can_step_ahead(self, entries: list[StepEntry]) -> bool:
+        """True if ``step`` can take the token ids of these single-token entries from the
+        device: the step is a recorded one."""
+        if self.graphs is None or not all(len(e.tokens) == 1 and e.want == [0] for e in entries):
+            return False
+        return self.graphs.ready((len(entries), self.graphs.capacity_for(entries)))
+
+    @torch.no_grad()
+    def step(self, entries: list[StepEntry], check: bool = True, static_logits: bool = False,
+             tokens_device: torch.Tensor | None = None) -> torch.Tensor:
         """Run one batch; returns float32 logits [wanted, vocab] in the order of
         the entries and of their ``want`` lists.  Every entry's request must be
         open and ``start`` must equal the number of tokens it already holds.
         ``check=False`` skips reading the device error word (no synchronisation);
         ``static_logits=True`` lets a replayed decode step return its graph's own
-        output buffer, which the next replay overwrites."""
+        output buffer, which the next replay overwrites.  ``tokens_device``: the token
+        ids of a recorded step (``can_step_ahead``), taken on the device instead of from
+        the entries."""
         if not entries:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         seen = set()
@@ -135,14 +146,18 @@ class ModelRunner:
         if self.graphs is not None and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
             key = (len(entries), self.graphs.capacity_for(entries))
             if self.graphs.ready(key):
-                logits = self.graphs.replay(key, entries, slots)
+                logits = self.graphs.replay(key, entries, slots, tokens_device)
                 if not static_logits:
                     logits = logits.clone()
+            elif tokens_device is not None:
+                raise ValueError("token ids on the device serve recorded steps only (see can_step_ahead)")
             else:
                 # this step runs eagerly (it also warms every kernel up); later ones replay
                 logits = self.forward(StepContext(entries, slots, self.device, self.err, self.split_size))
                 self.graphs.record(key)
         if logits is None:
+            if tokens_device is not None:
+                raise ValueError("token ids on the device serve recorded steps only (see can_step_ahead)")
             logits = self.forward(StepContext(entries, slots, self.device, self.err, self.split_size))
         for e in entries:
             self.cache.advance(e.uid, e.start + len(e.tokens))

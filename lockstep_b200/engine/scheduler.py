@@ -67,7 +67,17 @@ class Scheduler:
     """``backend`` gives ``cache`` (a CacheManager), ``step(entries) -> logits``
     and ``sample(logits, params) -> tokens``; ``ModelRunner`` with a ``Sampler``
     is one, a host-side fake is another (the scheduler's decisions are tested
-    without a device)."""
+    without a device).
+
+    A backend with ``supports_run_ahead`` also gives ``sample_async(logits, params) ->
+    pending`` (tokens stay on the device, their copy to the host is under way),
+    ``collect(pending) -> tokens``, ``can_step_ahead(entries)`` and ``step_ahead(entries,
+    pending) -> logits`` (a decode step whose token ids are the pending ones, taken on the
+    device).  While every running request only decodes and none can end by its token count,
+    the scheduler then launches step n + 1 before it waits for the tokens of step n, so the
+    host's share of a step runs beside the device's.  A request that ends on an end token
+    at step n has one more token computed at step n + 1, which is dropped; the other rows of
+    that step do not depend on it."""
 
     def __init__(self, backend, max_step_tokens: int = 2048, policy: Policy | None = None,
                  eos_token_ids=None, audit: bool = False, enable_prefix_cache: bool = False,
@@ -86,7 +96,9 @@ class Scheduler:
         self.step_index = 0
         self.events: list[tuple] = []          # (step, event, uid, detail)
         self.stats = {"preemptions": 0, "evictions": 0, "steps": 0, "tokens_run": 0,
-                      "mixed_steps": 0, "budget_cuts": 0}
+                      "mixed_steps": 0, "budget_cuts": 0, "launched_ahead": 0}
+        self._ahead = None                     # a launched step whose tokens have not been collected
+        self._step_limit = 1 << 62
         self.prefix = None
         if enable_prefix_cache:
             if len(self.cache.paged) != 1 or self.cache.paged[0].window or self.cache.states:
@@ -181,8 +193,26 @@ class Scheduler:
 
     # -- one step ---------------------------------------------------------------
     def step(self) -> bool:
+        if self._ahead is not None:
+            launched, self._ahead = self._ahead, None
+        else:
+            launched = self._plan_and_launch()
+            if launched is None:
+                return False
+            if launched is True:
+                return True
+        # the next step goes out before this one's tokens are waited for, where that is safe
+        if self._can_run_ahead(launched):
+            self._ahead = self._launch_ahead(launched)
+        self._collect(launched)
+        self.step_index += 1
+        return True
+
+    def _plan_and_launch(self):
+        """Admission, preemption and the plan of one step, and its launch.  None: nothing is
+        queued; True: a step went by without work for the device; else the launched step."""
         if not self.waiting and not self.running:
-            return False
+            return None
         state = self._state()
         for request in list(self.waiting):
             need = self._pages_for(request.total_tokens() + 1)
@@ -229,18 +259,25 @@ class Scheduler:
         if not planned:
             self.step_index += 1
             return True
+        return self._launch(planned)
 
+    def _launch(self, planned, ahead_of=None):
+        """Run the planned portions on the backend and start sampling; the tokens are taken
+        in ``_collect``.  ``ahead_of``: the launched step whose tokens this one feeds on."""
         entries = []
         for request, take in planned:
             start = request.kv_len
-            last = start + take == request.total_tokens()
-            entries.append(StepEntry(uid=request.uid, tokens=request.tokens(start, start + take), start=start,
-                                     want=[take - 1] if last else []))
+            last = ahead_of is not None or start + take == request.total_tokens()
+            tokens = [0] if ahead_of is not None else request.tokens(start, start + take)
+            entries.append(StepEntry(uid=request.uid, tokens=tokens, start=start, want=[take - 1] if last else []))
             self._event("decode" if take == 1 and last else "chunk", request.uid, (start, take))
         kinds = {len(e.tokens) == 1 for e in entries}
         if len(kinds) == 2:
             self.stats["mixed_steps"] += 1
-        logits = self.backend.step(entries)
+        if ahead_of is not None:
+            logits = self.backend.step_ahead(entries, ahead_of["pending"])
+        else:
+            logits = self.backend.step(entries)
         self.stats["steps"] += 1
         self.stats["tokens_run"] += sum(len(e.tokens) for e in entries)
 
@@ -248,13 +285,28 @@ class Scheduler:
         for (request, take), e in zip(planned, entries):
             request.kv_len = e.start + take
             if e.want:
+                # the position of the last token fed: the last context position
                 params.append(SamplingParams(uid=request.uid, seed=request.seed,
                                              temperature=request.temperature, top_p=request.top_p,
-                                             position=request.total_tokens() - 1))
+                                             position=e.start + take - 1))
                 owners.append(request)
-        tokens = self.backend.sample(logits, params)     # also where the backend reports device faults
-        for request, token in zip(owners, tokens):
+        launched = {"planned": planned, "owners": owners, "params": params, "logits": logits, "pending": None}
+        if getattr(self.backend, "supports_run_ahead", False):
+            launched["pending"] = self.backend.sample_async(logits, params)
+        return launched
+
+    def _collect(self, launched) -> None:
+        """Take the tokens of a launched step, append them, finish what has ended."""
+        if launched["pending"] is not None:
+            tokens = self.backend.collect(launched["pending"])
+        else:
+            tokens = self.backend.sample(launched["logits"], launched["params"])   # also reports device faults
+        owners = []
+        for request, token in zip(launched["owners"], tokens):
+            if request.finished or request not in self.running:
+                continue                      # ended on an end token while this step was under way
             request.generated.append(int(token))
+            owners.append(request)
 
         if self.audit_enabled:
             self.cache.audit()
@@ -270,12 +322,48 @@ class Scheduler:
                                        group.seqs[request.uid].pages, group)
                 self.cache.release(request.uid)
                 self._event("finish", request.uid)
-        self.step_index += 1
-        return True
+
+    def _can_run_ahead(self, launched) -> bool:
+        """True if the step after ``launched`` is known now: the same requests, one more token
+        each, whatever the tokens turn out to be (but for an end token, see the class)."""
+        if launched["pending"] is None or self.waiting or self.audit_enabled or self.prefix is not None:
+            return False
+        if not self.policy.allows_run_ahead or self.step_index + 2 > self._step_limit:
+            return False
+        planned = launched["planned"]
+        if len(launched["owners"]) != len(planned) or len(planned) != len(self.running):
+            return False
+        for request, take in planned:
+            # after the token under way it must still want another, and fit without making room
+            if take != 1 or len(request.generated) + 2 > request.max_new_tokens:
+                return False
+            if request.kv_len + 1 > self.cache.max_seq_len or not self.cache.can_reserve(request.uid, request.kv_len + 1):
+                return False
+        entries = [StepEntry(uid=r.uid, tokens=[0], start=r.kv_len, want=[0]) for r, _ in planned]
+        return self.backend.can_step_ahead(entries)
+
+    def _launch_ahead(self, launched):
+        planned = [(request, 1) for request, _ in launched["planned"]]
+        for request, _ in planned:
+            self.cache.reserve(request.uid, request.kv_len + 1)
+        self.stats["launched_ahead"] += 1
+        return self._launch(planned, ahead_of=launched)
+
+    def drain(self) -> None:
+        """Collect a step that was launched ahead (its tokens are appended)."""
+        if self._ahead is not None:
+            launched, self._ahead = self._ahead, None
+            self._collect(launched)
+            self.step_index += 1
 
     def run(self, max_steps: int = 1 << 30) -> dict[str, list[int]]:
-        while self.step_index < max_steps and self.step():
-            pass
+        self._step_limit = max_steps
+        try:
+            while self.step_index < max_steps and self.step():
+                pass
+            self.drain()
+        finally:
+            self._step_limit = 1 << 62
         if self.audit_enabled:
             self.cache.audit()
         return {r.uid: list(r.generated) for r in self.done}

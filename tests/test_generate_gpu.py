@@ -116,3 +116,40 @@ def test_a_fault_in_a_kernel_is_reported(tmp_path):
     runner.close("a")
     runner.open("b")                     # the engine stays usable
     assert runner.step([StepEntry("b", [1, 2], 0, [1])]).shape == (1, 256)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_give_the_same_tokens(tmp_path, dtype):
+    """Decode steps launched before the tokens of the step before are on the host (their ids
+    are taken on the device) against steps planned one by one: greedy and sampled requests
+    side by side, one of them ending on an end token while the next step is under way."""
+    from lockstep_b200 import Engine, Request
+
+    folder = H.make_model_folder(tmp_path, H.TINY_B, seed=31, dtype=dtype)
+    prompts = {f"a{i}": H.random_tokens(n, 500, 70 + i) for i, n in enumerate([6, 21, 40])}
+
+    def requests(new):
+        return [Request(uid=u, prompt=p, seed=5, max_new_tokens=new, temperature=0.8 if u == "a1" else 0.0,
+                        top_p=0.9) for u, p in prompts.items()]
+
+    def run(eos, **kw):
+        engine = Engine(folder, dtype=dtype, num_pages=48, page_size=H.PAGE_B, max_running=4,
+                        eos_token_ids=eos, **kw)
+        out = engine.generate(requests(40))
+        assert engine.cache.free_pages() == engine.cache.total_pages()
+        return out, engine.scheduler.stats["launched_ahead"]
+
+    one_by_one, ahead = run(None, audit=True)          # the audit after every step rules run-ahead out
+    assert ahead == 0
+    free, ahead = run(None)
+    assert ahead > 20 and free == one_by_one
+    check_tokens(folder, prompts["a0"], free["a0"], dtype)
+    check_tokens(folder, prompts["a1"], free["a1"][:12], dtype,
+                 sampling={"seed": 5, "uid": "a1", "top_p": 0.9, "temperature": 0.8}) if dtype == "float32" else None
+    # an end token in the middle of a0's tokens
+    eos = one_by_one["a0"][17]
+    cut = one_by_one["a0"][:one_by_one["a0"].index(eos) + 1]
+    ended, ahead = run([eos])
+    assert ahead > 0 and ended["a0"] == cut
+    planned, _ = run([eos], audit=True)
+    assert ended == planned

@@ -206,3 +206,100 @@ def test_windowed_group_frees_pages_while_decoding():
         run([Request("a", list(range(30)), max_new_tokens=60)], pages=8, page=4, window=12, seq=128,
             max_step_tokens=64)
     assert sched.cache.reused_pages() > 0
+
+
+# -- run-ahead: the next decode step is launched before the last one's tokens are collected ----
+
+class FakeAsyncBackend(FakeBackend):
+    """A backend whose tokens "stay on the device": ``sample_async`` works them out from the
+    tokens that were really fed (the fake's own history), ``step_ahead`` feeds them to the next
+    step without the scheduler having seen them, ``collect`` hands them over."""
+
+    supports_run_ahead = True
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.ahead_steps = 0
+        self.uncollected = 0
+
+    def sample_async(self, logits, params):
+        self.sampled.extend(params)
+        for p in params:                       # the position the scheduler names is the last one fed
+            assert p.position == len(self.history[p.uid]) - 1
+        self.uncollected += 1
+        return {"uids": [p.uid for p in params], "tokens": [next_token(self.history[p.uid]) for p in params]}
+
+    def collect(self, pending):
+        self.uncollected -= 1
+        return list(pending["tokens"])
+
+    def can_step_ahead(self, entries):
+        return all(len(e.tokens) == 1 and e.want == [0] for e in entries)
+
+    def step_ahead(self, entries, pending):
+        assert self.uncollected == 1           # the step it feeds on is still under way
+        assert [e.uid for e in entries] == pending["uids"]
+        for e, t in zip(entries, pending["tokens"]):
+            assert e.tokens == [0]
+            e.tokens = [t]
+        self.ahead_steps += 1
+        return self.step(entries)
+
+
+def run_ahead(requests, late=(), **kw):
+    backend_kw = {k: kw.pop(k) for k in ("pages", "page", "live", "seq", "window") if k in kw}
+    backend = FakeAsyncBackend(**backend_kw)
+    sched = Scheduler(backend, **kw)
+    for r in requests:
+        sched.submit(r)
+    late = dict(late)
+    while sched.step():
+        for r in late.pop(sched.step_index, []):
+            sched.submit(r)
+    sched.drain()
+    assert backend.uncollected == 0
+    return {r.uid: list(r.generated) for r in sched.done}, sched, backend
+
+
+def test_run_ahead_gives_the_same_tokens():
+    reqs = [Request(uid=f"r{i}", prompt=[3 + i, 5, 8 + i] * (i + 1), max_new_tokens=4 + 3 * i) for i in range(4)]
+    out, sched, backend = run_ahead(reqs)
+    for r in reqs:
+        assert out[r.uid] == expected(r.prompt, r.max_new_tokens)
+    assert backend.ahead_steps > 0
+    # no step after a request's last token: the count of tokens decides, and it is known ahead
+    assert sched.stats["tokens_run"] == sum(len(r.prompt) + r.max_new_tokens - 1 for r in reqs)
+    sched.cache.audit()
+    assert sched.cache.free_pages() == sched.cache.total_pages()
+
+
+def test_run_ahead_drops_the_token_after_an_end_token():
+    prompt = [4, 9, 2, 7]
+    full = expected(prompt, 40)
+    eos = full[5]
+    want = expected(prompt, 40, eos=(eos,))
+    assert len(want) < 40
+    other = Request(uid="other", prompt=[1, 2, 3], max_new_tokens=30)
+    reqs = [Request(uid="ends", prompt=prompt, max_new_tokens=40), other]
+    out, sched, backend = run_ahead(reqs, eos_token_ids=[eos])
+    assert out["ends"] == want
+    assert out["other"] == expected(other.prompt, 30, eos=(eos,))
+    assert backend.ahead_steps > 0
+    sched.cache.audit()
+    assert sched.cache.free_pages() == sched.cache.total_pages()
+
+
+def test_run_ahead_stops_for_arrivals_and_for_pages():
+    first = Request(uid="a", prompt=[5, 6, 7], max_new_tokens=20)
+    late = Request(uid="b", prompt=[9, 8, 7, 6, 5], max_new_tokens=6)
+    out, sched, backend = run_ahead([first], late={6: [late]})
+    assert out["a"] == expected(first.prompt, 20) and out["b"] == expected(late.prompt, 6)
+    # b's prompt ran beside one of a's decoded tokens: that step was planned, not launched ahead
+    assert any(len(step) == 2 and {n for _, _, n in step} == {1, 5} for step in backend.steps)
+    # so few pages that a request is preempted: whatever is launched ahead, the tokens are the same
+    reqs = [Request(uid=f"p{i}", prompt=[2 + i, 3, 4, 5], max_new_tokens=12) for i in range(3)]
+    out, sched, backend = run_ahead(reqs, pages=9, page=4)
+    for r in reqs:
+        assert out[r.uid] == expected(r.prompt, 12)
+    assert sched.stats["preemptions"] > 0
+    sched.cache.audit()
