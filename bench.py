@@ -43,6 +43,15 @@ QWEN3_0_6B = {
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
     "max_position_embeddings": 40960,
 }
+# the other sizes BASELINE.json names (configs[3] and [4]); `--model` runs one of them instead
+SIZES = {
+    "qwen3-0.6b": {},
+    "qwen3-4b": {"num_hidden_layers": 36, "hidden_size": 2560, "num_attention_heads": 32,
+                 "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 9728},
+    "qwen3-8b": {"num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32,
+                 "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+                 "tie_word_embeddings": False},
+}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16
@@ -235,6 +244,8 @@ def run_ours(args):
     from lockstep_b200.weights import write_random_model
 
     cfg = dict(QWEN3_0_6B)
+    cfg.update(SIZES[args.model])
+    label = args.model.replace("qwen3", "Qwen3").upper().replace("QWEN3", "Qwen3")
     layers_full = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -278,13 +289,13 @@ def run_ours(args):
     bytes_step = step_bytes(cfg, layers, args.batch, CONTEXT)
     achieved = bytes_step / (ms * 1e-3) / 1e9
     line = {
-        "metric": "decode tokens/s, Qwen3-0.6B sizes, batch 8, context 4096",
+        "metric": f"decode tokens/s, {label} sizes, batch {args.batch}, context {CONTEXT}",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
         "config": {
-            "model": "Qwen3-0.6B sizes, random weights N(0,0.02)", "layers": layers,
+            "model": f"{label} sizes, random weights N(0,0.02)", "layers": layers,
             "layers_of_model": layers_full, "hidden": cfg["hidden_size"],
             "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
@@ -316,6 +327,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0,
                     help="run fewer layers than the model has (named in config)")
+    ap.add_argument("--model", default="qwen3-0.6b", choices=sorted(SIZES),
+                    help="layer sizes (the default is the configuration the headline is quoted on)")
     ap.add_argument("--quick", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="time only this part and print a short line (for profiling a small case)")

@@ -32,19 +32,31 @@
 #include "common.cuh"
 #include "rope.cuh"
 
-// Into how many shares K is cut for a weight of N rows and depth K: a function
-// of the weight's shape alone.  One share unless the weight has fewer than 96
-// row tiles; then enough shares to give about 128 blocks, each share at least
-// four 64-element blocks deep, at most 8 (the portable cluster size).
+// Into how many shares K is cut for a weight of N rows and depth K: a function of the
+// weight's shape alone.  With few tokens a block streams one share of one row tile, a block
+// to an SM, and the device takes the blocks in rounds of 148 (its number of SMs: a constant
+// of this rule and not a query, so that the sums are the same on any device).  A round costs
+// the share's depth in 64-element blocks plus a fixed part worth 22 of them (the chain of
+// latencies of a block and the token rows it norms again; measured on the gate/up weights of
+// the 4B and 8B sizes, where 10 chose three shares and lost 14 us a layer at 8B).  The rule
+// takes the number of shares (each at least four blocks deep, at most 8, the portable cluster
+// size) with the smallest rounds x (depth / shares + 22), the fewest shares among equals.
 LS_API int ls_gemm_tc_k_shares(int N, int K) {
-  const int tiles = (N + 127) / 128;
-  const int kb = (K + 63) / 64;
-  if (tiles >= 96) return 1;
-  int want = (128 + tiles - 1) / tiles;
-  if (want > 8) want = 8;
-  int by_depth = kb / 4;
-  if (by_depth < 1) by_depth = 1;
-  return want < by_depth ? want : by_depth;
+  const long long tiles = (N + 127) / 128;
+  const long long kb = (K + 63) / 64;
+  const long long fixed = 22;
+  long long most = kb / 4;
+  if (most > 8) most = 8;
+  long long best = 1;
+  long long best_cost = ((tiles + 147) / 148) * (kb + fixed);        // cost x shares, compared as cross products
+  for (long long s = 2; s <= most; ++s) {
+    const long long cost = ((tiles * s + 147) / 148) * (kb + fixed * s);
+    if (cost * best < best_cost * s) {
+      best = s;
+      best_cost = cost;
+    }
+  }
+  return (int)best;
 }
 
 namespace {

@@ -74,6 +74,9 @@ def test_k_shares_depend_on_the_weight_alone():
     assert lib.ls_gemm_tc_k_shares(1024, 3072) == 8      # down
     assert lib.ls_gemm_tc_k_shares(151936, 1024) == 1    # head
     assert lib.ls_gemm_tc_k_shares(128, 64) == 1
+    assert lib.ls_gemm_tc_k_shares(12288, 4096) == 1     # gate/up of the 8B sizes: 96 row tiles, one round
+    assert lib.ls_gemm_tc_k_shares(2560, 4096) == 7      # o of the 4B sizes: 20 row tiles, 140 blocks
+    assert lib.ls_gemm_tc_k_shares(4096, 12288) == 4     # down of the 8B sizes
 
 
 @pytest.mark.parametrize("k,n", [(1024, 640), (3072, 384)])
