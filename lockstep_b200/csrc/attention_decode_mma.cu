@@ -164,25 +164,23 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
   }
 
   // issue the loads of chunk i (first key c0): K on bar_k, V on bar_v.  Called by the whole warp.
+  // Every box is issued by a lane of its own: a thread gets one TMA instruction out about
+  // every 300 ns, whatever the box's size, so one lane issuing a chunk's up to 16 boxes would
+  // spend several microseconds on it.
   auto issue = [&](int i, int c0, bool want_k, bool want_v) {
     const uint32_t bytes = (uint32_t)(HALVES * HALF_BYTES);
     if (lane == 0) {
       if (want_k) mbar_expect_tx(bar_k, bytes);
       if (want_v) mbar_expect_tx(bar_v, bytes);
     }
-    for (int b = 0; b < boxes; ++b) {
-      const int page = __shfl_sync(0xffffffffu, my_page, i * 4 + b);
-      if (lane == 0) {
-        const int in_page = ((c0 + b * rows_per_box) % page_size) / rows_per_box * rows_per_box;
-        const int y_k = ((page * 2 + 0) * nkv + kvh) * page_size + in_page;
-        const int y_v = ((page * 2 + 1) * nkv + kvh) * page_size + in_page;
-#pragma unroll
-        for (int h = 0; h < HALVES; ++h) {
-          const uint32_t off = (uint32_t)(h * HALF_BYTES + b * rows_per_box * 128);
-          if (want_k) tma_load_2d(k_smem + off, &map, h * 64, y_k, bar_k);
-          if (want_v) tma_load_2d(v_smem + off, &map, h * 64, y_v, bar_v);
-        }
-      }
+    __syncwarp();
+    const int b = lane / (2 * HALVES), h = (lane >> 1) % HALVES, is_v = lane & 1;    // this lane's box
+    const int page = __shfl_sync(0xffffffffu, my_page, i * 4 + (b < boxes ? b : 0));
+    if (b < boxes && (is_v ? want_v : want_k)) {
+      const int in_page = ((c0 + b * rows_per_box) % page_size) / rows_per_box * rows_per_box;
+      const int y = ((page * 2 + is_v) * nkv + kvh) * page_size + in_page;
+      const uint32_t off = (uint32_t)(h * HALF_BYTES + b * rows_per_box * 128);
+      tma_load_2d((is_v ? v_smem : k_smem) + off, &map, h * 64, y, is_v ? bar_v : bar_k);
     }
   };
 
@@ -251,11 +249,11 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
     __syncwarp();
     // K is consumed: fetch the next chunk's K while the softmax and PV of this one run
     const bool more = next < n_iter;
-    if (more && lane == 0) {
-      // the generic-proxy reads above are ordered before the async-proxy writes
+    if (more) {
+      // the generic-proxy reads above are ordered before the async-proxy writes (every lane issues)
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      issue(next, chunk_start(next), true, false);
     }
-    if (more) issue(next, chunk_start(next), true, false);
 
     // mask, online softmax (rows r0 and r0 + 8; columns nt * 8 + cq, +1)
     float tile_max[2] = {-CUDART_INF_F, -CUDART_INF_F};
@@ -340,7 +338,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map, const __nv_
     }
     __syncwarp();
     if (more) {
-      if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       issue(next, chunk_start(next), false, true);
     }
     parity ^= 1u;
