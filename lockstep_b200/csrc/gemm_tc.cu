@@ -659,23 +659,26 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
+    // The weights do not depend on the previous kernel; the token operand read by TMA does:
+    // the first round of the ring takes its weights before the wait and its tokens after.
+    // A stage of the first round is a lane's: a thread gets one TMA instruction out about
+    // every 300 ns, so the lanes issue side by side what one lane would issue in a row.
+    const int first_round = num_kb < stages ? num_kb : stages;
+    if (lane < first_round) {
+      const uint32_t stage = base + (uint32_t)lane * STAGE_BYTES;
+      mbar_expect_tx(&full[lane], STAGE_BYTES);
+      const int kx = (kb_begin + lane) * BK;
+      tma_load_2d(stage, &map_w, kx, n0, &full[lane]);
+      if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kx, N + n0, &full[lane]);
+    }
+    if (!NORM) {
+      ls_dependency_wait();
+      if (lane < first_round)
+        tma_load_2d(base + (uint32_t)lane * STAGE_BYTES + A_TILES * A_BYTES, &map_x, (kb_begin + lane) * BK, t0,
+                    &full[lane]);
+    }
+    __syncwarp();
     if (lane == 0) {
-      // the weights do not depend on the previous kernel; the token operand read by TMA does:
-      // the first round of the ring takes its weights before the wait and its tokens after
-      const int first_round = num_kb < stages ? num_kb : stages;
-      for (int kb = 0; kb < first_round; ++kb) {
-        const uint32_t stage = base + (uint32_t)kb * STAGE_BYTES;
-        mbar_expect_tx(&full[kb], STAGE_BYTES);
-        const int kx = (kb_begin + kb) * BK;
-        tma_load_2d(stage, &map_w, kx, n0, &full[kb]);
-        if (EPI == 2) tma_load_2d(stage + A_BYTES, &map_w, kx, N + n0, &full[kb]);
-      }
-      if (!NORM) {
-        ls_dependency_wait();
-        for (int kb = 0; kb < first_round; ++kb)
-          tma_load_2d(base + (uint32_t)kb * STAGE_BYTES + A_TILES * A_BYTES, &map_x, (kb_begin + kb) * BK, t0,
-                      &full[kb]);
-      }
       int issued = first_round;
       int s = 0;                                  // kb % stages and the parity of kb / stages, without dividing
       uint32_t phase = 1u;
