@@ -1,17 +1,20 @@
 // C[T, N] = X[T, K] * W[N, K]^T in bfloat16 on the 5th-generation tensor cores
 // (tcgen05.mma, accumulators in tensor memory, operands staged by TMA).
 //
-// Orientation: the weight tile is the MMA's M side (128 rows of W), the tokens
-// are its N side (16..256 per tile), so one orientation serves a batch of one
-// decoded token and a prompt of thousands; only the token tile's width varies
-// with T.  A block walks its share of K in ascending 64-element blocks.  Where
-// the weight gives too few tiles to occupy the device (few rows of tiles, deep
-// K), K is cut into shares run by the blocks of one thread-block cluster, and
-// the shares' partial tiles are summed in ascending share order through
-// distributed shared memory (pushed with st.async for few tokens, read after a
-// cluster barrier for more).  The number of shares is a function of the
-// weight's shape alone (ls_gemm_tc_k_shares), so an output element is the same
-// sum whatever the batch.
+// Orientation: up to 128 tokens, the weight tile is the MMA's M side (128 rows of
+// W) and the tokens are its N side (16..128 per tile), so a batch of one decoded
+// token wastes no rows of the MMA; more tokens are the M side themselves (128 a
+// tile, gemm_tc_rows_kernel), whose outputs then lie side by side in a thread.
+// Either way an output element is the same dot product, accumulated in the same
+// order, and the two give the same bits.  A block walks its share of K in
+// ascending 64-element blocks.  Where the weight gives too few tiles to occupy
+// the device (few rows of tiles, deep K) and the tokens are few, K is cut into
+// shares run by the blocks of one thread-block cluster, and the shares' partial
+// tiles are summed in ascending share order through distributed shared memory
+// (pushed with st.async for few tokens, read after a cluster barrier for more);
+// with many tokens one block walks the shares of its tile one after the other.
+// The number of shares is a function of the weight's shape alone
+// (ls_gemm_tc_k_shares), so an output element is the same sum whatever the batch.
 //
 // Roles inside a block (192 threads): warp 0 issues TMA loads into a ring of
 // shared-memory stages, warp 1 issues the MMAs and commits stages back, warps
@@ -165,6 +168,11 @@ __device__ __forceinline__ void fence_before_sync() {
 }
 __device__ __forceinline__ void fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 
 __host__ __device__ constexpr int tmem_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
@@ -920,9 +928,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 
-// EW epilogue warps: 4 (192 threads; token tiles up to 128 columns of sums per thread) or 8
-// (320 threads; the two groups of four epilogue warps split the token columns, so a tile of
-// 256 tokens fits, which halves the weight bytes read per output).
+// EW epilogue warps: 4 (192 threads; up to 128 running sums per thread) or 8 (320 threads: the
+// silu-mul epilogue at 128 tokens has 256 columns, which two groups of four warps split).
 template <int BN, int EPI, typename TC, int EW>
 __global__ void __launch_bounds__(EW == 8 ? 320 : 192, 1)
 gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -1127,6 +1134,234 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
 }
 
+// ---------------------------------------------------------------------------
+// Many tokens (more than 128): the persistent kernel with the tokens on the MMA's M side.
+// A tile is 128 tokens x FN features (256, or 128 for silu-mul whose weight tile is 128 gate
+// rows and the 128 up rows of the same features: one MMA of N = 256 makes both).  A token is
+// a lane of tensor memory and a thread of the epilogue, whose outputs for that token lie side
+// by side in memory and leave in 16-byte pieces (with the weights on the M side a thread had
+// one feature of 128 tokens and wrote 128 scattered elements, a quarter of the kernel's
+// time).  An output element is the same dot product in the same order of k as in the other
+// kernels, shares and all; the eight epilogue warps are two groups that split the features.
+// ---------------------------------------------------------------------------
+// FN: features per tile: 256, or 128 where 256 would leave SMs without a tile (and always 128
+// for silu-mul, whose stage holds 128 gate rows and 128 up rows).
+template <int EPI, int FN>
+struct RowsShape {
+  static_assert(FN == 128 || (FN == 256 && EPI != 2), "tile widths");
+  static constexpr int W_ROWS = EPI == 2 ? 256 : FN;        // weight rows per stage (MMA N)
+  static constexpr int X_BYTES = BM * BK * 2;               // 128 tokens
+  static constexpr int W_BYTES = W_ROWS * BK * 2;
+  static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;     // 48 or 32 KB
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int EPI, int FN, typename TC>
+__global__ void __launch_bounds__(320, 1)
+gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share, int shares,
+                    int tiles_t, int tiles_total, int* err) {
+  using S = RowsShape<EPI, FN>;
+  constexpr int COLS = 256;                      // columns of one accumulator region
+  constexpr int OUT = FN / 2;                    // outputs per epilogue thread (features of its group)
+  constexpr int SUMS = S::W_ROWS / 2;            // running sums per epilogue thread
+  ls_dependency_trigger();
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)S::STAGES * S::STAGE_BYTES);
+  uint64_t* full = bars;                        // [STAGES]
+  uint64_t* empty = bars + S::STAGES;           // [STAGES]
+  uint64_t* acc_full = bars + 2 * S::STAGES;    // [2] a share's accumulator is complete
+  uint64_t* acc_empty = acc_full + 2;           // [2] the epilogue has drained it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* failed = tmem_slot + 1;
+  constexpr uint32_t ACC_COLS = 512;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int r = 0; r < 2; ++r) {
+      mbar_init(&acc_full[r], 1);
+      mbar_init(&acc_empty[r], 8);
+    }
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(ACC_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  ls_dependency_wait();
+
+  // tiles are walked token-tile fastest: the blocks running at one time share a few weight tiles
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;                                 // k-blocks issued so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
+        const int t0 = (tile % tiles_t) * BM, n0 = (tile / tiles_t) * FN;
+        for (int kb = 0; kb < total_kb; ++kb, ++it) {
+          const int s = it % S::STAGES;
+          const uint32_t phase = (uint32_t)(it / S::STAGES) & 1u;
+          if (*failed || !mbar_wait(&empty[s], phase ^ 1u)) {
+            *failed = 1;
+            ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 900 + s);
+            ok = false;
+            break;
+          }
+          const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+          mbar_expect_tx(&full[s], S::STAGE_BYTES);
+          tma_load_2d(stage, &map_x, kb * BK, t0, &full[s]);
+          if (EPI == 2) {
+            tma_load_2d(stage + S::X_BYTES, &map_w, kb * BK, n0, &full[s]);                       // gate rows
+            tma_load_2d(stage + S::X_BYTES + S::W_BYTES / 2, &map_w, kb * BK, N + n0, &full[s]);  // up rows
+          } else {
+            tma_load_2d(stage + S::X_BYTES, &map_w, kb * BK, n0, &full[s]);
+          }
+        }
+      }
+      if (!ok) {
+        // wait (bounded) for the copies still in flight before the block exits
+        const int first = it > S::STAGES ? it - S::STAGES : 0;
+        for (int j = first; j < it; ++j) mbar_wait(&full[j % S::STAGES], (uint32_t)(j / S::STAGES) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BM, S::W_ROWS);
+      int it = 0, sc = 0;                         // k-blocks and shares consumed so far
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
+        for (int r = 0; r < shares && ok; ++r, ++sc) {
+          const int region = sc & 1;
+          const uint32_t acc_addr = tmem_base + (uint32_t)(region * COLS);
+          if (*failed || !mbar_wait(&acc_empty[region], ((uint32_t)(sc >> 1) & 1u) ^ 1u)) {
+            *failed = 1;
+            ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 950 + region);
+            ok = false;
+            break;
+          }
+          fence_after_sync();
+          const int kb_lo = r * kb_per_share;
+          int kb_hi = kb_lo + kb_per_share;
+          if (kb_hi > total_kb) kb_hi = total_kb;
+          for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+            const int s = it % S::STAGES;
+            const uint32_t phase = (uint32_t)(it / S::STAGES) & 1u;
+            if (!mbar_wait(&full[s], phase)) {
+              *failed = 1;
+              ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 920 + s);
+              ok = false;
+              break;
+            }
+            fence_after_sync();
+            const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+            const uint64_t adesc = smem_desc(stage), bdesc = smem_desc(stage + S::X_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma(acc_addr, adesc + 2 * k, bdesc + 2 * k, idesc, (kb == kb_lo && k == 0) ? 0u : 1u);
+            umma_commit(&empty[s]);
+          }
+          if (ok) umma_commit(&acc_full[region]);
+        }
+      }
+    }
+  } else {
+    // epilogue: warp w may touch tensor-memory lanes 32*(w%4) .. +32; this thread has token `row`
+    // of the tile and the features OUT * group .. + OUT of it (for silu-mul their gate and up sums)
+    const int quad = warp & 3;
+    const int group = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float sum[SUMS];
+    int sc = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
+      const int t = (tile % tiles_t) * BM + row, n_first = (tile / tiles_t) * FN + group * OUT;
+      for (int r = 0; r < shares; ++r, ++sc) {
+        const int region = sc & 1;
+        bool got = mbar_wait(&acc_full[region], (uint32_t)(sc >> 1) & 1u);
+        if (!got) {
+          *failed = 1;
+          if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 970 + quad);
+        }
+        ok = __all_sync(0xffffffffu, got);
+        if (!ok) break;
+        fence_after_sync();
+        // columns of the region: store/residual: this group's 128 features; silu-mul: gate columns
+        // OUT * group .. and up columns 128 + OUT * group ..
+#pragma unroll
+        for (int c0 = 0; c0 < SUMS; c0 += 32) {
+          uint32_t g[32];
+          const int col = EPI == 2 ? (c0 < OUT ? group * OUT + c0 : 128 + group * OUT + (c0 - OUT)) : group * OUT + c0;
+          tmem_ld32(lane_base + (uint32_t)(region * COLS + col), g);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[c0 + j] = (r == 0 ? 0.f : sum[c0 + j]) + __uint_as_float(g[j]);
+        }
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[region]);
+      }
+      if (ok && t < T) {
+        TC* crow = C + (int64_t)t * ldc + n_first;
+        constexpr int PER = 16 / (int)sizeof(TC);              // outputs of a 16-byte piece
+        const bool pieces = (reinterpret_cast<uintptr_t>(crow) & 15) == 0 && n_first + OUT <= N;
+#pragma unroll
+        for (int c0 = 0; c0 < OUT; c0 += PER) {
+          float v[PER];
+#pragma unroll
+          for (int j = 0; j < PER; ++j) {
+            const float a = sum[c0 + j];
+            v[j] = EPI == 2 ? a / (1.0f + expf(-a)) * sum[OUT + c0 + j] : a;
+          }
+          if (pieces) {
+            if constexpr (sizeof(TC) == 4) {
+              float4* p = reinterpret_cast<float4*>(crow + c0);
+              if (EPI == 1) {
+                const float4 old = *p;
+                v[0] += old.x; v[1] += old.y; v[2] += old.z; v[3] += old.w;
+              }
+              *p = make_float4(v[0], v[1], v[2], v[3]);
+            } else {
+              uint4 out;
+              out.x = pack2_bf16(v[0], v[1]); out.y = pack2_bf16(v[2], v[3]);
+              out.z = pack2_bf16(v[4], v[5]); out.w = pack2_bf16(v[6], v[7]);
+              *reinterpret_cast<uint4*>(crow + c0) = out;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < PER; ++j)
+              if (n_first + c0 + j < N)
+                crow[c0 + j] = ls_from_float<TC>(EPI == 1 ? ls_to_float<TC>(crow[c0 + j]) + v[j] : v[j]);
+          }
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ACC_COLS)
+                 : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                 CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -1171,11 +1406,8 @@ Plan make_plan(int T, int N, int K, int epilogue) {
   p.kb_per_share = (total_kb + want - 1) / want;
   p.shares = (total_kb + p.kb_per_share - 1) / p.kb_per_share;    // every share has work
   p.in_cluster = p.shares > 1 && T <= 128;
-  int cap = 128;                                    // cluster: the partial tile is staged in shared memory
-  if (!p.in_cluster) cap = epilogue == 2 ? 128 : 256;   // walked: running sums in registers, over one or
-                                                        // two epilogue warpgroups
-  p.bn = 16;
-  while (p.bn < T && p.bn < cap) p.bn *= 2;
+  p.bn = 16;                                        // token tile of the kernels with the weights on the M side
+  while (p.bn < T && p.bn < 128) p.bn *= 2;         // (more than 128 tokens go to the kernel with tokens as rows)
   return p;
 }
 
@@ -1295,6 +1527,51 @@ int launch_walk(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, in
   }
 }
 
+template <int EPI, int FN, typename TC>
+int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int64_t ldc,
+                const Plan& plan, int* err, cudaStream_t stream) {
+  using S = RowsShape<EPI, FN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_rows_kernel<EPI, FN, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)S::SMEM) != cudaSuccess)
+      return LS_E_SMEM;
+    configured = true;
+  }
+  const int tiles_t = (T + BM - 1) / BM, tiles_n = (N + FN - 1) / FN;
+  const int tiles = tiles_t * tiles_n;
+  const int sms = sm_count();
+  ls_launch(gemm_tc_rows_kernel<EPI, FN, TC>, tiles < sms ? tiles : sms, 320, S::SMEM, stream, mw, mx, (TC*)C, T, N,
+            K, ldc, plan.kb_per_share, plan.shares, tiles_t, tiles, err);
+  return ls_launch_status();
+}
+
+// more than 128 tokens: the kernel with the tokens on the M side
+int run_rows(const void* X, const void* W, void* C, int c_dtype, int T, int N, int K, int64_t ldx, int64_t ldw,
+             int64_t ldc, int epilogue, const Plan& plan, int* err, cudaStream_t stream) {
+  typedef __nv_bfloat16 bf16;
+  if ((ldx % 8) || ((uintptr_t)X & 15)) return LS_E_ALIGN;
+  CUtensorMap mw, mx;
+  // tiles of 256 features unless they would leave SMs without one (the tile's width changes no sum)
+  const bool wide = epilogue != 2 && ((T + BM - 1) / BM) * ((N + 255) / 256) >= sm_count();
+  if (!make_map(&mw, W, epilogue == 2 ? 2 * N : N, K, ldw, wide ? 256 : 128)) return LS_E_SIZE;
+  if (!make_map(&mx, X, T, K, ldx, BM)) return LS_E_SIZE;
+  if (epilogue == 2) {
+    if (c_dtype == LS_BF16) return launch_rows<2, 128, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+    return LS_E_DTYPE;
+  }
+  if (epilogue == 0 && c_dtype == LS_BF16)
+    return wide ? launch_rows<0, 256, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream)
+                : launch_rows<0, 128, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+  if (epilogue == 0 && c_dtype == LS_F32)
+    return wide ? launch_rows<0, 256, float>(mw, mx, C, T, N, K, ldc, plan, err, stream)
+                : launch_rows<0, 128, float>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+  if (epilogue == 1 && c_dtype == LS_F32)
+    return wide ? launch_rows<1, 256, float>(mw, mx, C, T, N, K, ldc, plan, err, stream)
+                : launch_rows<1, 128, float>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+  return LS_E_DTYPE;
+}
+
 // norm == nullptr: the token operand is read through `mx`; heads: the q/k/v epilogue's targets
 template <int BN, int EPI, typename TC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs* norm, const LsQkvStore* heads, void* C, int T,
@@ -1354,6 +1631,10 @@ int run(const void* X, const NormArgs* norm, const LsQkvStore* heads, const void
   const Plan plan = make_plan(T, N, K, epilogue);
   const int bn = plan.bn;
   if (epilogue == 3 && (!plan.in_cluster || bn > 32)) return LS_E_SIZE;    // before any work is done
+  if (T > 128) {
+    if (norm != nullptr || epilogue == 3) return LS_E_SIZE;
+    return run_rows(X, W, C, c_dtype, T, N, K, ldx, ldw, ldc, epilogue, plan, err, stream);
+  }
   const int w_rows = epilogue == 2 ? 2 * N : N;
   CUtensorMap mw, mx;
   if (!make_map(&mw, W, w_rows, K, ldw, BM)) return LS_E_SIZE;
@@ -1373,7 +1654,6 @@ int run(const void* X, const NormArgs* norm, const LsQkvStore* heads, const void
     case 32: return dispatch<32>(mw, mx, norm, heads, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
     case 64: return dispatch<64>(mw, mx, norm, heads, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
     case 128: return dispatch<128>(mw, mx, norm, heads, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
-    case 256: return dispatch<256>(mw, mx, norm, heads, C, c_dtype, T, N, K, ldc, epilogue, plan, err, stream);
   }
   return LS_E_SIZE;
 }
