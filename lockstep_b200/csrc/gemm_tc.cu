@@ -175,6 +175,16 @@ __device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// silu(a) * up as every epilogue of this file computes it: the exponential and the reciprocal
+// are the hardware's approximations (within 2 ulp each; the product is rounded to bfloat16 by
+// its one user).  With expf and a division the silu-mul epilogue of a 128 x 128 tile took as
+// long as the tile's MMAs.  Far below zero the result is -0 * up, as with the exact form.
+__device__ __forceinline__ float silu_mul(float a, float up) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * -1.4426950408889634f));
+  return __fdividef(a, 1.0f + e) * up;
+}
+
 __host__ __device__ constexpr int tmem_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
 template <int BN, int EPI>
@@ -195,7 +205,7 @@ __device__ __forceinline__ void epilogue_store(TC* c, float a, float up) {
   } else if (EPI == 1) {
     *c = ls_from_float<TC>(ls_to_float<TC>(*c) + a);
   } else {
-    *c = ls_from_float<TC>(a / (1.0f + expf(-a)) * up);
+    *c = ls_from_float<TC>(silu_mul(a, up));
   }
 }
 
@@ -1117,7 +1127,7 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const float a = sum[c0 + j];
                 if (EPI == 0) *c = ls_from_float<TC>(a);
                 else if (EPI == 1) *c = ls_from_float<TC>(old[j] + a);
-                else *c = ls_from_float<TC>(a / (1.0f + expf(-a)) * sum[TOK + c0 + j]);
+                else *c = ls_from_float<TC>(silu_mul(a, sum[TOK + c0 + j]));
               }
             }
           }
@@ -1146,23 +1156,94 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // ---------------------------------------------------------------------------
 // FN: features per tile: 256, or 128 where 256 would leave SMs without a tile (and always 128
 // for silu-mul, whose stage holds 128 gate rows and 128 up rows).
-template <int EPI, int FN>
+// CTAS: 1, or 2 for a pair of blocks (a cluster) on one tile of 256 tokens: each block holds its
+// own 128 tokens and half of the weight rows, one thread of the first block issues MMAs of
+// M = 256 (tcgen05 cta_group::2) that read both blocks' shared memory and write each block's
+// 128 tokens into its own tensor memory.  A block then loads 2/3 (3/4 at FN = 128) of the
+// bytes per MMA cycle, and what bounds this kernel is what L2 delivers.
+template <int EPI, int FN, int CTAS>
 struct RowsShape {
   static_assert(FN == 128 || (FN == 256 && EPI != 2), "tile widths");
-  static constexpr int W_ROWS = EPI == 2 ? 256 : FN;        // weight rows per stage (MMA N)
+  static_assert(CTAS == 1 || CTAS == 2, "a block or a pair");
+  static constexpr int W_ROWS = EPI == 2 ? 256 : FN;        // weight rows per k-block (MMA N)
+  static constexpr int W_BOXES = (EPI == 2 && CTAS == 1) ? 2 : 1;   // gate and up rows of one block come apart
   static constexpr int X_BYTES = BM * BK * 2;               // 128 tokens
-  static constexpr int W_BYTES = W_ROWS * BK * 2;
-  static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;     // 48 or 32 KB
+  static constexpr int W_BYTES = W_ROWS / CTAS * BK * 2;    // this block's part of the weight rows
+  static constexpr int KB_BYTES = X_BYTES + W_BYTES;        // a k-block: 48, 32 or 24 KB
+  static constexpr int STAGE_KB = 2;                        // k-blocks per stage: one wait and one commit for both
+  static constexpr int STAGE_BYTES = STAGE_KB * KB_BYTES;
   static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
-  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int BOXES = STAGE_KB * (1 + W_BOXES);    // TMA loads per stage, a lane each
+  static constexpr int STAGING = 8 * 4096;                  // a warp's 32 tokens x 128 bytes on their way out
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + STAGING + 1024 + 256;
 };
 
-template <int EPI, int FN, typename TC>
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// a TMA load whose bytes count on a barrier of the pair's first block
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+// true in one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+template <int CTAS>
+__device__ __forceinline__ void tma_load_2d_any(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  if constexpr (CTAS == 2) {
+    tma_load_2d_pair(dst, map, x, y, bar);
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void umma_pair(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// the barrier at this offset in both blocks of the pair gets an arrival when the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  // (not .release.cluster: that waits for the thread's earlier accesses to be seen by the whole
+  // cluster, 250 ns and more an arrival; the tensor-memory reads this orders are complete already)
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+template <int EPI, int FN, int CTAS, typename TC>
 __global__ void __launch_bounds__(320, 1)
 gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share, int shares,
                     int tiles_t, int tiles_total, int* err) {
-  using S = RowsShape<EPI, FN>;
+  using S = RowsShape<EPI, FN, CTAS>;
   constexpr int COLS = 256;                      // columns of one accumulator region
   constexpr int OUT = FN / 2;                    // outputs per epilogue thread (features of its group)
   constexpr int SUMS = S::W_ROWS / 2;            // running sums per epilogue thread
@@ -1170,17 +1251,20 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)S::STAGES * S::STAGE_BYTES);
-  uint64_t* full = bars;                        // [STAGES]
+  uint8_t* staging = aligned + (size_t)S::STAGES * S::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + S::STAGING);
+  uint64_t* full = bars;                        // [STAGES] (a pair uses those of its first block)
   uint64_t* empty = bars + S::STAGES;           // [STAGES]
   uint64_t* acc_full = bars + 2 * S::STAGES;    // [2] a share's accumulator is complete
-  uint64_t* acc_empty = acc_full + 2;           // [2] the epilogue has drained it
+  uint64_t* acc_empty = acc_full + 2;           // [2] the epilogue has drained it (a pair: the first block's)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* failed = tmem_slot + 1;
   constexpr uint32_t ACC_COLS = 512;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_kb = (K + BK - 1) / BK;
+  const int rank = CTAS == 2 ? (int)cluster_rank() : 0;     // this block's place in its pair
+  const int first_tile = blockIdx.x / CTAS, tile_step = gridDim.x / CTAS;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
@@ -1189,100 +1273,150 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     for (int r = 0; r < 2; ++r) {
       mbar_init(&acc_full[r], 1);
-      mbar_init(&acc_empty[r], 8);
+      mbar_init(&acc_empty[r], 8 * CTAS);
     }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_slot)),
-                 "r"(ACC_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (CTAS == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"(ACC_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                   "r"(ACC_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   fence_before_sync();
   __syncthreads();
+  if constexpr (CTAS == 2) {        // the peer's barriers exist before anything arrives on them
+    cluster_arrive();
+    cluster_wait();
+  }
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   ls_dependency_wait();
 
   // tiles are walked token-tile fastest: the blocks running at one time share a few weight tiles
   if (warp == 0) {
-    if (lane == 0) {
-      int it = 0;                                 // k-blocks issued so far, over all tiles
+    // A stage is up to two k-blocks of one share; each of its boxes goes out from a lane of its
+    // own (a thread gets a TMA load out only every few hundred cycles, lanes side by side scale).
+    if (lane < S::BOXES) {
+      const int half = lane / (1 + S::W_BOXES), part = lane % (1 + S::W_BOXES);   // k-block of the stage; tokens, weights
+      const uint32_t full0 = CTAS == 2 ? map_to_rank(smem_u32(&full[0]), 0) : smem_u32(&full[0]);
+      int s = 0, issued = 0;
+      uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
-        const int t0 = (tile % tiles_t) * BM, n0 = (tile / tiles_t) * FN;
-        for (int kb = 0; kb < total_kb; ++kb, ++it) {
-          const int s = it % S::STAGES;
-          const uint32_t phase = (uint32_t)(it / S::STAGES) & 1u;
-          if (*failed || !mbar_wait(&empty[s], phase ^ 1u)) {
-            *failed = 1;
-            ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 900 + s);
-            ok = false;
-            break;
-          }
-          const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
-          mbar_expect_tx(&full[s], S::STAGE_BYTES);
-          tma_load_2d(stage, &map_x, kb * BK, t0, &full[s]);
-          if (EPI == 2) {
-            tma_load_2d(stage + S::X_BYTES, &map_w, kb * BK, n0, &full[s]);                       // gate rows
-            tma_load_2d(stage + S::X_BYTES + S::W_BYTES / 2, &map_w, kb * BK, N + n0, &full[s]);  // up rows
-          } else {
-            tma_load_2d(stage + S::X_BYTES, &map_w, kb * BK, n0, &full[s]);
+      for (int tile = first_tile; tile < tiles_total && ok; tile += tile_step) {
+        const int t0 = (tile % tiles_t) * (BM * CTAS) + rank * BM, n0 = (tile / tiles_t) * FN;
+        // this block's weight rows: all of the tile's; of a pair, the gate rows in the first block
+        // and the up rows in the second, or each its half of the features
+        const int w0 = EPI == 2 ? (CTAS == 2 ? rank * N + n0 : n0 + (part == 2 ? N : 0)) : n0 + rank * (FN / CTAS);
+        const CUtensorMap* map = part == 0 ? &map_x : &map_w;
+        const int y = part == 0 ? t0 : w0;
+        const uint32_t within = (uint32_t)(half * S::KB_BYTES + (part == 0 ? 0 : S::X_BYTES + (part - 1) * (S::W_BYTES / 2)));
+        for (int r = 0; r < shares && ok; ++r) {
+          const int kb_lo = r * kb_per_share;
+          int kb_hi = kb_lo + kb_per_share;
+          if (kb_hi > total_kb) kb_hi = total_kb;
+          for (int kb = kb_lo; kb < kb_hi; kb += S::STAGE_KB) {
+            const int n = kb_hi - kb < S::STAGE_KB ? kb_hi - kb : S::STAGE_KB;
+            if (*failed || !mbar_wait(&empty[s], phase ^ 1u)) {
+              *failed = 1;
+              if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 900 + s);
+              ok = false;
+              break;
+            }
+            if (lane == 0 && rank == 0) mbar_expect_tx(&full[s], (uint32_t)(CTAS * n * S::KB_BYTES));
+            if (half < n)
+              tma_load_2d_any<CTAS>(base + (uint32_t)s * S::STAGE_BYTES + within, map, (kb + half) * BK, y,
+                                    full0 + (uint32_t)s * 8u);
+            ++issued;
+            if (++s == S::STAGES) {
+              s = 0;
+              phase ^= 1u;
+            }
           }
         }
       }
-      if (!ok) {
+      if (!ok && lane == 0 && rank == 0) {
         // wait (bounded) for the copies still in flight before the block exits
-        const int first = it > S::STAGES ? it - S::STAGES : 0;
-        for (int j = first; j < it; ++j) mbar_wait(&full[j % S::STAGES], (uint32_t)(j / S::STAGES) & 1u);
+        for (int j = issued > S::STAGES ? issued - S::STAGES : 0; j < issued; ++j)
+          mbar_wait(&full[j % S::STAGES], (uint32_t)(j / S::STAGES) & 1u);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BM, S::W_ROWS);
-      int it = 0, sc = 0;                         // k-blocks and shares consumed so far
+    // The whole warp walks the loop and one elected lane issues: what the instructions take
+    // (descriptors, addresses) is then the same in every lane and stays in uniform registers;
+    // inside a branch of one lane each MMA paid for moving them there.
+    if (rank == 0) {
+      constexpr uint32_t idesc = instr_desc(BM * CTAS, S::W_ROWS);
+      const bool issuer = elect_one();
+      int s = 0, sc = 0;                          // the stage in turn; shares consumed so far
+      uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
+      for (int tile = first_tile; tile < tiles_total && ok; tile += tile_step) {
         for (int r = 0; r < shares && ok; ++r, ++sc) {
           const int region = sc & 1;
           const uint32_t acc_addr = tmem_base + (uint32_t)(region * COLS);
-          if (*failed || !mbar_wait(&acc_empty[region], ((uint32_t)(sc >> 1) & 1u) ^ 1u)) {
+          ok = __all_sync(0xffffffffu, !*failed && mbar_wait(&acc_empty[region], ((uint32_t)(sc >> 1) & 1u) ^ 1u));
+          if (!ok) {
             *failed = 1;
-            ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 950 + region);
-            ok = false;
+            if (issuer) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 950 + region);
             break;
           }
           fence_after_sync();
           const int kb_lo = r * kb_per_share;
           int kb_hi = kb_lo + kb_per_share;
           if (kb_hi > total_kb) kb_hi = total_kb;
-          for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
-            const int s = it % S::STAGES;
-            const uint32_t phase = (uint32_t)(it / S::STAGES) & 1u;
-            if (!mbar_wait(&full[s], phase)) {
+          for (int kb = kb_lo; kb < kb_hi; kb += S::STAGE_KB) {
+            const int n = kb_hi - kb < S::STAGE_KB ? kb_hi - kb : S::STAGE_KB;
+            ok = __all_sync(0xffffffffu, mbar_wait(&full[s], phase));
+            if (!ok) {
               *failed = 1;
-              ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 920 + s);
-              ok = false;
+              if (issuer) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 920 + s);
               break;
             }
             fence_after_sync();
             const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
             const uint64_t adesc = smem_desc(stage), bdesc = smem_desc(stage + S::X_BYTES);
+            if (issuer) {
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)
-              umma(acc_addr, adesc + 2 * k, bdesc + 2 * k, idesc, (kb == kb_lo && k == 0) ? 0u : 1u);
-            umma_commit(&empty[s]);
+              for (int h = 0; h < S::STAGE_KB; ++h) {
+                if (h < n) {
+#pragma unroll
+                  for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint32_t acc = (kb == kb_lo && h == 0 && k == 0) ? 0u : 1u;
+                    const uint64_t step = (uint64_t)((h * S::KB_BYTES) >> 4) + 2 * k;
+                    if constexpr (CTAS == 2) umma_pair(acc_addr, adesc + step, bdesc + step, idesc, acc);
+                    else umma(acc_addr, adesc + step, bdesc + step, idesc, acc);
+                  }
+                }
+              }
+              if constexpr (CTAS == 2) umma_commit_pair(&empty[s]);
+              else umma_commit(&empty[s]);
+            }
+            __syncwarp();
+            if (++s == S::STAGES) {
+              s = 0;
+              phase ^= 1u;
+            }
           }
-          if (ok) umma_commit(&acc_full[region]);
+          if (ok && issuer) {
+            if constexpr (CTAS == 2) umma_commit_pair(&acc_full[region]);
+            else umma_commit(&acc_full[region]);
+          }
+          __syncwarp();
         }
       }
     }
   } else {
     // epilogue: warp w may touch tensor-memory lanes 32*(w%4) .. +32; this thread has token `row`
-    // of the tile and the features OUT * group .. + OUT of it (for silu-mul their gate and up sums)
+    // of the block's 128 and the features OUT * group .. + OUT of it (for silu-mul their gate and up sums)
     const int quad = warp & 3;
     const int group = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
@@ -1290,8 +1424,8 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     float sum[SUMS];
     int sc = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
-      const int t = (tile % tiles_t) * BM + row, n_first = (tile / tiles_t) * FN + group * OUT;
+    for (int tile = first_tile; tile < tiles_total && ok; tile += tile_step) {
+      const int t = (tile % tiles_t) * (BM * CTAS) + rank * BM + row, n_first = (tile / tiles_t) * FN + group * OUT;
       for (int r = 0; r < shares; ++r, ++sc) {
         const int region = sc & 1;
         bool got = mbar_wait(&acc_full[region], (uint32_t)(sc >> 1) & 1u);
@@ -1315,39 +1449,82 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[region]);
+        if (lane == 0) {
+          if constexpr (CTAS == 2) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty[region]), 0));
+          else mbar_arrive(&acc_empty[region]);
+        }
       }
-      if (ok && t < T) {
-        TC* crow = C + (int64_t)t * ldc + n_first;
-        constexpr int PER = 16 / (int)sizeof(TC);              // outputs of a 16-byte piece
-        const bool pieces = (reinterpret_cast<uintptr_t>(crow) & 15) == 0 && n_first + OUT <= N;
+      if (!ok) break;
+      constexpr int PER = 16 / (int)sizeof(TC);                // outputs of a 16-byte piece
+      constexpr int CH = 8 * PER;                              // outputs of a 128-byte chunk of a row
+      // whole 16-byte pieces of rows that start on 16-byte boundaries (the same answer in every lane)
+      const bool pieces = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc % PER) == 0 && n_first + OUT <= N;
+      if (pieces) {
+        // Through shared memory, 128 bytes of each of the warp's 32 tokens at a time: a lane puts
+        // its token's chunk there, then eight lanes together take one token's chunk to memory, four
+        // tokens an instruction.  (A lane writing its own token's pieces touched 32 lines per
+        // instruction, and the tile's stores took as long as its MMAs.)
+        uint8_t* mine = staging + (warp - 2) * 4096;
+        const int t_warp = t - lane;                           // the warp's first token
+        TC* cbase = C + (int64_t)t_warp * ldc + n_first;
 #pragma unroll
-        for (int c0 = 0; c0 < OUT; c0 += PER) {
-          float v[PER];
+        for (int c0 = 0; c0 < OUT; c0 += CH) {
 #pragma unroll
-          for (int j = 0; j < PER; ++j) {
-            const float a = sum[c0 + j];
-            v[j] = EPI == 2 ? a / (1.0f + expf(-a)) * sum[OUT + c0 + j] : a;
-          }
-          if (pieces) {
+          for (int j = 0; j < 8; ++j) {
+            float v[PER];
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+              const float a = sum[c0 + j * PER + e];
+              v[e] = EPI == 2 ? silu_mul(a, sum[OUT + c0 + j * PER + e]) : a;
+            }
+            uint4 piece;
             if constexpr (sizeof(TC) == 4) {
-              float4* p = reinterpret_cast<float4*>(crow + c0);
-              if (EPI == 1) {
-                const float4 old = *p;
-                v[0] += old.x; v[1] += old.y; v[2] += old.z; v[3] += old.w;
-              }
-              *p = make_float4(v[0], v[1], v[2], v[3]);
+              piece = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
             } else {
-              uint4 out;
-              out.x = pack2_bf16(v[0], v[1]); out.y = pack2_bf16(v[2], v[3]);
-              out.z = pack2_bf16(v[4], v[5]); out.w = pack2_bf16(v[6], v[7]);
-              *reinterpret_cast<uint4*>(crow + c0) = out;
+              piece.x = pack2_bf16(v[0], v[1]); piece.y = pack2_bf16(v[2], v[3]);
+              piece.z = pack2_bf16(v[4], v[5]); piece.w = pack2_bf16(v[6], v[7]);
+            }
+            *reinterpret_cast<uint4*>(mine + lane * 128 + ((j ^ (lane & 7)) << 4)) = piece;
+          }
+          __syncwarp();
+          const int slot = lane & 7;
+          if constexpr (EPI == 1) {
+            constexpr int AT_ONCE = SUMS > 64 ? 4 : 8;         // old values asked for together (registers allowing)
+#pragma unroll
+            for (int i0 = 0; i0 < 8; i0 += AT_ONCE) {
+              float4 old[AT_ONCE];
+#pragma unroll
+              for (int i = 0; i < AT_ONCE; ++i) {
+                const int r = (i0 + i) * 4 + (lane >> 3);
+                if (t_warp + r < T) old[i] = *reinterpret_cast<const float4*>(cbase + (int64_t)r * ldc + c0 + slot * PER);
+              }
+#pragma unroll
+              for (int i = 0; i < AT_ONCE; ++i) {
+                const int r = (i0 + i) * 4 + (lane >> 3);
+                const float4 add = *reinterpret_cast<const float4*>(mine + r * 128 + ((slot ^ (r & 7)) << 4));
+                if (t_warp + r < T)
+                  *reinterpret_cast<float4*>(cbase + (int64_t)r * ldc + c0 + slot * PER) =
+                      make_float4(add.x + old[i].x, add.y + old[i].y, add.z + old[i].z, add.w + old[i].w);
+              }
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < PER; ++j)
-              if (n_first + c0 + j < N)
-                crow[c0 + j] = ls_from_float<TC>(EPI == 1 ? ls_to_float<TC>(crow[c0 + j]) + v[j] : v[j]);
+            for (int i = 0; i < 8; ++i) {
+              const int r = i * 4 + (lane >> 3);
+              const uint4 piece = *reinterpret_cast<const uint4*>(mine + r * 128 + ((slot ^ (r & 7)) << 4));
+              if (t_warp + r < T) *reinterpret_cast<uint4*>(cbase + (int64_t)r * ldc + c0 + slot * PER) = piece;
+            }
+          }
+          __syncwarp();
+        }
+      } else if (t < T) {
+        TC* crow = C + (int64_t)t * ldc + n_first;
+#pragma unroll
+        for (int c0 = 0; c0 < OUT; ++c0) {
+          if (n_first + c0 < N) {
+            const float a = sum[c0];
+            const float v = EPI == 2 ? silu_mul(a, sum[OUT + c0]) : a;
+            crow[c0] = ls_from_float<TC>(EPI == 1 ? v + ls_to_float<TC>(crow[c0]) : v);
           }
         }
       }
@@ -1355,10 +1532,16 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
   fence_before_sync();
   __syncthreads();
+  if constexpr (CTAS == 2) {        // nothing of the pair's is in flight towards a block that has left
+    cluster_arrive();
+    cluster_wait();
+  }
   if (warp == 2) {
     fence_after_sync();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ACC_COLS)
-                 : "memory");
+    if constexpr (CTAS == 2)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ACC_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ACC_COLS) : "memory");
   }
 }
 
@@ -1527,23 +1710,72 @@ int launch_walk(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, in
   }
 }
 
+// How many pairs of blocks the device runs at one time (0: pairs cannot be launched).
 template <int EPI, int FN, typename TC>
+int resident_pairs() {
+  using S = RowsShape<EPI, FN, 2>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * sm_count());
+  cfg.blockDim = dim3(320);
+  cfg.dynamicSmemBytes = S::SMEM;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int pairs = 0;
+  if (cudaOccupancyMaxActiveClusters(&pairs, gemm_tc_rows_kernel<EPI, FN, 2, TC>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return pairs;
+}
+
+template <int EPI, int FN, int CTAS, typename TC>
 int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int64_t ldc,
                 const Plan& plan, int* err, cudaStream_t stream) {
-  using S = RowsShape<EPI, FN>;
+  using S = RowsShape<EPI, FN, CTAS>;
   static bool configured = false;
+  static int resident = 0;                       // blocks, or pairs of them, that run at one time
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc_rows_kernel<EPI, FN, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tc_rows_kernel<EPI, FN, CTAS, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)S::SMEM) != cudaSuccess)
       return LS_E_SMEM;
+    resident = CTAS == 2 ? resident_pairs<EPI, FN, TC>() : sm_count();
     configured = true;
   }
-  const int tiles_t = (T + BM - 1) / BM, tiles_n = (N + FN - 1) / FN;
+  if (resident <= 0) return LS_E_SIZE;
+  const int tiles_t = (T + BM * CTAS - 1) / (BM * CTAS), tiles_n = (N + FN - 1) / FN;
   const int tiles = tiles_t * tiles_n;
-  const int sms = sm_count();
-  ls_launch(gemm_tc_rows_kernel<EPI, FN, TC>, tiles < sms ? tiles : sms, 320, S::SMEM, stream, mw, mx, (TC*)C, T, N,
-            K, ldc, plan.kb_per_share, plan.shares, tiles_t, tiles, err);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(CTAS * (tiles < resident ? tiles : resident));
+  cfg.blockDim = dim3(320);
+  cfg.dynamicSmemBytes = S::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ls_dependent_launch ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_rows_kernel<EPI, FN, CTAS, TC>, mw, mx, (TC*)C, T, N, K, ldc,
+                                     plan.kb_per_share, plan.shares, tiles_t, tiles, err);
+  if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
+}
+
+int rows_pairs = 1;     // 1: tiles of 256 tokens on pairs of blocks; 0: tiles of 128 tokens on single blocks
+
+template <int EPI, int FN, typename TC>
+int launch_rows_as(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int64_t ldc,
+                   const Plan& plan, int* err, cudaStream_t stream) {
+  if (rows_pairs) return launch_rows<EPI, FN, 2, TC>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+  return launch_rows<EPI, FN, 1, TC>(mw, mx, C, T, N, K, ldc, plan, err, stream);
 }
 
 // more than 128 tokens: the kernel with the tokens on the M side
@@ -1552,23 +1784,27 @@ int run_rows(const void* X, const void* W, void* C, int c_dtype, int T, int N, i
   typedef __nv_bfloat16 bf16;
   if ((ldx % 8) || ((uintptr_t)X & 15)) return LS_E_ALIGN;
   CUtensorMap mw, mx;
+  const int ctas = rows_pairs ? 2 : 1;
   // tiles of 256 features unless they would leave SMs without one (the tile's width changes no sum)
-  const bool wide = epilogue != 2 && ((T + BM - 1) / BM) * ((N + 255) / 256) >= sm_count();
-  if (!make_map(&mw, W, epilogue == 2 ? 2 * N : N, K, ldw, wide ? 256 : 128)) return LS_E_SIZE;
+  const int tiles_t = (T + BM * ctas - 1) / (BM * ctas);
+  const bool wide = epilogue != 2 && tiles_t * ((N + 255) / 256) * ctas >= sm_count();
+  // a block's box of weight rows: the tile's (silu-mul: its gate rows, then its up rows), half of them in a pair
+  const int box = epilogue == 2 ? 128 : (wide ? 256 : 128) / ctas;
+  if (!make_map(&mw, W, epilogue == 2 ? 2 * N : N, K, ldw, box)) return LS_E_SIZE;
   if (!make_map(&mx, X, T, K, ldx, BM)) return LS_E_SIZE;
   if (epilogue == 2) {
-    if (c_dtype == LS_BF16) return launch_rows<2, 128, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+    if (c_dtype == LS_BF16) return launch_rows_as<2, 128, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream);
     return LS_E_DTYPE;
   }
   if (epilogue == 0 && c_dtype == LS_BF16)
-    return wide ? launch_rows<0, 256, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream)
-                : launch_rows<0, 128, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+    return wide ? launch_rows_as<0, 256, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream)
+                : launch_rows_as<0, 128, bf16>(mw, mx, C, T, N, K, ldc, plan, err, stream);
   if (epilogue == 0 && c_dtype == LS_F32)
-    return wide ? launch_rows<0, 256, float>(mw, mx, C, T, N, K, ldc, plan, err, stream)
-                : launch_rows<0, 128, float>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+    return wide ? launch_rows_as<0, 256, float>(mw, mx, C, T, N, K, ldc, plan, err, stream)
+                : launch_rows_as<0, 128, float>(mw, mx, C, T, N, K, ldc, plan, err, stream);
   if (epilogue == 1 && c_dtype == LS_F32)
-    return wide ? launch_rows<1, 256, float>(mw, mx, C, T, N, K, ldc, plan, err, stream)
-                : launch_rows<1, 128, float>(mw, mx, C, T, N, K, ldc, plan, err, stream);
+    return wide ? launch_rows_as<1, 256, float>(mw, mx, C, T, N, K, ldc, plan, err, stream)
+                : launch_rows_as<1, 128, float>(mw, mx, C, T, N, K, ldc, plan, err, stream);
   return LS_E_DTYPE;
 }
 
@@ -1661,6 +1897,10 @@ int run(const void* X, const NormArgs* norm, const LsQkvStore* heads, const void
 }  // namespace
 
 LS_API void ls_set_dependent_launch_tc(int on) { ls_dependent_launch = on ? 1 : 0; }
+
+// Whether products of more than 128 tokens run on pairs of blocks (the default) or on single
+// blocks; the sums are the same either way.
+LS_API void ls_set_gemm_tc_pairs(int on) { rows_pairs = on ? 1 : 0; }
 
 // The token tile for T tokens of a product with an (N, K) weight (it does not change any sum).
 LS_API int ls_gemm_tc_token_tile(int T, int N, int K, int epilogue) {

@@ -103,6 +103,15 @@ def library(name: str = "core") -> ctypes.CDLL:
     return lib
 
 
+def set_gemm_tc_pairs(on: bool) -> None:
+    """Whether tensor-core products of more than 128 tokens run on pairs of blocks that share
+    a tile of 256 tokens (tcgen05 cta_group::2; the default) or on single blocks with tiles of
+    128 tokens.  The sums are the same either way."""
+    fn = library("tc").ls_set_gemm_tc_pairs
+    fn.argtypes, fn.restype = [c_int], None
+    fn(1 if on else 0)
+
+
 def set_dependent_launch(on: bool) -> None:
     """Programmatic dependent launch of all kernels (on by default): a kernel is
     scheduled while its predecessor drains and waits for it before it touches memory."""

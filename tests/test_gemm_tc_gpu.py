@@ -96,6 +96,40 @@ def test_a_row_has_the_same_bits_in_every_batch(k, n):
     K.raise_on_fault(err)
 
 
+@pytest.mark.parametrize("t,n,k", [(2048, 4096, 1024), (2048, 1024, 2048), (300, 264, 328), (129, 3072, 1024),
+                                   (1000, 384, 3080), (257, 130, 136), (2304, 2048, 512)])
+def test_pairs_of_blocks_give_the_bits_of_single_blocks(t, n, k):
+    """Tiles of 256 tokens on two blocks (cta_group::2) against tiles of 128 tokens on one, every epilogue,
+    tiles of 256 and of 128 features, edges in every dimension."""
+    from lockstep_b200 import kernels as K
+
+    g = torch.Generator().manual_seed(t + n + k)
+    x = torch.randn(t, k, generator=g).to(torch.bfloat16).to(dev())
+    w = (torch.randn(2 * n, k, generator=g) * 0.3).to(torch.bfloat16).to(dev())
+    res = torch.randn(t, n, generator=g).to(dev())
+    err = K.new_error_word(dev())
+    got = {}
+    try:
+        for pairs in (False, True):
+            K.set_gemm_tc_pairs(pairs)
+            c = torch.empty(t, n, dtype=torch.bfloat16, device=dev())
+            assert K.gemm_nt_tc(x, w[:n].contiguous(), c, K.EPILOGUE_STORE, err)
+            cf = torch.empty(t, n, dtype=torch.float32, device=dev())
+            assert K.gemm_nt_tc(x, w[:n].contiguous(), cf, K.EPILOGUE_STORE, err)
+            rd = res.clone()
+            assert K.gemm_nt_tc(x, w[:n].contiguous(), rd, K.EPILOGUE_RESIDUAL, err)
+            act = torch.empty(t, n, dtype=torch.bfloat16, device=dev())
+            assert K.gemm_nt_tc(x, w, act, K.EPILOGUE_SILU_MUL, err)
+            K.raise_on_fault(err)
+            got[pairs] = (c, cf, rd, act)
+    finally:
+        K.set_gemm_tc_pairs(True)
+    for a, b in zip(got[False], got[True]):
+        assert torch.equal(a, b)
+    want = x.double() @ w[:n].double().T
+    assert (got[True][1].double() - want).abs().max().item() <= 2e-5 * (float(want.abs().max()) + 1e-6)
+
+
 def test_unaligned_depth_falls_back_to_the_cuda_cores():
     from lockstep_b200 import kernels as K
 
