@@ -112,6 +112,18 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, ui
       "}\n" ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// true in one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
@@ -284,17 +296,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       page = page_next;
     }
   } else if (warp == 1) {
-    // ---- MMA issue ----
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = instr_desc(BLOCK_M, BLOCK_N, false);
-      constexpr uint32_t idesc_o = instr_desc(BLOCK_M, D, true);
-      bool ok = mbar_wait(q_full, 0);
-      auto issue_s = [&](int it) {       // S(it) = Q K(it)^T into S buffer it & 1
-        const int s = it & 1;
-        const uint32_t phase = (uint32_t)(it >> 1) & 1u;
-        if (!mbar_wait(&k_full[s], phase)) return false;
-        if (it >= 2 && !mbar_wait(&s_free[s], (uint32_t)((it >> 1) - 1) & 1u)) return false;
-        fence_after_sync();
+    // ---- MMA issue: the whole warp walks the loop and one elected lane issues, so that the
+    // instructions' operands are the same in every lane and stay in uniform registers (inside a
+    // branch of one lane every MMA paid for moving them there) ----
+    constexpr uint32_t idesc_s = instr_desc(BLOCK_M, BLOCK_N, false);
+    constexpr uint32_t idesc_o = instr_desc(BLOCK_M, D, true);
+    const bool issuer = elect_one();
+    bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0));
+    auto issue_s = [&](int it) {       // S(it) = Q K(it)^T into S buffer it & 1
+      const int s = it & 1;
+      const uint32_t phase = (uint32_t)(it >> 1) & 1u;
+      bool got = mbar_wait(&k_full[s], phase);
+      if (it >= 2) got = got && mbar_wait(&s_free[s], (uint32_t)((it >> 1) - 1) & 1u);
+      if (!__all_sync(0xffffffffu, got)) return false;
+      fence_after_sync();
+      if (issuer) {
 #pragma unroll
         for (int k = 0; k < D / UMMA_K; ++k) {
           const uint32_t koff = (uint32_t)((k >> 2) * HALF_BYTES + (k & 3) * UMMA_K * 2);
@@ -303,19 +319,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         umma_commit(&s_full[s]);
         umma_commit(&k_free[s]);
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int it = 0; it < n_tiles && ok; ++it) {
-        const int s = it & 1;
-        const uint32_t phase = (uint32_t)(it >> 1) & 1u;
-        if (it + 1 < n_tiles) ok = issue_s(it + 1);
-        if (!ok) break;
-        if (!mbar_wait(p_full, (uint32_t)it & 1u) || !mbar_wait(&v_full[s], phase)) {
-          ok = false;
-          break;
-        }
-        fence_after_sync();
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_s(0);
+    for (int it = 0; it < n_tiles && ok; ++it) {
+      const int s = it & 1;
+      const uint32_t phase = (uint32_t)(it >> 1) & 1u;
+      if (it + 1 < n_tiles) ok = issue_s(it + 1);
+      if (!ok) break;
+      ok = __all_sync(0xffffffffu, mbar_wait(p_full, (uint32_t)it & 1u) && mbar_wait(&v_full[s], phase));
+      if (!ok) break;
+      fence_after_sync();
+      if (issuer) {
 #pragma unroll
         for (int k = 0; k < BLOCK_N / UMMA_K; ++k) {
           // P: 16 keys are 32 bytes of a row; V: 16 keys are 16 rows of 128 bytes
@@ -326,10 +343,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         umma_commit(&o_full[s]);
         umma_commit(&v_free[s]);
       }
-      if (!ok) {
-        *failed = 1;
-        ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 820);
-      }
+      __syncwarp();
+    }
+    if (!ok) {
+      *failed = 1;
+      if (issuer) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 820);
     }
   } else if (warp < 10) {
     // ---- softmax: two threads per row (a token, lane `row` of tensor memory): the thread of

@@ -144,6 +144,18 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, ui
       : "memory");
 }
 
+// true in one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
@@ -344,32 +356,37 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BM, BN);
-      bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % S::STAGES;
-        const uint32_t phase = (uint32_t)(kb / S::STAGES) & 1u;
-        if (*failed || !mbar_wait(&full[s], phase)) {
-          *failed = 1;
-          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 200 + s);
-          ok = false;
-          break;
-        }
-        fence_after_sync();
-        const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
-        const uint32_t xs = stage + S::A_TILES * A_BYTES;
+    // the whole warp walks the loop and one elected lane issues: the instructions' operands
+    // are then the same in every lane and need no move into uniform registers per MMA
+    constexpr uint32_t idesc = instr_desc(BM, BN);
+    const bool issuer = elect_one();
+    bool ok = true;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % S::STAGES;
+      const uint32_t phase = (uint32_t)(kb / S::STAGES) & 1u;
+      ok = __all_sync(0xffffffffu, !*failed && mbar_wait(&full[s], phase));
+      if (!ok) {
+        *failed = 1;
+        if (issuer) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 200 + s);
+        break;
+      }
+      fence_after_sync();
+      const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+      const uint64_t adesc = smem_desc(stage), udesc = smem_desc(stage + A_BYTES);
+      const uint64_t bdesc = smem_desc(stage + S::A_TILES * A_BYTES);
+      if (issuer) {
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
-          const uint64_t bdesc = smem_desc(xs + k * UMMA_K * 2);
           const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
-          umma(tmem_base, smem_desc(stage + k * UMMA_K * 2), bdesc, idesc, acc);
-          if (EPI == 2) umma(tmem_base + BN, smem_desc(stage + A_BYTES + k * UMMA_K * 2), bdesc, idesc, acc);
+          umma(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+          if (EPI == 2) umma(tmem_base + BN, udesc + 2 * k, bdesc + 2 * k, idesc, acc);
         }
         if (kb + S::STAGES < num_kb) umma_commit(&empty[s]);     // only a stage that is filled again
       }
-      if (ok) umma_commit(acc_full);
+      __syncwarp();
     }
+    if (ok && issuer) umma_commit(acc_full);
+    __syncwarp();
   } else {
     // epilogue warps: warp w may touch tensor-memory lanes 32*(w%4) .. +32
     const int quad = warp & 3;
@@ -727,28 +744,32 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncwarp();
     cluster_wait();
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BM, BN);
-      bool ok = true;
-      if (NORM && !mbar_wait(x_ready, 0)) {
+    // the whole warp walks the loop and one elected lane issues (see gemm_tc_cluster_kernel)
+    constexpr uint32_t idesc = instr_desc(BM, BN);
+    const bool issuer = elect_one();
+    bool ok = true;
+    if (NORM) {
+      ok = __all_sync(0xffffffffu, mbar_wait(x_ready, 0));
+      if (!ok) {
         *failed = 1;
-        ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 560);
-        ok = false;
+        if (issuer) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 560);
       }
-      int s = 0;
-      uint32_t phase = 0u;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        if (!mbar_wait(&full[s], phase)) {           // runs out too when the producer gave up
-          *failed = 1;
-          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 500 + s);
-          ok = false;
-          break;
-        }
-        fence_after_sync();
-        const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
-        const uint32_t xs = NORM ? x_base + (uint32_t)(kb * BN * 128) : stage + A_TILES * A_BYTES;
-        // a step of 16 elements along K is 32 bytes: 2 in the descriptor's address field
-        const uint64_t adesc = smem_desc(stage), udesc = smem_desc(stage + A_BYTES), bdesc = smem_desc(xs);
+    }
+    int s = 0;
+    uint32_t phase = 0u;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&full[s], phase));     // runs out too when the producer gave up
+      if (!ok) {
+        *failed = 1;
+        if (issuer) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 500 + s);
+        break;
+      }
+      fence_after_sync();
+      const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
+      const uint32_t xs = NORM ? x_base + (uint32_t)(kb * BN * 128) : stage + A_TILES * A_BYTES;
+      // a step of 16 elements along K is 32 bytes: 2 in the descriptor's address field
+      const uint64_t adesc = smem_desc(stage), udesc = smem_desc(stage + A_BYTES), bdesc = smem_desc(xs);
+      if (issuer) {
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
           const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
@@ -756,13 +777,14 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           if (EPI == 2) umma(tmem_base + BN, udesc + 2 * k, bdesc + 2 * k, idesc, acc);
         }
         if (kb + stages < num_kb) umma_commit(&empty[s]);     // only a stage that is filled again
-        if (++s == stages) {
-          s = 0;
-          phase ^= 1u;
-        }
       }
-      if (ok) umma_commit(acc_full);
+      __syncwarp();
+      if (++s == stages) {
+        s = 0;
+        phase ^= 1u;
+      }
     }
+    if (ok && issuer) umma_commit(acc_full);
     __syncwarp();
     cluster_wait();
   } else {
@@ -1022,46 +1044,54 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BM, BN);
-      int it = 0, sc = 0;                         // k-blocks and shares consumed so far
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
-        for (int r = 0; r < shares && ok; ++r, ++sc) {
-          const int region = sc & 1;
-          const uint32_t acc_addr = tmem_base + (uint32_t)(region * COLS);
-          if (*failed || !mbar_wait(&acc_empty[region], ((uint32_t)(sc >> 1) & 1u) ^ 1u)) {
+    // the whole warp walks the loop and one elected lane issues (see gemm_tc_cluster_kernel)
+    constexpr uint32_t idesc = instr_desc(BM, BN);
+    const bool issuer = elect_one();
+    int s = 0, sc = 0;                            // the stage in turn; shares consumed so far
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles_total && ok; tile += gridDim.x) {
+      for (int r = 0; r < shares && ok; ++r, ++sc) {
+        const int region = sc & 1;
+        const uint32_t acc_addr = tmem_base + (uint32_t)(region * COLS);
+        ok = __all_sync(0xffffffffu, !*failed && mbar_wait(&acc_empty[region], ((uint32_t)(sc >> 1) & 1u) ^ 1u));
+        if (!ok) {
+          *failed = 1;
+          if (issuer) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 250 + region);
+          break;
+        }
+        fence_after_sync();
+        const int kb_lo = r * kb_per_share;
+        int kb_hi = kb_lo + kb_per_share;
+        if (kb_hi > total_kb) kb_hi = total_kb;
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          ok = __all_sync(0xffffffffu, !*failed && mbar_wait(&full[s], phase));
+          if (!ok) {
             *failed = 1;
-            ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 250 + region);
-            ok = false;
+            if (issuer) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 200 + s);
             break;
           }
           fence_after_sync();
-          const int kb_lo = r * kb_per_share;
-          int kb_hi = kb_lo + kb_per_share;
-          if (kb_hi > total_kb) kb_hi = total_kb;
-          for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
-            const int s = it % S::STAGES;
-            const uint32_t phase = (uint32_t)(it / S::STAGES) & 1u;
-            if (*failed || !mbar_wait(&full[s], phase)) {
-              *failed = 1;
-              ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 200 + s);
-              ok = false;
-              break;
-            }
-            fence_after_sync();
-            const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+          const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
+          const uint64_t adesc = smem_desc(stage), udesc = smem_desc(stage + A_BYTES);
+          const uint64_t bdesc = smem_desc(stage + S::A_TILES * A_BYTES);
+          if (issuer) {
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t bdesc = smem_desc(stage + S::A_TILES * A_BYTES + k * UMMA_K * 2);
               const uint32_t acc = (kb == kb_lo && k == 0) ? 0u : 1u;
-              umma(acc_addr, smem_desc(stage + k * UMMA_K * 2), bdesc, idesc, acc);
-              if (EPI == 2) umma(acc_addr + BN, smem_desc(stage + A_BYTES + k * UMMA_K * 2), bdesc, idesc, acc);
+              umma(acc_addr, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+              if (EPI == 2) umma(acc_addr + BN, udesc + 2 * k, bdesc + 2 * k, idesc, acc);
             }
             umma_commit(&empty[s]);
           }
-          if (ok) umma_commit(&acc_full[region]);
+          __syncwarp();
+          if (++s == S::STAGES) {
+            s = 0;
+            phase ^= 1u;
+          }
         }
+        if (ok && issuer) umma_commit(&acc_full[region]);
+        __syncwarp();
       }
     }
   } else if (warp >= EPI_FIRST) {
@@ -1190,18 +1220,6 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
       : "memory");
-}
-// true in one lane of the (converged) warp
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "elect.sync _|p, 0xffffffff;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(pred));
-  return pred != 0;
 }
 template <int CTAS>
 __device__ __forceinline__ void tma_load_2d_any(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
