@@ -160,6 +160,115 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, const LsQkv
     ls_qkv_head_store<T>(args, reinterpret_cast<const T*>(row_smem) + head * args.d, t, head, lane, err);
 }
 
+// The same for bfloat16 heads of D = 64 or 128 elements that are rotated whole, at a fraction
+// of the instructions: what belongs to the token (position, page, cosines, sines, gains) is
+// looked up once per token and not once per head, a lane keeps its four (two) elements of a
+// head in registers and writes the results over the staged row, and the row leaves in 16-byte
+// pieces.  Every sum and product is ls_norm_rope_head's, in its order: the bits are the same.
+template <int D>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_whole_kernel(const __nv_bfloat16* __restrict__ qkv, const LsQkvStore args, int tokens, int* err) {
+  typedef __nv_bfloat16 bf16;
+  constexpr int PER_LANE = D / 32;                // a lane's elements of a head: lane, lane + 32, ...
+  constexpr int VEC = D / 8;                      // 16-byte pieces of a head
+  ls_dependency_trigger();
+  extern __shared__ uint4 row_smem[];
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = args.nq, nkv = args.nkv;
+  const int heads_total = nq + 2 * nkv;
+  // weights first: they do not wait for the kernel before
+  float gq[PER_LANE], gk[PER_LANE];
+  const bool normed = args.q_gain != nullptr;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    gq[j] = gk[j] = 1.f;
+    if (normed) {
+      const int i = lane + 32 * j;
+      if (args.gain_bf16) {
+        gq[j] = __bfloat162float(reinterpret_cast<const bf16*>(args.q_gain)[i]);
+        gk[j] = __bfloat162float(reinterpret_cast<const bf16*>(args.k_gain)[i]);
+      } else {
+        gq[j] = reinterpret_cast<const float*>(args.q_gain)[i];
+        gk[j] = reinterpret_cast<const float*>(args.k_gain)[i];
+      }
+    }
+  }
+  ls_dependency_wait();
+  const uint4* row = reinterpret_cast<const uint4*>(qkv + (int64_t)t * heads_total * D);
+  for (int i = threadIdx.x; i < heads_total * VEC; i += blockDim.x) row_smem[i] = row[i];
+  // the token's place: the same in every thread
+  const int pos = args.positions[t];
+  const bool pos_ok = pos >= 0 && pos < args.max_positions;
+  int page = 0;
+  bool page_ok = false;
+  if (args.write_cache && pos_ok) {
+    page = args.block_table[(int64_t)args.token_req[t] * args.table_stride + pos / args.page_size];
+    page_ok = page >= 0 && page < args.num_pages;
+  }
+  float cs[PER_LANE / 2], sn[PER_LANE / 2];
+#pragma unroll
+  for (int j = 0; j < PER_LANE / 2; ++j) {
+    cs[j] = sn[j] = 0.f;
+    if (pos_ok) {
+      cs[j] = args.cos_table[(int64_t)pos * (D / 2) + lane + 32 * j];
+      sn[j] = args.sin_table[(int64_t)pos * (D / 2) + lane + 32 * j];
+    }
+  }
+  if (threadIdx.x == 0) {
+    if (!pos_ok) ls_record_fault(err, LS_DEV_POSITION_RANGE, t);
+    else if (args.write_cache && !page_ok) ls_record_fault(err, LS_DEV_PAGE_RANGE, t);
+  }
+  __syncthreads();
+  bf16* staged = reinterpret_cast<bf16*>(row_smem);
+  if (pos_ok) {
+    const int normed_heads = args.write_cache && page_ok ? nq + nkv : nq;      // v heads leave as they came
+    for (int head = warp; head < normed_heads; head += 8) {
+      bf16* h = staged + head * D;
+      const float* gain = head < nq ? gq : gk;
+      float v[PER_LANE];
+      float rstd = 1.f;
+#pragma unroll
+      for (int j = 0; j < PER_LANE; ++j) v[j] = __bfloat162float(h[lane + 32 * j]);
+      if (normed) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) ss = fmaf(v[j], v[j], ss);
+        ss = ls_warp_sum(ss);
+        rstd = 1.0f / sqrtf(ss / (float)D + args.eps);
+      }
+#pragma unroll
+      for (int j = 0; j < PER_LANE / 2; ++j) {
+        float lo = __fmul_rn(v[j], rstd);
+        float hi = __fmul_rn(v[j + PER_LANE / 2], rstd);
+        if (normed) {
+          lo = __fmul_rn(lo, gain[j]);
+          hi = __fmul_rn(hi, gain[j + PER_LANE / 2]);
+        }
+        h[lane + 32 * j] = __float2bfloat16_rn(__fsub_rn(__fmul_rn(lo, cs[j]), __fmul_rn(hi, sn[j])));
+        h[lane + 32 * j + D / 2] = __float2bfloat16_rn(__fadd_rn(__fmul_rn(hi, cs[j]), __fmul_rn(lo, sn[j])));
+      }
+    }
+  }
+  __syncthreads();
+  // out: q heads side by side into q_out's row; k and v heads each to its line of the page
+  const int first = pos_ok ? 0 : nq * VEC;                                  // a bad position writes nothing
+  const int last = args.write_cache && page_ok ? heads_total * VEC : nq * VEC;
+  uint4* q_dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(args.q_out) + (int64_t)t * nq * D);
+  const int slot = args.write_cache && page_ok ? pos % args.page_size : 0;
+  for (int i = first + threadIdx.x; i < last; i += blockDim.x) {
+    const int head = i / VEC, piece = i % VEC;
+    if (head < nq) {
+      q_dst[i] = row_smem[i];
+    } else {
+      const int is_v = head >= nq + nkv ? 1 : 0;
+      const int kvh = head - nq - is_v * nkv;
+      const int64_t line = (((int64_t)page * 2 + is_v) * nkv + kvh) * args.page_size + slot;
+      reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(args.pages) + line * D)[piece] = row_smem[i];
+    }
+  }
+}
+
 LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int dtype,
                                  const void* q_gain, const void* k_gain, int gain_dtype,
                                  const float* cos_table, const float* sin_table,
@@ -210,6 +319,16 @@ LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int 
   args.max_positions = max_positions;
   args.write_cache = write_cache;
   args.eps = eps;
+  // whole heads of 64 or 128 bfloat16, rows and targets on 16-byte boundaries: the short kernel
+  const bool whole = dtype == LS_BF16 && (d == 64 || d == 128) && rot_dim == d && (q_gain == nullptr) == (k_gain == nullptr) &&
+                     (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pages) & 15) == 0 && smem <= 48 * 1024;
+  if (whole) {
+    if (d == 64)
+      ls_launch(qk_norm_rope_store_whole_kernel<64>, grid, 256, smem, stream, (const __nv_bfloat16*)qkv, args, tokens, err);
+    else
+      ls_launch(qk_norm_rope_store_whole_kernel<128>, grid, 256, smem, stream, (const __nv_bfloat16*)qkv, args, tokens, err);
+    return ls_launch_status();
+  }
   if (dtype == LS_F32)
     ls_launch(qk_norm_rope_store_kernel<float>, grid, warps * 32, smem, stream, (const float*)qkv, args, tokens, err);
   else if (dtype == LS_BF16)

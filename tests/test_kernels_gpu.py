@@ -114,7 +114,8 @@ def paged_from_dense(kk, vv, page_size, num_pages, seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nq,nkv,d,rot,page", [(6, 3, 48, 48, 8), (4, 1, 32, 16, 16), (16, 8, 128, 128, 32)])
+@pytest.mark.parametrize("nq,nkv,d,rot,page", [(6, 3, 48, 48, 8), (4, 1, 32, 16, 16), (16, 8, 128, 128, 32),
+                                               (5, 1, 64, 64, 16), (3, 3, 128, 64, 8)])
 def test_qk_norm_rope_store(dtype, nq, nkv, d, rot, page):
     k = K()
     g = torch.Generator().manual_seed(d)
