@@ -8,16 +8,18 @@
 //   S = Q K^T     tcgen05.mma, Q [128 x d] and the key tile [128 x d] K-major in
 //                 shared memory (TMA, 128-byte swizzle), S in tensor memory
 //   softmax       the threads of a row read it from S with tcgen05.ld: maximum,
-//                 p = exp2(s * scale * log2 e - m), running m and l in registers; P
-//                 rounded to bfloat16 goes to shared memory in the K-major layout
-//   PV            tcgen05.mma, P [128 x 128] K-major, the value tile [128 keys x d]
-//                 as it lies in the cache (MN-major), into tensor memory, and the
-//                 threads add it to their running row  O = O * alpha + PV
+//                 p = exp2(s * scale * log2 e - m_ref), the running sum l in registers; P
+//                 rounded to bfloat16 goes back to tensor memory (tcgen05.st), two keys a column
+//   PV            tcgen05.mma with P [128 x 128] as the A operand in tensor memory and the
+//                 value tile [128 keys x d] as it lies in the cache (MN-major) in shared
+//                 memory, adding to O in tensor memory over all tiles.  m_ref follows the
+//                 row's maximum lazily (when it has grown by more than 8, a factor 256, the
+//                 row of O is scaled and m_ref moved); O / l does not depend on m_ref.
 //
 // Eleven warps: warp 0 fetches Q once and the key tiles, warp 10 the value tiles, into
 // two stages each (a lane per page of a tile: look-up and TMA box), warp 1 issues the MMAs
 // (S of the next tile before PV of this one, so the tensor cores work while the
-// softmax runs; S has two buffers in tensor memory, PV two), warps 2..9 are the
+// softmax runs; S and P have two buffers each in tensor memory), warps 2..9 are the
 // softmax, two threads per row: one has the first 64 keys of a tile and the first
 // half of the head's dimensions, the other the rest; they share the row's maximum
 // through shared memory.  Every wait is bounded; a wait that runs out records
@@ -112,6 +114,17 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, ui
       "}\n" ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// the same with the A operand in tensor memory (row = lane, two bfloat16 of neighbouring k a column)
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // true in one lane of the (converged) warp
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
@@ -141,6 +154,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
+        "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_before_sync() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -159,7 +185,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // HALVES = d / 64.  Shared memory: Q [HALVES][128 rows][128 B]; two stages of K and of V
-// [HALVES][128 keys][128 B]; P [2][128 rows][128 B] (keys 0..63, 64..127); barriers.
+// [HALVES][128 keys][128 B]; barriers.  Tensor memory: two S buffers, O, two P buffers (bfloat16).
 template <int HALVES>
 __global__ void __launch_bounds__(352, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
@@ -169,8 +195,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   ls_dependency_trigger();
   constexpr int D = HALVES * 64;
   constexpr int KV_BYTES = HALVES * HALF_BYTES;          // K (or V) of one tile; also Q
-  constexpr int P_BYTES = 2 * HALF_BYTES;
-  constexpr uint32_t S_COL = 0, O_COL = 2 * BLOCK_N;     // tensor memory: S buffers, then PV buffers
+  // tensor memory: two S buffers, O, and two P buffers (bfloat16, two keys a column)
+  constexpr uint32_t S_COL = 0, O_COL = 2 * BLOCK_N, P_COL = O_COL + 128, P_COLS = BLOCK_N / 2;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -178,10 +204,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t q_smem = base;
   const uint32_t k_smem = q_smem + KV_BYTES;             // [STAGES]
   const uint32_t v_smem = k_smem + STAGES * KV_BYTES;    // [STAGES]
-  const uint32_t p_smem = v_smem + STAGES * KV_BYTES;
-  uint8_t* p_ptr = aligned + (p_smem - base);
+  const uint32_t bars_smem = v_smem + STAGES * KV_BYTES;
   uint8_t* v_ptr = aligned + (v_smem - base);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (p_smem - base) + P_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (bars_smem - base));
   uint64_t* q_full = bars;             // Q landed
   uint64_t* k_full = bars + 1;         // [2] keys of a tile landed
   uint64_t* v_full = bars + 3;         // [2] values landed
@@ -189,9 +214,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint64_t* v_free = bars + 7;         // [2] PV has read the stage
   uint64_t* s_full = bars + 9;         // [2] S of a tile is in tensor memory
   uint64_t* s_free = bars + 11;        // [2] the softmax warps have read it (8 arrivals)
-  uint64_t* p_full = bars + 13;        // P of a tile is in shared memory (8 arrivals)
-  uint64_t* o_full = bars + 14;        // [2] PV of a tile is in tensor memory (and P may be overwritten)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* p_full = bars + 16;        // [2] P of a tile is in tensor memory (8 arrivals)
+  uint64_t* o_full = bars + 14;        // [2] PV of a tile has been added to O (and its P may be overwritten)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile uint32_t* failed = tmem_slot + 1;
   float* row_max = reinterpret_cast<float*>(bars + 32);   // [2 tiles][2 groups][128 rows], then reused for l
 
@@ -222,7 +247,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&s_free[s], 8);
       mbar_init(&o_full[s], 1);
     }
-    mbar_init(p_full, 8);
+    mbar_init(&p_full[0], 8);
+    mbar_init(&p_full[1], 8);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -238,6 +264,25 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  const int rows_per_box = page_size < BLOCK_N ? page_size : BLOCK_N;
+  const int boxes = BLOCK_N / rows_per_box;              // at most 16: lane b fetches box b of a tile
+  // the page of this lane's box of tile `it`, looked up one tile ahead
+  auto lookup = [&](int it) {
+    int page = 0;
+    if (it < n_tiles && lane < boxes) {
+      int key = (tile_first + it) * BLOCK_N + lane * rows_per_box;
+      if (key > pos_last) key = pos_last;                // past the last key: any page that exists
+      if (key < key_lo) key = key_lo;                    // behind the window: pages may have been given back
+      page = table_row[key / page_size];
+      if (page < 0 || page >= num_pages) {
+        ls_record_fault(err, LS_DEV_PAGE_RANGE, key);
+        page = 0;
+      }
+    }
+    return page;
+  };
+  // the block table is the step's input, older than the kernel before this one
+  int page = (warp == 0 || warp == 10) ? lookup(0) : 0;
   ls_dependency_wait();                 // q and this step's keys and values come from the kernel before
 
   if (warp == 0 || warp == 10) {
@@ -247,30 +292,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
       for (int hh = 0; hh < HALVES; ++hh) tma_load_2d(q_smem + hh * HALF_BYTES, &map_q, h * D + hh * 64, tok0, q_full);
     }
-    const int rows_per_box = page_size < BLOCK_N ? page_size : BLOCK_N;
-    const int boxes = BLOCK_N / rows_per_box;            // at most 16: lane b fetches box b of a tile
-    // the page of this lane's box of tile `it`, looked up one tile ahead
-    auto lookup = [&](int it) {
-      int page = 0;
-      if (it < n_tiles && lane < boxes) {
-        int key = (tile_first + it) * BLOCK_N + lane * rows_per_box;
-        if (key > pos_last) key = pos_last;              // past the last key: any page that exists
-        if (key < key_lo) key = key_lo;                  // behind the window: pages may have been given back
-        page = table_row[key / page_size];
-        if (page < 0 || page >= num_pages) {
-          ls_record_fault(err, LS_DEV_PAGE_RANGE, key);
-          page = 0;
-        }
-      }
-      return page;
-    };
     // warp 0 fetches the key tiles, warp 10 the value tiles: a key stage is free two tiles
     // before the value stage of the same tile, and neither waits for the other's
     const bool keys = warp == 0;
     uint64_t* free_bar = keys ? k_free : v_free;
     uint64_t* full_bar = keys ? k_full : v_full;
     const uint32_t dst_base = keys ? k_smem : v_smem;
-    int page = lookup(0);
     for (int it = 0; it < n_tiles; ++it) {
       const int s = it & 1;
       const uint32_t phase = (uint32_t)(it >> 1) & 1u;
@@ -329,16 +356,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const uint32_t phase = (uint32_t)(it >> 1) & 1u;
       if (it + 1 < n_tiles) ok = issue_s(it + 1);
       if (!ok) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(p_full, (uint32_t)it & 1u) && mbar_wait(&v_full[s], phase));
+      ok = __all_sync(0xffffffffu, mbar_wait(&p_full[s], phase) && mbar_wait(&v_full[s], phase));
       if (!ok) break;
       fence_after_sync();
       if (issuer) {
 #pragma unroll
         for (int k = 0; k < BLOCK_N / UMMA_K; ++k) {
-          // P: 16 keys are 32 bytes of a row; V: 16 keys are 16 rows of 128 bytes
-          const uint64_t a = desc_k_major(p_smem + (k >> 2) * HALF_BYTES + (k & 3) * UMMA_K * 2);
+          // P from tensor memory: 16 keys are 8 columns; V: 16 keys are 16 rows of 128 bytes
           const uint64_t b = desc_mn_major(v_smem + s * KV_BYTES + k * UMMA_K * 128, HALF_BYTES);
-          umma(tmem_base + O_COL + s * D, a, b, idesc_o, k != 0 ? 1u : 0u);
+          umma_ts(tmem_base + O_COL, tmem_base + P_COL + s * P_COLS + k * (UMMA_K / 2), b, idesc_o,
+                  (it | k) != 0 ? 1u : 0u);
         }
         umma_commit(&o_full[s]);
         umma_commit(&v_free[s]);
@@ -362,25 +389,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int pos = pos0 + row;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
-    float o[HD];
-#pragma unroll
-    for (int c = 0; c < HD; ++c) o[c] = 0.f;
-    float m_run = -CUDART_INF_F, l_run = 0.f, alpha_pending = 1.f;
+    // O = sum of P V stays in tensor memory, the MMAs of every tile adding to it, in units of
+    // 2^m_ref of its row.  m_ref follows the row's maximum lazily: only when the maximum has
+    // grown by more than 8 (a factor 256, which bfloat16 P and float32 sums take easily) is the
+    // row of O scaled down and m_ref moved, which after the first tiles hardly ever happens.
+    // The quotient O / l does not depend on m_ref.
+    constexpr float LAZY = 8.f;
+    float m_ref = -CUDART_INF_F, l_run = 0.f;
     bool ok = true;
-
-    // O = O * alpha + PV of tile `it` (its scale alpha was fixed when its P was made)
-    auto take_pv = [&](int it) {
-      const int s = it & 1;
-      if (!mbar_wait(&o_full[s], (uint32_t)(it >> 1) & 1u)) return false;
-      fence_after_sync();
-      uint32_t g[HD];
-#pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) tmem_ld32(lane_base + O_COL + s * D + group * HD + c0, g + c0);
-      tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < HD; ++c) o[c] = fmaf(o[c], alpha_pending, __uint_as_float(g[c]));
-      return true;
-    };
 
     // A wait that runs out clears `ok`; the loop still runs to its end, skipping the work, so
     // that every thread meets the named barrier of every tile.
@@ -416,18 +432,36 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       row_max[(it & 1) * 256 + group * 128 + row] = tile_max;
       asm volatile("bar.sync 1, 256;" ::: "memory");
       tile_max = fmaxf(tile_max, row_max[(it & 1) * 256 + (group ^ 1) * 128 + row]);
-      const float m_new = fmaxf(m_run, tile_max * scale_log2);
-      const float alpha = (m_run == -CUDART_INF_F) ? 0.f : ex2(m_run - m_new);       // m_new >= m_run
-      // the tile before this one must be through PV before its P is overwritten; its PV is taken
-      // after this tile's P has gone out, while the tensor cores work on it
-      if (ok && it > 0 && !mbar_wait(&o_full[(it - 1) & 1], (uint32_t)((it - 1) >> 1) & 1u)) ok = false;
-      // p = exp2(s * scale - m), rounded to bfloat16 into this thread's 128-byte line of P
-      // (K-major, keys 64 * group ..); the sum in four running sums, folded in a fixed order
+      // both threads of a row work out the same m_ref from the same numbers
+      const float m_new = tile_max * scale_log2;
+      const bool move = m_new > m_ref + LAZY;                      // true too for the first key a row sees
+      const float factor = move ? ((m_ref == -CUDART_INF_F) ? 0.f : ex2(m_ref - m_new)) : 1.f;
+      if (move) m_ref = m_new;
+      // this tile's P buffer was read by the PV of two tiles ago (long done); O is scaled only
+      // after the PV of the tile before has been added to it
+      if (ok && it > 1 && !mbar_wait(&o_full[s], (uint32_t)((it - 2) >> 1) & 1u)) ok = false;
+      if (it > 0 && __any_sync(0xffffffffu, move)) {
+        if (ok && !mbar_wait(&o_full[(it - 1) & 1], (uint32_t)((it - 1) >> 1) & 1u)) ok = false;
+        if (__all_sync(0xffffffffu, ok)) {
+          fence_after_sync();
+          uint32_t og[HD];
+#pragma unroll
+          for (int q0 = 0; q0 < HD; q0 += 32) tmem_ld32(lane_base + O_COL + group * HD + q0, og + q0);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < HD; ++c) og[c] = __float_as_uint(__uint_as_float(og[c]) * factor);
+#pragma unroll
+          for (int q0 = 0; q0 < HD; q0 += 32) tmem_st32(lane_base + O_COL + group * HD + q0, og + q0);
+        }
+      }
+      // p = exp2(s * scale - m_ref), rounded to bfloat16, two keys a column, into this thread's 32
+      // columns of the tile's P buffer in tensor memory (keys 64 * group ..), from where the PV
+      // product takes it as its A operand; the sum in four running sums, folded in a fixed order
       float ps[4] = {0.f, 0.f, 0.f, 0.f};
-      const bool dead = m_new == -CUDART_INF_F;          // nothing seen yet by this row
-      const float neg_m = dead ? 0.f : -m_new;
-      uint8_t* line = p_ptr + group * HALF_BYTES + row * 128;
-      if (ok) {
+      const bool dead = m_ref == -CUDART_INF_F;          // nothing seen yet by this row
+      const float neg_m = dead ? 0.f : -m_ref;
+      uint32_t pk[HC / 2];
+      {
         const bool plain = full_tile & !dead;             // uniform over the block but for `dead`
 #pragma unroll
         for (int n0 = 0; n0 < HC; n0 += 8) {
@@ -446,10 +480,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           }
 #pragma unroll
           for (int j = 0; j < 8; ++j) ps[j & 3] += p[j];
-          *reinterpret_cast<uint4*>(line + (((n0 >> 3) ^ (row & 7)) << 4)) =
-              make_uint4(pack_bf16(p[0], p[1]), pack_bf16(p[2], p[3]), pack_bf16(p[4], p[5]), pack_bf16(p[6], p[7]));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) pk[(n0 >> 1) + j] = pack_bf16(p[2 * j], p[2 * j + 1]);
         }
       }
+      tmem_st32(lane_base + P_COL + s * P_COLS + group * (HC / 2), pk);
       const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
       // value rows of keys past the last position were never written: they must not be NaN,
       // since P is zero there and the MMA multiplies all the same
@@ -460,35 +495,40 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
           for (int q8 = 0; q8 < 8; ++q8) vrow[q8] = make_uint4(0u, 0u, 0u, 0u);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tmem_st_wait();
+      fence_before_sync();
       __syncwarp();
-      if (lane == 0 && ok) mbar_arrive(p_full);
-      // the tile before: its PV into the running row, with the scale its own P was made with
-      if (ok && it > 0 && !take_pv(it - 1)) ok = false;
-      l_run = fmaf(l_run, alpha, psum);
-      alpha_pending = alpha;
-      m_run = m_new;
+      if (lane == 0 && ok) mbar_arrive(&p_full[s]);
+      l_run = fmaf(l_run, factor, psum);
     }
-    if (ok && n_tiles > 0) ok = take_pv(n_tiles - 1);
     // the row's sum is that of its two threads
     row_max[group * 128 + row] = l_run;
     asm volatile("bar.sync 1, 256;" ::: "memory");
     const float l_row = group == 0 ? l_run + row_max[128 + row] : row_max[row] + l_run;
+    if (ok && n_tiles > 0 && !mbar_wait(&o_full[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) >> 1) & 1u)) ok = false;
     if (!ok) {
       *failed = 1;
       if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 840 + quad);
-    } else if (row < ntok) {
-      const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
-      __nv_bfloat16* dst = out + ((int64_t)(tok0 + row) * nq + h) * D + group * HD;
+    } else {
+      fence_after_sync();
+      uint32_t og[HD];
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
-        uint4 v;
-        v.x = pack_bf16(o[c] * inv, o[c + 1] * inv);
-        v.y = pack_bf16(o[c + 2] * inv, o[c + 3] * inv);
-        v.z = pack_bf16(o[c + 4] * inv, o[c + 5] * inv);
-        v.w = pack_bf16(o[c + 6] * inv, o[c + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + c) = v;
+      for (int q0 = 0; q0 < HD; q0 += 32) tmem_ld32(lane_base + O_COL + group * HD + q0, og + q0);
+      tmem_ld_wait();
+      if (row < ntok) {
+        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+        __nv_bfloat16* dst = out + ((int64_t)(tok0 + row) * nq + h) * D + group * HD;
+#pragma unroll
+        for (int c = 0; c < HD; c += 8) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(og[c]) * inv, __uint_as_float(og[c + 1]) * inv);
+          v.y = pack_bf16(__uint_as_float(og[c + 2]) * inv, __uint_as_float(og[c + 3]) * inv);
+          v.z = pack_bf16(__uint_as_float(og[c + 4]) * inv, __uint_as_float(og[c + 5]) * inv);
+          v.w = pack_bf16(__uint_as_float(og[c + 6]) * inv, __uint_as_float(og[c + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + c) = v;
+        }
       }
     }
   }
@@ -535,7 +575,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
            const int* block_table, int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
            float scale, int* err, cudaStream_t stream) {
   constexpr int KV_BYTES = HALVES * HALF_BYTES;
-  const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 2 * HALF_BYTES + 256 + 2048 + 1024;
+  const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 256 + 2048 + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,

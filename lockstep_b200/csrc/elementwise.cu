@@ -38,6 +38,32 @@ LS_API int ls_embed_gather(const int* ids, const void* table, int table_dtype, f
   return ls_launch_status();
 }
 
+// four gains as floats in one access, and four outputs out in one access (the row's and the
+// gain's starts are 16-byte aligned where these are used)
+template <typename TG>
+__device__ __forceinline__ float4 ls_load4(const TG* p) {
+  if constexpr (sizeof(TG) == 4) {
+    return *reinterpret_cast<const float4*>(p);
+  } else {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    return make_float4(__bfloat162float(a.x), __bfloat162float(a.y), __bfloat162float(b.x), __bfloat162float(b.y));
+  }
+}
+template <typename TO>
+__device__ __forceinline__ void ls_store4(TO* p, float a, float b, float c, float d) {
+  if constexpr (sizeof(TO) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+}
+
 // --------------------------------------------------------------------------
 // RMSNorm over float32 rows: y = x * rsqrt(mean(x^2) + eps) * gain
 // rows may be gathered through row_index (the rows whose logits are wanted).
@@ -46,6 +72,18 @@ LS_API int ls_embed_gather(const int* ids, const void* table, int table_dtype, f
 // them in registers between the two passes (rows up to 8192 wide; wider rows are
 // read twice), sums its squares in that order and the lanes by an xor tree.  The
 // order depends on the width alone.
+// y[0..4) = x * rstd * gain, in one access each for the gains and the outputs where `vec`
+template <typename TO, typename TG>
+__device__ __forceinline__ void rmsnorm_out4(TO* y, const TG* gain, const float* x, float rstd, bool vec) {
+  if (vec) {
+    const float4 gn = ls_load4<TG>(gain);
+    ls_store4<TO>(y, x[0] * rstd * gn.x, x[1] * rstd * gn.y, x[2] * rstd * gn.z, x[3] * rstd * gn.w);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) y[e] = ls_from_float<TO>(x[e] * rstd * ls_to_float<TG>(gain[e]));
+  }
+}
+
 template <typename TO, typename TG>
 __global__ void __launch_bounds__(128)
 rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
@@ -64,6 +102,8 @@ rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
   const float* xr = x + (int64_t)src * width;
   TO* yr = y + (int64_t)r * width;
   const bool vec = (width & 3) == 0 && ((uintptr_t)xr & 15) == 0;
+  // four outputs an access where the outputs and the gains allow it (this changes no sum)
+  const bool vec_out = ((uintptr_t)y & (4 * sizeof(TO) - 1)) == 0 && ((uintptr_t)gain & (4 * sizeof(TG) - 1)) == 0;
   float keep[KEEP];
   float ss = 0.f;
   if (vec) {
@@ -90,18 +130,12 @@ rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
 #pragma unroll
     for (int i = 0; i < KEEP / 4; ++i) {
       const int g = lane + 32 * i;
-      if (g < groups) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          yr[4 * g + e] = ls_from_float<TO>(keep[4 * i + e] * rstd * ls_to_float<TG>(gain[4 * g + e]));
-      }
+      if (g < groups) rmsnorm_out4<TO, TG>(yr + 4 * g, gain + 4 * g, keep + 4 * i, rstd, vec_out);
     }
     for (int g = lane + 32 * (KEEP / 4); g < groups; g += 32) {
       const float4 v = *reinterpret_cast<const float4*>(xr + 4 * g);
-      yr[4 * g + 0] = ls_from_float<TO>(v.x * rstd * ls_to_float<TG>(gain[4 * g + 0]));
-      yr[4 * g + 1] = ls_from_float<TO>(v.y * rstd * ls_to_float<TG>(gain[4 * g + 1]));
-      yr[4 * g + 2] = ls_from_float<TO>(v.z * rstd * ls_to_float<TG>(gain[4 * g + 2]));
-      yr[4 * g + 3] = ls_from_float<TO>(v.w * rstd * ls_to_float<TG>(gain[4 * g + 3]));
+      const float four[4] = {v.x, v.y, v.z, v.w};
+      rmsnorm_out4<TO, TG>(yr + 4 * g, gain + 4 * g, four, rstd, vec_out);
     }
   } else {
     for (int i = lane; i < width; i += 32)
