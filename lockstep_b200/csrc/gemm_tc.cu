@@ -1259,8 +1259,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
 template <int EPI, int FN, int CTAS, typename TC>
 __global__ void __launch_bounds__(320, 1)
 gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                    TC* __restrict__ C, int T, int N, int K, int64_t ldc, int kb_per_share, int shares,
-                    int tiles_t, int tiles_total, int* err) {
+                    const __grid_constant__ CUtensorMap map_c, int store_by_tma, TC* __restrict__ C, int T, int N,
+                    int K, int64_t ldc, int kb_per_share, int shares, int tiles_t, int tiles_total, int* err) {
   using S = RowsShape<EPI, FN, CTAS>;
   constexpr int COLS = 256;                      // columns of one accumulator region
   constexpr int OUT = FN / 2;                    // outputs per epilogue thread (features of its group)
@@ -1487,6 +1487,10 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         TC* cbase = C + (int64_t)t_warp * ldc + n_first;
 #pragma unroll
         for (int c0 = 0; c0 < OUT; c0 += CH) {
+          if (EPI != 1 && store_by_tma) {                      // the store before has read the staging chunk
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             float v[PER];
@@ -1525,6 +1529,17 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                       make_float4(add.x + old[i].x, add.y + old[i].y, add.z + old[i].z, add.w + old[i].w);
               }
             }
+          } else if (store_by_tma) {
+            // the chunk (its layout is the 128-byte swizzle) leaves as one TMA store, which this
+            // warp does not wait for: tokens past T and features past N are cut off by the map
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_c),
+                           "r"(smem_u32(mine)), "r"(n_first + c0), "r"(t_warp)
+                           : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
           } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -1547,6 +1562,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
     }
+    if (EPI != 1 && store_by_tma && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   }
   fence_before_sync();
   __syncthreads();
@@ -1755,6 +1771,11 @@ template <int EPI, int FN, int CTAS, typename TC>
 int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, int N, int K, int64_t ldc,
                 const Plan& plan, int* err, cudaStream_t stream) {
   using S = RowsShape<EPI, FN, CTAS>;
+  // bfloat16 outputs that are not added to leave by TMA stores, where the map can be made
+  CUtensorMap mc = mx;
+  int store_by_tma = 0;
+  if (EPI != 1 && sizeof(TC) == 2 && ((uintptr_t)C & 15) == 0 && (ldc % 8) == 0 && make_map(&mc, C, T, N, ldc, 32))
+    store_by_tma = 1;
   static bool configured = false;
   static int resident = 0;                       // blocks, or pairs of them, that run at one time
   if (!configured) {
@@ -1781,8 +1802,8 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, in
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ls_dependent_launch ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_rows_kernel<EPI, FN, CTAS, TC>, mw, mx, (TC*)C, T, N, K, ldc,
-                                     plan.kb_per_share, plan.shares, tiles_t, tiles, err);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_rows_kernel<EPI, FN, CTAS, TC>, mw, mx, mc, store_by_tma, (TC*)C, T,
+                                     N, K, ldc, plan.kb_per_share, plan.shares, tiles_t, tiles, err);
   if (e != cudaSuccess) return (int)e;
   return ls_launch_status();
 }
