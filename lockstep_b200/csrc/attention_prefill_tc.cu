@@ -236,6 +236,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int tile_end = pos_last / BLOCK_N + 1;
   const int n_tiles = tile_end - tile_first;
 
+  const int rows_per_box = page_size < BLOCK_N ? page_size : BLOCK_N;
+  const int boxes = BLOCK_N / rows_per_box;              // at most 16: lane b fetches box b of a tile
+  // the page of this lane's box of tile `it`, looked up one tile ahead (not yet checked)
+  auto lookup = [&](int it) {
+    int page = 0;
+    if (it < n_tiles && lane < boxes) {
+      int key = (tile_first + it) * BLOCK_N + lane * rows_per_box;
+      if (key > pos_last) key = pos_last;                // past the last key: any page that exists
+      if (key < key_lo) key = key_lo;                    // behind the window: pages may have been given back
+      page = table_row[key / page_size];               // checked where it is used: the load stays in flight
+    }
+    return page;
+  };
+  // the block table is the step's input, older than the kernel before this one; the look-up's trip
+  // to memory runs under the set-up below
+  int page = (warp == 0 || warp == 10) ? lookup(0) : 0;
+
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) {
@@ -264,25 +281,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const int rows_per_box = page_size < BLOCK_N ? page_size : BLOCK_N;
-  const int boxes = BLOCK_N / rows_per_box;              // at most 16: lane b fetches box b of a tile
-  // the page of this lane's box of tile `it`, looked up one tile ahead
-  auto lookup = [&](int it) {
-    int page = 0;
-    if (it < n_tiles && lane < boxes) {
-      int key = (tile_first + it) * BLOCK_N + lane * rows_per_box;
-      if (key > pos_last) key = pos_last;                // past the last key: any page that exists
-      if (key < key_lo) key = key_lo;                    // behind the window: pages may have been given back
-      page = table_row[key / page_size];
-      if (page < 0 || page >= num_pages) {
-        ls_record_fault(err, LS_DEV_PAGE_RANGE, key);
-        page = 0;
-      }
-    }
-    return page;
-  };
-  // the block table is the step's input, older than the kernel before this one
-  int page = (warp == 0 || warp == 10) ? lookup(0) : 0;
   ls_dependency_wait();                 // q and this step's keys and values come from the kernel before
 
   if (warp == 0 || warp == 10) {
@@ -302,7 +300,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int s = it & 1;
       const uint32_t phase = (uint32_t)(it >> 1) & 1u;
       const int c0 = (tile_first + it) * BLOCK_N;
-      const int page_next = lookup(it + 1);
       bool ok = *failed == 0 && mbar_wait(&free_bar[s], phase ^ 1u);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -313,6 +310,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (lane == 0) mbar_expect_tx(&full_bar[s], KV_BYTES);
       __syncwarp();
       if (lane < boxes) {
+        if (page < 0 || page >= num_pages) {
+          ls_record_fault(err, LS_DEV_PAGE_RANGE, c0 + lane * rows_per_box);
+          page = 0;
+        }
         const int in_page = ((c0 + lane * rows_per_box) % page_size) / rows_per_box * rows_per_box;
         const int y = ((page * 2 + (keys ? 0 : 1)) * nkv + kvh) * page_size + in_page;
 #pragma unroll
@@ -320,7 +321,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           tma_load_2d(dst_base + (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + lane * rows_per_box * 128), &map_kv,
                       hh * 64, y, &full_bar[s]);
       }
-      page = page_next;
+      page = lookup(it + 1);            // after this tile's loads have gone out
     }
   } else if (warp == 1) {
     // ---- MMA issue: the whole warp walks the loop and one elected lane issues, so that the
