@@ -3,8 +3,10 @@
 //
 // Orientation: up to 128 tokens, the weight tile is the MMA's M side (128 rows of
 // W) and the tokens are its N side (16..128 per tile), so a batch of one decoded
-// token wastes no rows of the MMA; more tokens are the M side themselves (128 a
-// tile, gemm_tc_rows_kernel), whose outputs then lie side by side in a thread.
+// token wastes no rows of the MMA; more tokens are the M side themselves
+// (gemm_tc_rows_kernel: 256 a tile on a pair of blocks, tcgen05 cta_group::2, each
+// block with its 128 tokens and half of the weight rows), whose outputs then lie
+// side by side in a thread.
 // Either way an output element is the same dot product, accumulated in the same
 // order, and the two give the same bits.  A block walks its share of K in
 // ascending 64-element blocks.  Where the weight gives too few tiles to occupy
@@ -16,13 +18,14 @@
 // The number of shares is a function of the weight's shape alone
 // (ls_gemm_tc_k_shares), so an output element is the same sum whatever the batch.
 //
-// Roles inside a block (192 threads): warp 0 issues TMA loads into a ring of
-// shared-memory stages, warp 1 issues the MMAs and commits stages back, warps
-// 2..5 read the accumulator from tensor memory and write the epilogue:
+// Roles inside a block (192 threads; 320 with eight epilogue warps): warp 0 issues
+// TMA loads into a ring of shared-memory stages, warp 1 walks the loop of the MMAs
+// whole and one elected lane of it issues them and commits stages back, warps
+// 2.. read the accumulator from tensor memory and write the epilogue:
 //   0 store     C[t, n]  = acc                      (bfloat16 or float32)
 //   1 residual  C[t, n] += acc                      (float32, in place)
 //   2 silu-mul  C[t, n]  = silu(acc_gate) * acc_up  (W holds gate rows [0, N)
-//                                                    and up rows [N, 2N))
+//                                                    and up rows [N, 2N); silu_mul())
 //   3 q/k/v     the rows of W are q, k and v heads: each head of a token is
 //               rounded to bfloat16 and goes where ls_qkv_head_store puts it (q
 //               normed and rotated, k normed and rotated into its cache page, v
