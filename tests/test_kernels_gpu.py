@@ -268,6 +268,32 @@ def test_attention_finds_one_far_key(dtype, d):
                 assert (got[0, h] - vv[far, h // 2].float()).abs().max() <= 2e-2, (far, decode_kernel)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+def test_prefill_attention_follows_rising_maxima(d):
+    """Scores that grow from key tile to key tile: by less than the tensor-core kernel's lazy threshold (its
+    reference maximum stays behind and P exceeds 1), by more (the row of O in tensor memory is scaled), and
+    far more (the scaled part all but vanishes).  Every row sees a different prefix of the steps."""
+    k = K()
+    nq, nkv, page, total = 4, 2, 16, 640
+    g = torch.Generator().manual_seed(d)
+    direction = torch.randn(d, generator=g)
+    direction = direction / direction.norm()
+    # score of key j for every query: level[j] (natural units, scale 1) plus a little noise
+    level = torch.zeros(total)
+    level[128:256] = 3.0        # + 4.3 in powers of two: no move
+    level[256:384] = 10.0       # + 10: a move
+    level[384:512] = 11.0       # + 1.4: none
+    level[512:] = 40.0          # + 42: what was there before counts for nothing
+    q = (torch.randn(total, nq, d, generator=g) * 0.05 + direction * 2.0).to(torch.bfloat16)
+    kk = (torch.randn(total, nkv, d, generator=g) * 0.05 + direction * (level / 2.0).view(-1, 1, 1)).to(torch.bfloat16)
+    vv = torch.randn(total, nkv, d, generator=g).to(torch.bfloat16)
+    want = plain.causal_attention(q.double(), kk.double(), vv.double(), 1.0, window=0).float()
+    pages, ids = paged_from_dense(kk, vv, page, 64, seed=1)
+    for lo, hi in [(0, 640), (200, 640), (500, 530)]:
+        got = run_attention(k, q[lo:hi], pages, ids, lo, 0, 1.0, "prefill_tc")
+        assert (got - want[lo:hi]).abs().max() <= 2e-2, (lo, hi)
+
+
 def test_argmax_ties_go_to_lowest_id():
     k = K()
     logits = torch.full((3, 1001), -1.0)
