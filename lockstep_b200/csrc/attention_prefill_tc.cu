@@ -16,13 +16,13 @@
 //                 row's maximum lazily (when it has grown by more than 8, a factor 256, the
 //                 row of O is scaled and m_ref moved); O / l does not depend on m_ref.
 //
-// Eleven warps: warp 0 fetches Q once and the key tiles, warp 10 the value tiles, into
+// Nineteen warps: warp 0 fetches Q once and the key tiles, warp 18 the value tiles, into
 // two stages each (a lane per page of a tile: look-up and TMA box), warp 1 issues the MMAs
 // (S of the next tile before PV of this one, so the tensor cores work while the
-// softmax runs; S and P have two buffers each in tensor memory), warps 2..9 are the
-// softmax, two threads per row: one has the first 64 keys of a tile and the first
-// half of the head's dimensions, the other the rest; they share the row's maximum
-// through shared memory.  Every wait is bounded; a wait that runs out records
+// softmax runs; S and P have two buffers each in tensor memory), warps 2..17 are the
+// softmax, four threads per row: each has 32 keys of a tile and a quarter of the head's
+// dimensions; they share the row's maximum through shared memory.  (With two threads per
+// row the softmax warps, two to a scheduler, were short of issue slots.)  Every wait is bounded; a wait that runs out records
 // LS_DEV_WAIT_TIMEOUT and the block winds down and frees its tensor memory.
 #include <cuda.h>
 #include <math_constants.h>
@@ -38,6 +38,9 @@ constexpr int STAGES = 2;
 constexpr int UMMA_K = 16;
 constexpr int HALF_BYTES = 128 * 128;     // 128 rows of 64 elements
 constexpr uint32_t TMEM_COLS = 512;
+constexpr int GROUPS = 4;                 // softmax threads per row (warpgroups of the softmax)
+constexpr int THREADS = (3 + 4 * GROUPS) * 32;
+constexpr int V_WARP = 2 + 4 * GROUPS;    // the warp that fetches the value tiles
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -166,6 +169,38 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(taddr)
+      : "memory");
+}
+// N columns (a multiple of 16) of this thread's lane to or from registers
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r) {
+  static_assert(N % 16 == 0, "columns in sixteens");
+#pragma unroll
+  for (int c = 0; c + 32 <= N; c += 32) tmem_ld32(taddr + c, r + c);
+  if constexpr (N % 32) tmem_ld16(taddr + N - 16, r + N - 16);
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t* r) {
+  static_assert(N % 16 == 0, "columns in sixteens");
+#pragma unroll
+  for (int c = 0; c + 32 <= N; c += 32) tmem_st32(taddr + c, r + c);
+  if constexpr (N % 32) tmem_st16(taddr + N - 16, r + N - 16);
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_before_sync() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -187,7 +222,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // HALVES = d / 64.  Shared memory: Q [HALVES][128 rows][128 B]; two stages of K and of V
 // [HALVES][128 keys][128 B]; barriers.  Tensor memory: two S buffers, O, two P buffers (bfloat16).
 template <int HALVES>
-__global__ void __launch_bounds__(352, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             __nv_bfloat16* __restrict__ out, const int* __restrict__ work,
                             const int* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size,
@@ -218,7 +253,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint64_t* o_full = bars + 14;        // [2] PV of a tile has been added to O (and its P may be overwritten)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile uint32_t* failed = tmem_slot + 1;
-  float* row_max = reinterpret_cast<float*>(bars + 32);   // [2 tiles][2 groups][128 rows], then reused for l
+  float* row_max = reinterpret_cast<float*>(bars + 32);   // [2 tiles][GROUPS][128 rows], then reused for l
 
   // blocks are handed out head-fastest, so the tiles with the longest context (listed
   // first) start first for every head and the short ones fill the tail
@@ -251,7 +286,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   };
   // the block table is the step's input, older than the kernel before this one; the look-up's trip
   // to memory runs under the set-up below
-  int page = (warp == 0 || warp == 10) ? lookup(0) : 0;
+  int page = (warp == 0 || warp == V_WARP) ? lookup(0) : 0;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -261,11 +296,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&k_free[s], 1);
       mbar_init(&v_free[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_free[s], 8);
+      mbar_init(&s_free[s], 4 * GROUPS);
       mbar_init(&o_full[s], 1);
     }
-    mbar_init(&p_full[0], 8);
-    mbar_init(&p_full[1], 8);
+    mbar_init(&p_full[0], 4 * GROUPS);
+    mbar_init(&p_full[1], 4 * GROUPS);
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -283,7 +318,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t tmem_base = *tmem_slot;
   ls_dependency_wait();                 // q and this step's keys and values come from the kernel before
 
-  if (warp == 0 || warp == 10) {
+  if (warp == 0 || warp == V_WARP) {
     // ---- producers ----
     if (warp == 0 && lane == 0) {
       mbar_expect_tx(q_full, KV_BYTES);
@@ -377,12 +412,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       *failed = 1;
       if (issuer) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 820);
     }
-  } else if (warp < 10) {
-    // ---- softmax: two threads per row (a token, lane `row` of tensor memory): the thread of
-    // group 0 (warps 2..5) has keys 0..63 of a tile and the first half of the head's
-    // dimensions, the thread of group 1 (warps 6..9) keys 64..127 and the second half ----
-    constexpr int HC = BLOCK_N / 2;               // keys of a tile per thread
-    constexpr int HD = D / 2;                     // output dimensions per thread
+  } else if (warp < V_WARP) {
+    // ---- softmax: GROUPS threads per row (a token, lane `row` of tensor memory): the thread of
+    // group g (warps 2 + 4 g .. 5 + 4 g) has keys 32 g .. 32 g + 31 of a tile and the g-th
+    // quarter of the head's dimensions ----
+    constexpr int HC = BLOCK_N / GROUPS;          // keys of a tile per thread
+    constexpr int HD = D / GROUPS;                // output dimensions per thread
+    constexpr int ROWS = 128 * GROUPS;            // threads of the softmax
     const int quad = warp & 3;
     const int group = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
@@ -408,8 +444,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       fence_after_sync();
       // this thread's 64 scores into registers; the buffer is free once all have theirs
       uint32_t g[HC];
-      tmem_ld32(lane_base + S_COL + s * BLOCK_N + group * HC, g);
-      tmem_ld32(lane_base + S_COL + s * BLOCK_N + group * HC + 32, g + 32);
+#pragma unroll
+      for (int q0 = 0; q0 < HC; q0 += 32) tmem_ld32(lane_base + S_COL + s * BLOCK_N + group * HC + q0, g + q0);
       tmem_ld_wait();
       fence_before_sync();
       __syncwarp();
@@ -430,9 +466,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       // the row's maximum is that of its two threads
       float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      row_max[(it & 1) * 256 + group * 128 + row] = tile_max;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      tile_max = fmaxf(tile_max, row_max[(it & 1) * 256 + (group ^ 1) * 128 + row]);
+      row_max[(it & 1) * ROWS + group * 128 + row] = tile_max;
+      asm volatile("bar.sync 1, %0;" ::"n"(ROWS) : "memory");
+#pragma unroll
+      for (int o = 0; o < GROUPS; ++o) tile_max = fmaxf(tile_max, row_max[(it & 1) * ROWS + o * 128 + row]);
       // both threads of a row work out the same m_ref from the same numbers
       const float m_new = tile_max * scale_log2;
       const bool move = m_new > m_ref + LAZY;                      // true too for the first key a row sees
@@ -446,13 +483,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (__all_sync(0xffffffffu, ok)) {
           fence_after_sync();
           uint32_t og[HD];
-#pragma unroll
-          for (int q0 = 0; q0 < HD; q0 += 32) tmem_ld32(lane_base + O_COL + group * HD + q0, og + q0);
+          tmem_ld_cols<HD>(lane_base + O_COL + group * HD, og);
           tmem_ld_wait();
 #pragma unroll
           for (int c = 0; c < HD; ++c) og[c] = __float_as_uint(__uint_as_float(og[c]) * factor);
-#pragma unroll
-          for (int q0 = 0; q0 < HD; q0 += 32) tmem_st32(lane_base + O_COL + group * HD + q0, og + q0);
+          tmem_st_cols<HD>(lane_base + O_COL + group * HD, og);
         }
       }
       // p = exp2(s * scale - m_ref), rounded to bfloat16, two keys a column, into this thread's 32
@@ -485,7 +520,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           for (int j = 0; j < 4; ++j) pk[(n0 >> 1) + j] = pack_bf16(p[2 * j], p[2 * j + 1]);
         }
       }
-      tmem_st32(lane_base + P_COL + s * P_COLS + group * (HC / 2), pk);
+      tmem_st_cols<HC / 2>(lane_base + P_COL + s * P_COLS + group * (HC / 2), pk);
       const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
       // value rows of keys past the last position were never written: they must not be NaN,
       // since P is zero there and the MMA multiplies all the same
@@ -506,8 +541,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     // the row's sum is that of its two threads
     row_max[group * 128 + row] = l_run;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    const float l_row = group == 0 ? l_run + row_max[128 + row] : row_max[row] + l_run;
+    asm volatile("bar.sync 1, %0;" ::"n"(ROWS) : "memory");
+    float l_row = row_max[row];                    // the same sum in the same order in each of the row's threads
+#pragma unroll
+    for (int o = 1; o < GROUPS; ++o) l_row += row_max[o * 128 + row];
     if (ok && n_tiles > 0 && !mbar_wait(&o_full[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) >> 1) & 1u)) ok = false;
     if (!ok) {
       *failed = 1;
@@ -515,8 +552,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     } else {
       fence_after_sync();
       uint32_t og[HD];
-#pragma unroll
-      for (int q0 = 0; q0 < HD; q0 += 32) tmem_ld32(lane_base + O_COL + group * HD + q0, og + q0);
+      tmem_ld_cols<HD>(lane_base + O_COL + group * HD, og);
       tmem_ld_wait();
       if (row < ntok) {
         const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
@@ -576,7 +612,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
            const int* block_table, int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
            float scale, int* err, cudaStream_t stream) {
   constexpr int KV_BYTES = HALVES * HALF_BYTES;
-  const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 256 + 2048 + 1024;
+  const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 256 + 2 * 128 * GROUPS * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -585,7 +621,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
     configured = true;
   }
   dim3 grid(nq, n_work);
-  ls_launch(attention_prefill_tc_kernel<HALVES>, grid, 352, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work,
+  ls_launch(attention_prefill_tc_kernel<HALVES>, grid, THREADS, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work,
             block_table, table_stride, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
   return ls_launch_status();
 }
