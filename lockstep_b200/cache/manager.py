@@ -272,6 +272,12 @@ class CacheManager:
     def can_reserve(self, uid: str, total_tokens: int) -> bool:
         return all(g.pages_short(uid, total_tokens) <= g.allocator.free_pages for g in self.paged)
 
+    def can_reserve_all(self, wants) -> bool:
+        """True if every (uid, total_tokens) of ``wants`` can be reserved, one after the
+        other, from the pages that are free now."""
+        return all(sum(g.pages_short(uid, total) for uid, total in wants) <= g.allocator.free_pages
+                   for g in self.paged)
+
     def reserve(self, uid: str, total_tokens: int) -> None:
         """Make room for ``total_tokens`` of ``uid`` in every paged group, or take nothing."""
         if total_tokens > self.max_seq_len:

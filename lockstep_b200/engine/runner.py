@@ -13,7 +13,7 @@ from pathlib import Path
 import torch
 
 from .. import kernels as K
-from ..cache import CacheManager
+from ..cache import CacheManager, OutOfPages
 from ..config import load_config
 from ..parts import Runtime
 from ..weights import load_weights
@@ -139,7 +139,18 @@ class ModelRunner:
                 raise KeyError(f"request {e.uid!r} is not open")
             if e.start != have:
                 raise ValueError(f"{e.uid}: portion starts at {e.start} but the cache holds {have} tokens")
-            self.cache.reserve(e.uid, e.start + len(e.tokens))
+            if not e.tokens:
+                raise ValueError(f"{e.uid}: an entry must bring at least one token")
+            if any(not 0 <= w < len(e.tokens) for w in e.want):
+                raise ValueError(f"{e.uid}: a wanted place lies outside its {len(e.tokens)} tokens")
+            if e.start + len(e.tokens) > self.max_seq_len:
+                raise ValueError(f"{e.uid}: {e.start + len(e.tokens)} tokens exceed max_seq_len {self.max_seq_len}")
+        # every entry is valid: only now are pages taken, for all entries or for none
+        wants = [(e.uid, e.start + len(e.tokens)) for e in entries]
+        if not self.cache.can_reserve_all(wants):
+            raise OutOfPages(f"the step needs more pages than the {self.cache.free_pages()} that are free")
+        for uid, total in wants:
+            self.cache.reserve(uid, total)
         self.cache.sync()
         slots = [self.cache.slots[e.uid] for e in entries]
         logits = None

@@ -113,7 +113,7 @@ class Scheduler:
         return self.cache.peak_pages(tokens, min(tokens, self.max_step_tokens))
 
     def _reclaimable(self) -> int:
-        return len(self.prefix.evictable(self.cache.paged[0])) if self.prefix else 0
+        return self.prefix.reclaimable(self.cache.paged[0]) if self.prefix else 0
 
     def _state(self) -> SchedulerState:
         return SchedulerState(
@@ -310,6 +310,8 @@ class Scheduler:
 
         if self.audit_enabled:
             self.cache.audit()
+            if self.prefix is not None:
+                self.prefix.audit()
 
         for request in owners:
             if len(request.generated) >= request.max_new_tokens or request.generated[-1] in self.eos:
@@ -334,11 +336,15 @@ class Scheduler:
         if len(launched["owners"]) != len(planned) or len(planned) != len(self.running):
             return False
         for request, take in planned:
-            # after the token under way it must still want another, and fit without making room
+            # after the token under way it must still want another
             if take != 1 or len(request.generated) + 2 > request.max_new_tokens:
                 return False
-            if request.kv_len + 1 > self.cache.max_seq_len or not self.cache.can_reserve(request.uid, request.kv_len + 1):
+            if request.kv_len + 1 > self.cache.max_seq_len:
                 return False
+        # and all of them together must fit without making room: several requests may cross a
+        # page edge in the same step, so the pages are counted for the whole step, group by group
+        if not self.cache.can_reserve_all([(request.uid, request.kv_len + 1) for request, _ in planned]):
+            return False
         entries = [StepEntry(uid=r.uid, tokens=[0], start=r.kv_len, want=[0]) for r, _ in planned]
         return self.backend.can_step_ahead(entries)
 

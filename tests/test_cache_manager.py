@@ -136,7 +136,7 @@ def test_prefix_index_shares_whole_pages():
     assert idx.insert(toks, g.seqs["a"].pages, g) == 2      # two whole pages
     m.release("a")
     m.audit()
-    assert g.allocator.free_pages == 14 and idx.evictable(g) == [0, 1]
+    assert g.allocator.free_pages == 14 and idx.evictable(g) == [1] and idx.reclaimable(g) == 2
     hit, pages = idx.lookup(toks[:9] + [99, 98])
     assert hit == 8 and pages == [0, 1]
     m.create("b")
@@ -145,7 +145,45 @@ def test_prefix_index_shares_whole_pages():
     m.audit()
     assert idx.evictable(g) == []                          # a running request holds them
     m.release("b")
-    assert idx.evict(0, g) and idx.evict(1, g)
+    with pytest.raises(ValueError):
+        idx.evict(0, g)                                    # page 1 comes after it in the chain
+    assert idx.evict(1, g) and idx.evictable(g) == [0] and idx.evict(0, g)
     m.audit()
     assert g.allocator.free_pages == 16
     assert idx.lookup(toks)[0] == 0
+
+
+def test_prefix_eviction_leaves_no_unreachable_page():
+    """Chains that share their first pages are evicted from their ends: whatever the order,
+    every indexed page stays reachable by ``lookup`` and no page stays pinned for nothing."""
+    rng = random.Random(4)
+    m = manager([FULL], pages=32, page=4)
+    g = m.paged[0]
+    idx = PrefixIndex(page_size=4)
+    stem = list(range(8))
+    chains = [stem + [50 + i] * 4 + [60 + i] * 4 for i in range(3)]
+    for i, toks in enumerate(chains):
+        uid = f"r{i}"
+        m.create(uid)
+        hit, pages = idx.lookup(toks)
+        g.adopt(uid, pages)
+        m.lengths[uid] = hit
+        m.reserve(uid, len(toks))
+        idx.insert(toks, g.seqs[uid].pages, g)
+        m.release(uid)
+    idx.audit()
+    assert len(idx.entries) == 2 + 3 * 2 and idx.reclaimable(g) == 8
+    while idx.entries:
+        offered = idx.evictable(g)
+        assert offered, "pages are indexed but none is offered"
+        idx.evict(rng.choice(offered), g)
+        idx.audit()
+        m.audit()
+        for toks in chains:                 # what lookup finds is exactly what is still indexed
+            hit, pages = idx.lookup(toks)
+            assert len(pages) == hit // 4
+        reachable = set()
+        for toks in chains:
+            reachable.update(idx.lookup(toks)[1])
+        assert reachable == {e.page for e in idx.entries.values()}
+    assert g.allocator.free_pages == 32

@@ -303,3 +303,19 @@ def test_run_ahead_stops_for_arrivals_and_for_pages():
         assert out[r.uid] == expected(r.prompt, 12)
     assert sched.stats["preemptions"] > 0
     sched.cache.audit()
+
+
+def test_run_ahead_counts_pages_for_the_whole_step():
+    """Two requests of equal length cross a page edge in the same step with one page free:
+    the step is not launched ahead (each alone would fit, both do not); the planned path
+    preempts and the tokens are those of a run without run-ahead."""
+    def reqs():
+        return [Request(uid=f"p{i}", prompt=[2 + i, 3, 4, 5], max_new_tokens=12) for i in range(2)]
+    want, plain_sched, _ = run(reqs(), pages=5, page=4)
+    out, sched, backend = run_ahead(reqs(), pages=5, page=4)
+    assert out == want
+    for r in reqs():
+        assert out[r.uid] == expected(r.prompt, 12)
+    assert sched.stats["preemptions"] > 0 and sched.stats["preemptions"] == plain_sched.stats["preemptions"]
+    sched.cache.audit()
+    assert sched.cache.free_pages() == sched.cache.total_pages()
