@@ -42,9 +42,18 @@ class _Seq:
     shared: int = 0                                  # leading pages adopted from the prefix index
 
 
+# What a freed page is filled with when ``poison_freed_pages`` is on: finite and far outside
+# anything a model computes.  A key or value of a page that was given back, read with any
+# weight but zero, then shows in the result at once.  (Not NaN, as in LockStep's
+# engine/kv/paged.py:103-113: these kernels load whole tiles and give the keys past a
+# request's length the weight zero, and 0 x NaN would flag a read that is harmless.)
+POISON = 1.0e30
+
+
 class PagedGroup:
     def __init__(self, need: CacheNeed, entries: list[int], num_pages: int, page_size: int,
-                 max_live: int, max_pages_per_seq: int, dtype, device, allocate: bool = True):
+                 max_live: int, max_pages_per_seq: int, dtype, device, allocate: bool = True,
+                 poison_freed_pages: bool = False):
         self.need, self.entries = need, list(entries)
         self.page_size, self.window = int(page_size), int(need.window)
         self.allocator = PageAllocator(num_pages)
@@ -61,6 +70,30 @@ class PagedGroup:
         self.seqs: dict[str, _Seq] = {}
         self._dirty: set[int] = set()
         self.pinned: dict[int, int] = {}
+        self.poison = bool(poison_freed_pages)
+        self.poisoned = 0
+
+    def _give_back(self, page: int) -> None:
+        """Drop one reference on ``page``; a page nobody holds any more is poisoned (debug option)."""
+        if self.allocator.release(page) and self.poison:
+            self.poisoned += 1
+            if self.pages is not None:
+                self.pages[:, page].fill_(POISON)
+
+    def assert_exclusive(self, uid: str, first_token: int, last_token: int) -> None:
+        """The pages ``uid`` is about to write (tokens first..last) are held by it alone: sharing
+        is by whole pages of a prefix, so a write never lands in a shared page
+        (LockStep: engine/kv/paged.py:162-181)."""
+        seq = self.seqs[uid]
+        for logical in range(first_token // self.page_size, last_token // self.page_size + 1):
+            page = seq.pages[logical] if logical < len(seq.pages) else -1
+            if page < 0:
+                raise AuditFailure(f"{uid} is about to write token {first_token}.. into logical page {logical}, "
+                                   "which it does not hold")
+            if self.allocator.refcount[page] != 1:
+                raise AuditFailure(
+                    f"{uid} is about to write physical page {page}, which has {self.allocator.refcount[page]} "
+                    f"holders ({self.pinned.get(page, 0)} of them the prefix index)")
 
     # -- accounting ---------------------------------------------------------
     def first_needed_page(self, kv_len_after: int, first_query_pos: int | None = None) -> int:
@@ -101,7 +134,7 @@ class PagedGroup:
         for logical in range(min(first, len(seq.pages))):
             page = seq.pages[logical]
             if page >= 0:
-                self.allocator.release(page)
+                self._give_back(page)
                 seq.pages[logical] = -1
                 self.table_host[seq.slot, logical] = -1
                 self._dirty.add(seq.slot)
@@ -128,7 +161,7 @@ class PagedGroup:
         seq = self.seqs.pop(uid)
         for page in seq.pages:
             if page >= 0:
-                self.allocator.release(page)
+                self._give_back(page)
         self.table_host[seq.slot, :] = -1
         self._dirty.add(seq.slot)
 
@@ -144,7 +177,7 @@ class PagedGroup:
             del self.pinned[page]
         else:
             self.pinned[page] = held - 1
-        self.allocator.release(page)
+        self._give_back(page)
 
     def sync(self) -> None:
         """Bring the device block table up to date (rows that changed)."""
@@ -194,11 +227,13 @@ class CacheManager:
     ``needs``: for every cache entry of the model's schedule (index = entry),
     the ``CacheNeed`` of the mixer that writes it (None for a mixer that keeps
     nothing).  ``allocate=False`` builds the books without device memory (for
-    host-side tests and planning).
+    host-side tests and planning).  ``poison_freed_pages`` (a debugging aid) fills a page
+    with ``POISON`` when its last holder gives it back.
     """
 
     def __init__(self, needs: list[CacheNeed | None], num_pages: int, page_size: int, max_live: int,
-                 max_seq_len: int, dtype=torch.float32, device="cpu", allocate: bool = True):
+                 max_seq_len: int, dtype=torch.float32, device="cpu", allocate: bool = True,
+                 poison_freed_pages: bool = False):
         self.page_size, self.max_live = int(page_size), int(max_live)
         self.max_seq_len = int(max_seq_len)
         self.device = torch.device(device)
@@ -217,7 +252,7 @@ class CacheManager:
             need = need_of[key]
             if need.kind == "paged_kv":
                 group = PagedGroup(need, entries, num_pages, page_size, max_live, max_pages_per_seq,
-                                   dtype, self.device, allocate)
+                                   dtype, self.device, allocate, poison_freed_pages)
                 self.paged.append(group)
             elif need.kind == "state":
                 group = StateGroup(need, entries, max_live, self.device, allocate)
@@ -288,6 +323,11 @@ class CacheManager:
             raise OutOfPages(f"{uid}: not enough free pages for {total_tokens} tokens (short by group: {short})")
         for g in self.paged:
             g.reserve(uid, total_tokens)
+
+    def assert_exclusive(self, uid: str, first_token: int, last_token: int) -> None:
+        """Every page that tokens first..last of ``uid`` are written to is held by ``uid`` alone."""
+        for g in self.paged:
+            g.assert_exclusive(uid, first_token, last_token)
 
     def advance(self, uid: str, kv_len: int) -> int:
         """Record that ``uid`` now holds ``kv_len`` tokens; windowed groups give

@@ -20,8 +20,6 @@
 
 #include "common.cuh"
 
-#define LS_SPLIT 256
-
 namespace {
 
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -420,7 +418,7 @@ int launch(const CUtensorMap& map, const void* q, float* part_acc, float* part_m
     configured = true;
   }
   dim3 grid(n_work, nkv);
-  ls_launch(attention_decode_mma_kernel<HALVES>, grid, WARPS * 32, smem, stream, 
+  LS_COUNT(LS_K_ATTENTION_DECODE_MMA), ls_launch(attention_decode_mma_kernel<HALVES>, grid, WARPS * 32, smem, stream, 
       map, (const __nv_bfloat16*)q, part_acc, part_ml, work, block_table, table_stride, nq, nkv, page_size,
       num_pages, window, scale, err);
   return ls_launch_status();
@@ -457,4 +455,11 @@ LS_API int ls_attention_decode_mma(const void* q, const void* pages, float* part
                      num_pages, window, scale, err, stream);
   return launch<2>(map, q, part_acc, part_ml, work, n_work, block_table, table_stride, nq, nkv, page_size,
                    num_pages, window, scale, err, stream);
+}
+
+LS_API const char* ls_constants_attention_decode_mma() {
+  static char buf[256];
+  static const LsConstant c[] = {{"attention_decode_mma.split_keys", LS_SPLIT}, {"attention_decode_mma.warp_keys", CHUNK},
+                                 {"attention_decode_mma.warps", WARPS}};
+  return ls_format_constants(buf, sizeof buf, c, (int)(sizeof c / sizeof c[0]));
 }

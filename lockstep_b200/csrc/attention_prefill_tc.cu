@@ -621,7 +621,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
     configured = true;
   }
   dim3 grid(nq, n_work);
-  ls_launch(attention_prefill_tc_kernel<HALVES>, grid, THREADS, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work,
+  LS_COUNT(LS_K_ATTENTION_PREFILL_TC), ls_launch(attention_prefill_tc_kernel<HALVES>, grid, THREADS, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work,
             block_table, table_stride, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
   return ls_launch_status();
 }
@@ -653,4 +653,11 @@ LS_API int ls_attention_prefill_tc(const void* q, const void* pages, void* out, 
                      window, scale, err, stream);
   return launch<2>(map_q, map_kv, out, work, n_work, block_table, table_stride, nq, nkv, page_size, num_pages,
                    window, scale, err, stream);
+}
+
+LS_API const char* ls_constants_attention_prefill_tc() {
+  static char buf[256];
+  static const LsConstant c[] = {{"attention_prefill_tc.queries", BLOCK_M}, {"attention_prefill_tc.keys", BLOCK_N},
+                                 {"attention_prefill_tc.softmax_threads_per_row", GROUPS}};
+  return ls_format_constants(buf, sizeof buf, c, (int)(sizeof c / sizeof c[0]));
 }

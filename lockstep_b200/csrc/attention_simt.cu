@@ -23,8 +23,6 @@
 #include "attention_fold.cuh"
 #include "common.cuh"
 
-#define LS_SPLIT 256
-
 namespace {
 
 constexpr int TILE_M = 16;   // query tokens of a tile kernel block
@@ -214,7 +212,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
                         float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const int* __restrict__ work, const int* __restrict__ block_table,
                         int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
-                        int window, float scale, int* err) {
+                        int window, float scale, int slot_limit, int* err) {
   ls_dependency_sync();
   extern __shared__ __align__(16) unsigned char dsm[];
   constexpr int VEC = 16 / sizeof(T);        // elements per 16-byte chunk
@@ -229,6 +227,13 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
   const int* w = work + (int64_t)blockIdx.x * 8;
   if (w[2] == 0) return;                     // padding item of a recorded launch
   const int req_row = w[0], tok = w[1], pos = w[3], split = w[4], slot = w[6];
+  // slot_limit > 0: the partials live in an array of that many slots that this kernel does not
+  // own (the fixed scratch of the entry point that allocates nothing): a work item that names
+  // a slot outside it is recorded and skipped, not written
+  if (slot_limit > 0 && (slot < 0 || slot >= slot_limit)) {
+    if (threadIdx.x == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, slot);
+    return;
+  }
   const int kvh = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int* table_row = block_table + (int64_t)req_row * table_stride;
@@ -347,11 +352,19 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
                                          const float* __restrict__ part_ml, T* __restrict__ out,
-                                         const int* __restrict__ items, int nq, int d) {
+                                         const int* __restrict__ items, int nq, int d, int slot_limit,
+                                         int* err) {
   ls_dependency_sync();
   const int* it = items + (int64_t)blockIdx.x * 4;
   const int tok = it[0], first = it[1], stride = it[2], n = it[3];
   if (n == 0) return;                        // padding item of a recorded launch
+  if (slot_limit > 0) {                      // see attention_decode_kernel
+    const long long last = (long long)first + (long long)stride * (n - 1);
+    if (first < 0 || first >= slot_limit || last < 0 || last >= slot_limit) {
+      if (threadIdx.x == 0) ls_record_fault(err, LS_DEV_ROW_RANGE, first);
+      return;
+    }
+  }
   const int h = blockIdx.y;
   for (int c = threadIdx.x; c < d; c += blockDim.x)
     out[((int64_t)tok * nq + h) * d + c] = ls_from_float<T>(ls_fold_row(part_acc, part_ml, first, stride, n, nq, h, d, c));
@@ -394,7 +407,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
                         : cudaFuncSetAttribute(attention_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
     if (smem > set_f32) set_f32 = smem;
-    ls_launch(attention_tile_kernel<float>, grid, 128, smem, stream, 
+    LS_COUNT(LS_K_ATTENTION_TILE), ls_launch(attention_tile_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, (float*)out, part_acc, part_ml, work, block_table,
         table_stride, nq, nkv, d, page_size, num_pages, window, scale, err);
   } else if (dtype == LS_BF16) {
@@ -402,7 +415,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
                          : cudaFuncSetAttribute(attention_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
     if (smem > set_bf16) set_bf16 = smem;
-    ls_launch(attention_tile_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
+    LS_COUNT(LS_K_ATTENTION_TILE), ls_launch(attention_tile_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, part_acc,
         part_ml, work, block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale,
         err);
@@ -412,13 +425,14 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
   return ls_launch_status();
 }
 
-// Returns LS_E_SIZE for shapes it does not take (group * d > 1024); the caller
-// then uses ls_attention_tile in parallel mode, which takes them all.
-LS_API int ls_attention_decode(const void* q, const void* pages, float* part_acc, float* part_ml,
-                               int dtype, const int* work, int n_work, const int* block_table,
-                               int table_stride, int nq, int nkv, int d, int page_size,
-                               int num_pages, int window, float scale, int* err,
-                               cudaStream_t stream) {
+namespace {
+
+// slot_limit: 0, or the number of slots the partial arrays hold (checked on the device)
+int launch_attention_decode(const void* q, const void* pages, float* part_acc, float* part_ml,
+                            int dtype, const int* work, int n_work, const int* block_table,
+                            int table_stride, int nq, int nkv, int d, int page_size,
+                            int num_pages, int window, float scale, int slot_limit, int* err,
+                            cudaStream_t stream) {
   if (n_work <= 0) return 0;
   if (!shape_ok(nq, nkv, d, page_size, DEC_TILE)) return LS_E_SIZE;
   const int group = nq / nkv;
@@ -432,38 +446,57 @@ LS_API int ls_attention_decode(const void* q, const void* pages, float* part_acc
                         : cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
     if (smem > set_f32) set_f32 = smem;
-    ls_launch(attention_decode_kernel<float>, grid, 128, smem, stream, 
+    LS_COUNT(LS_K_ATTENTION_DECODE), ls_launch(attention_decode_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, part_acc, part_ml, work, block_table, table_stride,
-        nq, nkv, d, page_size, num_pages, window, scale, err);
+        nq, nkv, d, page_size, num_pages, window, scale, slot_limit, err);
   } else if (dtype == LS_BF16) {
     const size_t smem = decode_smem_bytes(d, group, 2);
     e = smem <= set_bf16 ? cudaSuccess
                          : cudaFuncSetAttribute(attention_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return LS_E_SMEM;
     if (smem > set_bf16) set_bf16 = smem;
-    ls_launch(attention_decode_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
+    LS_COUNT(LS_K_ATTENTION_DECODE), ls_launch(attention_decode_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, part_acc, part_ml, work,
-        block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, err);
+        block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, slot_limit, err);
   } else {
     return LS_E_DTYPE;
   }
   return ls_launch_status();
 }
 
-LS_API int ls_attention_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
-                                const int* items, int n_items, int nq, int d,
-                                cudaStream_t stream) {
+int launch_attention_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
+                             const int* items, int n_items, int nq, int d, int slot_limit, int* err,
+                             cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (nq > 65535) return LS_E_SIZE;
   dim3 grid(n_items, nq);
   const int threads = d >= 128 ? 128 : (d >= 64 ? 64 : 32);
   if (dtype == LS_F32)
-    ls_launch(attention_combine_kernel<float>, grid, threads, 0, stream, part_acc, part_ml, (float*)out, items, nq, d);
+    LS_COUNT(LS_K_ATTENTION_COMBINE), ls_launch(attention_combine_kernel<float>, grid, threads, 0, stream, part_acc, part_ml, (float*)out, items, nq, d, slot_limit, err);
   else if (dtype == LS_BF16)
-    ls_launch(attention_combine_kernel<__nv_bfloat16>, grid, threads, 0, stream, part_acc, part_ml, (__nv_bfloat16*)out, items, nq, d);
+    LS_COUNT(LS_K_ATTENTION_COMBINE), ls_launch(attention_combine_kernel<__nv_bfloat16>, grid, threads, 0, stream, part_acc, part_ml, (__nv_bfloat16*)out, items, nq, d, slot_limit, err);
   else
     return LS_E_DTYPE;
   return ls_launch_status();
+}
+
+}  // namespace
+
+// Returns LS_E_SIZE for shapes it does not take (group * d > 1024); the caller
+// then uses ls_attention_tile in parallel mode, which takes them all.
+LS_API int ls_attention_decode(const void* q, const void* pages, float* part_acc, float* part_ml,
+                               int dtype, const int* work, int n_work, const int* block_table,
+                               int table_stride, int nq, int nkv, int d, int page_size,
+                               int num_pages, int window, float scale, int* err,
+                               cudaStream_t stream) {
+  return launch_attention_decode(q, pages, part_acc, part_ml, dtype, work, n_work, block_table, table_stride, nq,
+                                 nkv, d, page_size, num_pages, window, scale, 0, err, stream);
+}
+
+LS_API int ls_attention_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
+                                const int* items, int n_items, int nq, int d,
+                                cudaStream_t stream) {
+  return launch_attention_combine(part_acc, part_ml, out, dtype, items, n_items, nq, d, 0, nullptr, stream);
 }
 
 // --------------------------------------------------------------------------
@@ -516,9 +549,26 @@ LS_API int ls_attention_decode_noalloc(const void* q, const void* pages, void* o
   if (setup != 0) return setup;
   float* part_acc = scratch;                                   // [n_slots, nq, d]
   float* part_ml = scratch + (size_t)n_slots * nq * d;         // [n_slots, nq, 2]
-  const int status = ls_attention_decode(q, pages, part_acc, part_ml, dtype, work, n_work,
-                                         block_table, table_stride, nq, nkv, d, page_size,
-                                         num_pages, window, scale, err, stream);
+  // the kernels check every slot a work item names against n_slots: a wrong item is recorded
+  // in the error word (LS_DEV_ROW_RANGE) and skipped, it cannot write outside the array
+  const int status = launch_attention_decode(q, pages, part_acc, part_ml, dtype, work, n_work,
+                                             block_table, table_stride, nq, nkv, d, page_size,
+                                             num_pages, window, scale, n_slots, err, stream);
   if (status != 0) return status;
-  return ls_attention_combine(part_acc, part_ml, out, dtype, combine, n_combine, nq, d, stream);
+  return launch_attention_combine(part_acc, part_ml, out, dtype, combine, n_combine, nq, d, n_slots, err, stream);
+}
+
+LS_API const char* ls_constants_attention_simt() {
+  static char buf[256];
+  static const LsConstant c[] = {{"attention.split_keys", LS_SPLIT}, {"attention_tile.queries", TILE_M},
+                                 {"attention_tile.keys", TILE_N}, {"attention_decode.keys", DEC_TILE},
+                                 {"attention.max_head_dim", MAX_D}};
+  return ls_format_constants(buf, sizeof buf, c, (int)(sizeof c / sizeof c[0]));
+}
+
+// launches of this library's kernels so far, in the order of LS_KERNEL_NAMES
+LS_API const char* ls_kernel_names_core() { return LS_KERNEL_NAMES; }
+LS_API int ls_kernel_launches_core(unsigned long long* out, int n) {
+  for (int i = 0; i < n && i < LS_K_COUNT; ++i) out[i] = ls_kernel_launches[i];
+  return LS_K_COUNT;
 }

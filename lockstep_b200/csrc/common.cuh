@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #define LS_API extern "C" __attribute__((visibility("default")))
 
@@ -38,6 +39,42 @@ __device__ __forceinline__ void ls_record_fault(int* err, int code, int detail) 
     if (atomicCAS(err, 0, code) == 0) err[1] = detail;
   }
 }
+
+// Launch constants that fix the order of a reduction are defined once, here or in the one
+// source that uses them, and every source reports its own through ls_constants_<source>()
+// as "name=value;..." so that a run can record the table it ran with.
+#define LS_SPLIT 256         // keys of an attention split (fixed absolute positions)
+
+struct LsConstant {
+  const char* name;
+  long long value;
+};
+static inline const char* ls_format_constants(char* buf, size_t size, const LsConstant* c, int count) {
+  size_t at = 0;
+  buf[0] = 0;
+  for (int i = 0; i < count && at + 1 < size; ++i) {
+    int n = snprintf(buf + at, size - at, "%s%s=%lld", i ? ";" : "", c[i].name, c[i].value);
+    if (n < 0) break;
+    at += (size_t)n;
+  }
+  return buf;
+}
+
+// Which kernels a process has launched (launcher calls, counted on the host): tests assert
+// with it that the kernel they mean to check is the one that ran.
+enum LsKernelId {
+  LS_K_EMBED_GATHER = 0, LS_K_RMSNORM, LS_K_QK_NORM_ROPE, LS_K_QK_NORM_ROPE_WHOLE, LS_K_SILU_MUL,
+  LS_K_GEMM_SIMT, LS_K_ATTENTION_TILE, LS_K_ATTENTION_DECODE, LS_K_ATTENTION_COMBINE, LS_K_ARGMAX,
+  LS_K_SAMPLE, LS_K_GEMM_TC_FEW, LS_K_GEMM_TC_FEW_NORM, LS_K_GEMM_TC_FEW_QKV, LS_K_GEMM_TC_CLUSTER,
+  LS_K_GEMM_TC_WALK, LS_K_GEMM_TC_ROWS, LS_K_GEMM_TC_ROWS_PAIR, LS_K_ATTENTION_DECODE_MMA,
+  LS_K_ATTENTION_PREFILL_TC, LS_K_COUNT
+};
+#define LS_KERNEL_NAMES                                                                                  \
+  "embed_gather,rmsnorm,qk_norm_rope_store,qk_norm_rope_store_whole,silu_mul,gemm_simt,attention_tile," \
+  "attention_decode,attention_combine,argmax,sample,gemm_tc_few,gemm_tc_few_norm,gemm_tc_few_qkv,"      \
+  "gemm_tc_cluster,gemm_tc_walk,gemm_tc_rows,gemm_tc_rows_pair,attention_decode_mma,attention_prefill_tc"
+inline unsigned long long ls_kernel_launches[LS_K_COUNT];     // one table per library
+#define LS_COUNT(id) (++ls_kernel_launches[id])
 
 template <typename T>
 __device__ __forceinline__ float ls_to_float(T v);

@@ -30,9 +30,9 @@ LS_API int ls_embed_gather(const int* ids, const void* table, int table_dtype, f
   if (tokens <= 0) return 0;
   const int threads = width >= 1024 ? 256 : 128;
   if (table_dtype == LS_F32)
-    ls_launch(embed_gather_kernel<float>, tokens, threads, 0, stream, ids, (const float*)table, out, width, vocab, err);
+    LS_COUNT(LS_K_EMBED_GATHER), ls_launch(embed_gather_kernel<float>, tokens, threads, 0, stream, ids, (const float*)table, out, width, vocab, err);
   else if (table_dtype == LS_BF16)
-    ls_launch(embed_gather_kernel<__nv_bfloat16>, tokens, threads, 0, stream, ids, (const __nv_bfloat16*)table, out, width, vocab, err);
+    LS_COUNT(LS_K_EMBED_GATHER), ls_launch(embed_gather_kernel<__nv_bfloat16>, tokens, threads, 0, stream, ids, (const __nv_bfloat16*)table, out, width, vocab, err);
   else
     return LS_E_DTYPE;
   return ls_launch_status();
@@ -151,7 +151,7 @@ LS_API int ls_rmsnorm(const float* x, const int* row_index, const void* gain, in
   const int warps = rows >= 1024 ? 4 : 1;
   const int blocks = (rows + warps - 1) / warps;
 #define LS_RMS(TO, TG)                                                                          \
-  ls_launch(rmsnorm_kernel<TO, TG>, blocks, warps * 32, 0, stream, x, row_index, (const TG*)gain, (TO*)y, \
+  LS_COUNT(LS_K_RMSNORM), ls_launch(rmsnorm_kernel<TO, TG>, blocks, warps * 32, 0, stream, x, row_index, (const TG*)gain, (TO*)y, \
                                                             rows, width, src_rows, eps, err)
   if (y_dtype == LS_F32 && gain_dtype == LS_F32) LS_RMS(float, float);
   else if (y_dtype == LS_F32 && gain_dtype == LS_BF16) LS_RMS(float, __nv_bfloat16);
@@ -358,15 +358,15 @@ LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int 
                      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pages) & 15) == 0 && smem <= 48 * 1024;
   if (whole) {
     if (d == 64)
-      ls_launch(qk_norm_rope_store_whole_kernel<64>, grid, 256, smem, stream, (const __nv_bfloat16*)qkv, args, tokens, err);
+      LS_COUNT(LS_K_QK_NORM_ROPE_WHOLE), ls_launch(qk_norm_rope_store_whole_kernel<64>, grid, 256, smem, stream, (const __nv_bfloat16*)qkv, args, tokens, err);
     else
-      ls_launch(qk_norm_rope_store_whole_kernel<128>, grid, 256, smem, stream, (const __nv_bfloat16*)qkv, args, tokens, err);
+      LS_COUNT(LS_K_QK_NORM_ROPE_WHOLE), ls_launch(qk_norm_rope_store_whole_kernel<128>, grid, 256, smem, stream, (const __nv_bfloat16*)qkv, args, tokens, err);
     return ls_launch_status();
   }
   if (dtype == LS_F32)
-    ls_launch(qk_norm_rope_store_kernel<float>, grid, warps * 32, smem, stream, (const float*)qkv, args, tokens, err);
+    LS_COUNT(LS_K_QK_NORM_ROPE), ls_launch(qk_norm_rope_store_kernel<float>, grid, warps * 32, smem, stream, (const float*)qkv, args, tokens, err);
   else if (dtype == LS_BF16)
-    ls_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, warps * 32, smem, stream, (const __nv_bfloat16*)qkv, args,
+    LS_COUNT(LS_K_QK_NORM_ROPE), ls_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, warps * 32, smem, stream, (const __nv_bfloat16*)qkv, args,
               tokens, err);
   else
     return LS_E_DTYPE;
@@ -398,9 +398,9 @@ LS_API int ls_silu_mul(const void* gate_up, void* out, int dtype, int rows, int 
   const int64_t n = (int64_t)rows * width;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   if (dtype == LS_F32)
-    ls_launch(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, rows, width);
+    LS_COUNT(LS_K_SILU_MUL), ls_launch(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, rows, width);
   else if (dtype == LS_BF16)
-    ls_launch(silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, width);
+    LS_COUNT(LS_K_SILU_MUL), ls_launch(silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, width);
   else
     return LS_E_DTYPE;
   return ls_launch_status();

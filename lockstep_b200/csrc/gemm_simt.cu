@@ -98,13 +98,13 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t l
   if (grid.y > 65535) return LS_E_SIZE;
   switch (epilogue) {
     case 0:
-      ls_launch(gemm_nt_kernel<TA, TW, TC, 0>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+      LS_COUNT(LS_K_GEMM_SIMT), ls_launch(gemm_nt_kernel<TA, TW, TC, 0>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
       break;
     case 1:
-      ls_launch(gemm_nt_kernel<TA, TW, TC, 1>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+      LS_COUNT(LS_K_GEMM_SIMT), ls_launch(gemm_nt_kernel<TA, TW, TC, 1>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
       break;
     case 2:
-      ls_launch(gemm_nt_kernel<TA, TW, TC, 2>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
+      LS_COUNT(LS_K_GEMM_SIMT), ls_launch(gemm_nt_kernel<TA, TW, TC, 2>, grid, 256, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, lda, ldw, ldc);
       break;
     default:
       return LS_E_SIZE;
@@ -130,4 +130,10 @@ LS_API int ls_gemm_nt_simt(const void* A, const void* W, void* C, int a_dtype, i
   if (a_dtype == LS_BF16 && c_dtype == LS_F32)
     return launch<bf16, bf16, float>(A, W, C, M, N, K, lda, ldw, ldc, epilogue, stream);
   return LS_E_DTYPE;
+}
+
+LS_API const char* ls_constants_gemm_simt() {
+  static char buf[256];
+  static const LsConstant c[] = {{"gemm_simt.tile_m", BM}, {"gemm_simt.tile_n", BN}, {"gemm_simt.tile_k", BK}};
+  return ls_format_constants(buf, sizeof buf, c, (int)(sizeof c / sizeof c[0]));
 }

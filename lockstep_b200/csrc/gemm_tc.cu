@@ -47,16 +47,20 @@
 // the 4B and 8B sizes, where 10 chose three shares and lost 14 us a layer at 8B).  The rule
 // takes the number of shares (each at least four blocks deep, at most 8, the portable cluster
 // size) with the smallest rounds x (depth / shares + 22), the fewest shares among equals.
+#define LS_SHARE_RULE_BLOCKS 148        // blocks of a round
+#define LS_SHARE_RULE_FIXED 22          // fixed cost of a round, in 64-element blocks of K
+#define LS_SHARE_RULE_MIN_DEPTH 4       // a share is at least this many blocks deep
+#define LS_SHARE_RULE_MAX_SHARES 8      // the portable cluster size
 LS_API int ls_gemm_tc_k_shares(int N, int K) {
   const long long tiles = (N + 127) / 128;
   const long long kb = (K + 63) / 64;
-  const long long fixed = 22;
-  long long most = kb / 4;
-  if (most > 8) most = 8;
+  const long long fixed = LS_SHARE_RULE_FIXED, round = LS_SHARE_RULE_BLOCKS;
+  long long most = kb / LS_SHARE_RULE_MIN_DEPTH;
+  if (most > LS_SHARE_RULE_MAX_SHARES) most = LS_SHARE_RULE_MAX_SHARES;
   long long best = 1;
-  long long best_cost = ((tiles + 147) / 148) * (kb + fixed);        // cost x shares, compared as cross products
+  long long best_cost = ((tiles + round - 1) / round) * (kb + fixed);        // cost x shares, compared as cross products
   for (long long s = 2; s <= most; ++s) {
-    const long long cost = ((tiles * s + 147) / 148) * (kb + fixed * s);
+    const long long cost = ((tiles * s + round - 1) / round) * (kb + fixed * s);
     if (cost * best < best_cost * s) {
       best = s;
       best_cost = cost;
@@ -1666,6 +1670,7 @@ int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T,
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ls_dependent_launch ? 2 : 1;
+  LS_COUNT(LS_K_GEMM_TC_CLUSTER);
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<BN, EPI, TC>, mw, mx, (TC*)C, T,
                                      N, K, ldc, plan.kb_per_share, plan.shares, err);
   if (e != cudaSuccess) return (int)e;
@@ -1717,6 +1722,7 @@ int launch_few(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs& nor
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ls_dependent_launch ? 2 : 1;
+  LS_COUNT(EPI == 3 ? LS_K_GEMM_TC_FEW_QKV : NORM ? LS_K_GEMM_TC_FEW_NORM : LS_K_GEMM_TC_FEW);
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_few_kernel<BN, EPI, TC, NORM>, mw, mx, norm, heads, (TC*)C, T, N,
                                      K, ldc, plan.kb_per_share, plan.shares, lay, err);
   if (e != cudaSuccess) return (int)e;
@@ -1739,6 +1745,7 @@ int launch_walk(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, in
     const int tiles_n = (N + BM - 1) / BM, tiles_t = (T + BN - 1) / BN;
     const int tiles = tiles_n * tiles_t;
     const int sms = sm_count();
+    LS_COUNT(LS_K_GEMM_TC_WALK);
     ls_launch(gemm_tc_walk_kernel<BN, EPI, TC, EW>, tiles < sms ? tiles : sms, EW == 8 ? 320 : 192, S::SMEM,
               stream, mw, mx, (TC*)C, T, N, K, ldc, plan.kb_per_share, plan.shares, tiles_n, tiles, err);
     return ls_launch_status();
@@ -1805,6 +1812,7 @@ int launch_rows(const CUtensorMap& mw, const CUtensorMap& mx, void* C, int T, in
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ls_dependent_launch ? 2 : 1;
+  LS_COUNT(CTAS == 2 ? LS_K_GEMM_TC_ROWS_PAIR : LS_K_GEMM_TC_ROWS);
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_rows_kernel<EPI, FN, CTAS, TC>, mw, mx, mc, store_by_tma, (TC*)C, T,
                                      N, K, ldc, plan.kb_per_share, plan.shares, tiles_t, tiles, err);
   if (e != cudaSuccess) return (int)e;
@@ -1939,6 +1947,24 @@ int run(const void* X, const NormArgs* norm, const LsQkvStore* heads, const void
 }  // namespace
 
 LS_API void ls_set_dependent_launch_tc(int on) { ls_dependent_launch = on ? 1 : 0; }
+
+LS_API const char* ls_constants_gemm_tc() {
+  static char buf[512];
+  static const LsConstant c[] = {{"gemm_tc.weight_rows_per_tile", BM}, {"gemm_tc.k_block", BK},
+                                 {"gemm_tc.share_rule.blocks_per_round", LS_SHARE_RULE_BLOCKS},
+                                 {"gemm_tc.share_rule.fixed_cost", LS_SHARE_RULE_FIXED},
+                                 {"gemm_tc.share_rule.min_depth", LS_SHARE_RULE_MIN_DEPTH},
+                                 {"gemm_tc.share_rule.max_shares", LS_SHARE_RULE_MAX_SHARES},
+                                 {"gemm_tc.few_tokens_norm_bytes", NORM_X_BYTES}};
+  return ls_format_constants(buf, sizeof buf, c, (int)(sizeof c / sizeof c[0]));
+}
+
+// launches of this library's kernels so far, in the order of LS_KERNEL_NAMES
+LS_API const char* ls_kernel_names_tc() { return LS_KERNEL_NAMES; }
+LS_API int ls_kernel_launches_tc(unsigned long long* out, int n) {
+  for (int i = 0; i < n && i < LS_K_COUNT; ++i) out[i] = ls_kernel_launches[i];
+  return LS_K_COUNT;
+}
 
 // Whether products of more than 128 tokens run on pairs of blocks (the default) or on single
 // blocks; the sums are the same either way.

@@ -18,8 +18,11 @@
 //  - The scratch holds LS_NOALLOC_SCRATCH_FLOATS floats (8 MiB).  A call needs
 //    n_slots * nq * (d + 2) of them, where n_slots is one more than the largest
 //    slot a work item names; a larger call is refused with LS_E_NOALLOC_TOO_LARGE
-//    and launches nothing.  Every GPU that loads the library holds these 8 MiB
-//    until the process exits.
+//    and launches nothing.  The work and combine items live on the device, so the
+//    host cannot read them: the kernels themselves compare every slot an item
+//    names with n_slots, record LS_DEV_ROW_RANGE in the error word for one that
+//    lies outside, and skip it, so a wrong item cannot write past the array.
+//    Every GPU that loads the library holds these 8 MiB until the process exits.
 //  - The first call on a device looks up the scratch's device address (once per
 //    device, with that device current).  Make that first call outside any
 //    stream capture.

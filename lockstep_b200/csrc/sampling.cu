@@ -260,12 +260,12 @@ LS_API int ls_argmax(const float* logits, int* out, void* scratch, int rows, int
                      cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (scratch == nullptr || vocab < 4 * ARGMAX_CHUNKS) {
-    ls_launch(argmax_kernel, rows, 512, 0, stream, logits, out, vocab);
+    LS_COUNT(LS_K_ARGMAX), ls_launch(argmax_kernel, rows, 512, 0, stream, logits, out, vocab);
     return ls_launch_status();
   }
   float* cval = (float*)scratch;
   int* cidx = (int*)(cval + (size_t)rows * ARGMAX_CHUNKS);
-  ls_launch(argmax_chunk_kernel, dim3(rows, ARGMAX_CHUNKS), 256, 0, stream, logits, cval, cidx, vocab);
+  LS_COUNT(LS_K_ARGMAX), ls_launch(argmax_chunk_kernel, dim3(rows, ARGMAX_CHUNKS), 256, 0, stream, logits, cval, cidx, vocab);
   ls_launch(argmax_final_kernel, rows, 32, 0, stream, cval, cidx, out);
   return ls_launch_status();
 }
@@ -275,7 +275,13 @@ LS_API int ls_sample(const float* logits, float* probs, const float* temperature
                      const float* top_p, const uint32_t* keys, const uint32_t* positions, int* out,
                      int rows, int vocab, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  ls_launch(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, probs, temperature, top_p, keys,
+  LS_COUNT(LS_K_SAMPLE), ls_launch(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, probs, temperature, top_p, keys,
                                                      positions, out, vocab);
   return ls_launch_status();
+}
+
+LS_API const char* ls_constants_sampling() {
+  static char buf[256];
+  static const LsConstant c[] = {{"argmax.chunks", ARGMAX_CHUNKS}, {"sample.threads", SAMPLE_THREADS}};
+  return ls_format_constants(buf, sizeof buf, c, (int)(sizeof c / sizeof c[0]));
 }

@@ -25,11 +25,13 @@ class Engine:
     def __init__(self, model_dir, dtype="bfloat16", device="cuda:0", num_pages: int | None = None,
                  page_size: int = 16, max_running: int = 32, max_step_tokens: int = 2048,
                  max_seq_len: int | None = None, enable_prefix_cache: bool = False,
-                 eos_token_ids=None, policy: Policy | None = None, audit: bool = False):
+                 eos_token_ids=None, policy: Policy | None = None, audit: bool = False,
+                 trajectory: bool = False, poison_freed_pages: bool = False):
         if num_pages is None:
             num_pages = 4096
         self.runner = ModelRunner(model_dir, dtype=dtype, device=device, num_pages=num_pages,
-                                  page_size=page_size, max_live=max_running, max_seq_len=max_seq_len)
+                                  page_size=page_size, max_live=max_running, max_seq_len=max_seq_len,
+                                  poison_freed_pages=poison_freed_pages)
         self.sampler = Sampler(self.runner.device)
         # two pinned buffers in turn (a step may be launched before the last one is collected):
         # sampled ids, then the two words of the device error word
@@ -38,7 +40,8 @@ class Engine:
         self.cache = self.runner.cache
         self.config = self.runner.config
         self._options = dict(max_step_tokens=max_step_tokens, policy=policy, eos_token_ids=eos_token_ids,
-                             audit=audit, enable_prefix_cache=enable_prefix_cache, max_running=max_running)
+                             audit=audit, enable_prefix_cache=enable_prefix_cache, max_running=max_running,
+                             trajectory=trajectory)
         self.scheduler = self._new_scheduler()
 
     def _new_scheduler(self) -> Scheduler:

@@ -3,7 +3,12 @@
 A step whose entries all bring one token launches a few hundred small kernels;
 recorded once and replayed, the host's share of the step shrinks to filling one
 pinned buffer.  A graph is keyed by (number of requests, capacity of the
-attention work list).  Everything that changes from step to step (token ids,
+attention work list); the capacity is rounded up to a multiple of
+max(CAPACITY_STEP, 4 x requests), so that a batch records a new graph about every
+1,024 decoded tokens whatever its size, and at most MAX_GRAPHS graphs are kept
+(the least recently replayed one is dropped first).  A graph holds its input
+buffer (a few KB), its activations (a few hundred KB a request) and its logits
+[requests, vocabulary] in float32, all from one memory pool shared by the graphs.  Everything that changes from step to step (token ids,
 positions, slots, wanted rows, the attention work lists) lives in one device
 buffer that is refilled before each replay; work lists are padded to the
 capacity with null items, which the kernels skip.  Nothing about the
@@ -15,11 +20,15 @@ Only models whose parts are all ``graph_safe`` are recorded.
 from __future__ import annotations
 
 import gc
+from collections import OrderedDict
 
 import numpy as np
 import torch
 
 from .batch import AttentionPlan, plan_attention
+
+CAPACITY_STEP = 32      # the attention work list of a recorded step holds a multiple of this many items
+MAX_GRAPHS = 24         # recorded steps kept; the least recently used one goes first
 
 
 class StaticStepContext:
@@ -120,16 +129,18 @@ def split_items(entries, windows: list[int], split_size: int) -> int:
 
 
 class DecodeGraphs:
-    def __init__(self, runner, round_to: int = 32):
-        self.runner, self.round_to = runner, round_to
+    def __init__(self, runner, round_to: int = CAPACITY_STEP, max_graphs: int = MAX_GRAPHS):
+        self.runner, self.round_to, self.max_graphs = runner, round_to, max(1, int(max_graphs))
         self.windows = sorted(set().union(*(b.attention_windows() for b in runner.model.blocks)) or {0})
-        self.graphs: dict[tuple[int, int], tuple] = {}
+        self.graphs: OrderedDict[tuple[int, int], tuple] = OrderedDict()
         self.pool = None
         self.replays = 0
+        self.dropped = 0
 
     def capacity_for(self, entries) -> int:
         n = split_items(entries, self.windows, self.runner.split_size)
-        return -(-n // self.round_to) * self.round_to
+        step = max(self.round_to, 4 * len(entries))
+        return -(-n // step) * step
 
     def ready(self, key) -> bool:
         return key in self.graphs
@@ -160,6 +171,10 @@ class DecodeGraphs:
         recorded = K.LAUNCHES[0] - before
         K.LAUNCHES[0] = before               # recording launches nothing
         self.graphs[key] = (graph, ctx, logits, recorded)
+        while len(self.graphs) > self.max_graphs:
+            # nothing of the dropped graph is in flight: record() synchronised above
+            self.graphs.popitem(last=False)
+            self.dropped += 1
 
     def replay(self, key, entries, slots, tokens_device=None) -> torch.Tensor:
         """``tokens_device`` (int32, one per entry, on the device): the step's token ids, in
@@ -168,6 +183,7 @@ class DecodeGraphs:
         from .. import kernels as K
 
         graph, ctx, logits, recorded = self.graphs[key]
+        self.graphs.move_to_end(key)
         ctx.fill(entries, slots)
         if tokens_device is not None:
             ctx.token_ids.copy_(tokens_device, non_blocking=True)

@@ -34,7 +34,7 @@ def parse_dtype(dtype) -> torch.dtype:
 class ModelRunner:
     def __init__(self, model_dir, dtype="bfloat16", device="cuda:0", num_pages: int = 512,
                  page_size: int = 16, max_live: int = 64, max_seq_len: int | None = None,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, poison_freed_pages: bool = False, check_exclusive: bool = False):
         K.require_cuda()
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
@@ -60,7 +60,10 @@ class ModelRunner:
         self.model.bind(tensors)
         self.cache = CacheManager(self.model.cache_needs(), num_pages=num_pages, page_size=page_size,
                                   max_live=max_live, max_seq_len=self.max_seq_len, dtype=self.dtype,
-                                  device=self.device)
+                                  device=self.device, poison_freed_pages=poison_freed_pages)
+        # debugging aids: freed pages are filled with a poison value; before a step writes a
+        # request's new tokens, the pages they go to are checked to be that request's alone
+        self.check_exclusive = bool(check_exclusive or poison_freed_pages)
         self.steps_run = 0
         # decode steps are recorded as CUDA graphs when every part allows it
         self.graphs = None
@@ -151,6 +154,9 @@ class ModelRunner:
             raise OutOfPages(f"the step needs more pages than the {self.cache.free_pages()} that are free")
         for uid, total in wants:
             self.cache.reserve(uid, total)
+        if self.check_exclusive:
+            for e in entries:
+                self.cache.assert_exclusive(e.uid, e.start, e.start + len(e.tokens) - 1)
         self.cache.sync()
         slots = [self.cache.slots[e.uid] for e in entries]
         logits = None

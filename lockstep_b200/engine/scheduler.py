@@ -22,7 +22,9 @@ from dataclasses import dataclass, field
 from ..cache import OutOfPages, PrefixIndex
 from ..sampling import SamplingParams
 from .batch import StepEntry
+from .lifecycle import Lifecycle
 from .policy import DefaultPolicy, Policy, SchedulerState
+from .trajectory import Trajectory
 
 
 @dataclass
@@ -81,7 +83,7 @@ class Scheduler:
 
     def __init__(self, backend, max_step_tokens: int = 2048, policy: Policy | None = None,
                  eos_token_ids=None, audit: bool = False, enable_prefix_cache: bool = False,
-                 max_running: int = 32):
+                 max_running: int = 32, trajectory: bool = False):
         self.backend = backend
         self.cache = backend.cache
         self.max_step_tokens = int(max_step_tokens)
@@ -95,6 +97,10 @@ class Scheduler:
         self.done: list[Request] = []
         self.step_index = 0
         self.events: list[tuple] = []          # (step, event, uid, detail)
+        self.lifecycle = Lifecycle()           # every event is checked against the table of legal ones
+        # trajectory=True: every step's work, tokens, logits bytes and cache digests go into one
+        # running hash (the logits rows are read back each step, so no step is launched ahead)
+        self.trajectory = Trajectory() if trajectory else None
         self.stats = {"preemptions": 0, "evictions": 0, "steps": 0, "tokens_run": 0,
                       "mixed_steps": 0, "budget_cuts": 0, "launched_ahead": 0}
         self._ahead = None                     # a launched step whose tokens have not been collected
@@ -107,6 +113,7 @@ class Scheduler:
 
     # -- bookkeeping ----------------------------------------------------------
     def _event(self, name: str, uid: str, detail=()):
+        self.lifecycle.observe(uid, name)
         self.events.append((self.step_index, name, uid, tuple(detail)))
 
     def _pages_for(self, tokens: int) -> int:
@@ -139,6 +146,7 @@ class Scheduler:
         self.cache.create(request.uid)
         request.kv_len = 0
         request.cache_hit_tokens = 0
+        self._event("resume" if request.preempt_count else "admit", request.uid)
         if self.prefix is not None:
             group = self.cache.paged[0]
             context = request.context()
@@ -151,7 +159,6 @@ class Scheduler:
                 request.kv_len = request.cache_hit_tokens = hit
                 self.cache.lengths[request.uid] = hit
                 self._event("cache_hit", request.uid, (hit,))
-        self._event("resume" if request.preempt_count else "admit", request.uid)
 
     def _preempt(self, request: Request) -> None:
         self.cache.release(request.uid)
@@ -270,7 +277,7 @@ class Scheduler:
             last = ahead_of is not None or start + take == request.total_tokens()
             tokens = [0] if ahead_of is not None else request.tokens(start, start + take)
             entries.append(StepEntry(uid=request.uid, tokens=tokens, start=start, want=[take - 1] if last else []))
-            self._event("decode" if take == 1 and last else "chunk", request.uid, (start, take))
+            self._event("decode" if last else "chunk", request.uid, (start, take))
         kinds = {len(e.tokens) == 1 for e in entries}
         if len(kinds) == 2:
             self.stats["mixed_steps"] += 1
@@ -290,7 +297,8 @@ class Scheduler:
                                              temperature=request.temperature, top_p=request.top_p,
                                              position=e.start + take - 1))
                 owners.append(request)
-        launched = {"planned": planned, "owners": owners, "params": params, "logits": logits, "pending": None}
+        launched = {"planned": planned, "owners": owners, "params": params, "logits": logits, "pending": None,
+                    "work": [(e.uid, e.start, list(e.tokens)) for e in entries]}
         if getattr(self.backend, "supports_run_ahead", False):
             launched["pending"] = self.backend.sample_async(logits, params)
         return launched
@@ -307,6 +315,13 @@ class Scheduler:
                 continue                      # ended on an end token while this step was under way
             request.generated.append(int(token))
             owners.append(request)
+        if self.trajectory is not None:
+            rows = launched["logits"]
+            raw = rows.detach().cpu().contiguous().numpy().tobytes() if hasattr(rows, "detach") else repr(rows).encode()
+            self.trajectory.observe_step(
+                self.step_index, launched["work"],
+                [(r.uid, r.generated[-1]) for r in owners], raw,
+                (self.cache.digest(), self.prefix.digest() if self.prefix is not None else ()))
 
         if self.audit_enabled:
             self.cache.audit()
@@ -329,6 +344,8 @@ class Scheduler:
         """True if the step after ``launched`` is known now: the same requests, one more token
         each, whatever the tokens turn out to be (but for an end token, see the class)."""
         if launched["pending"] is None or self.waiting or self.audit_enabled or self.prefix is not None:
+            return False
+        if self.trajectory is not None:
             return False
         if not self.policy.allows_run_ahead or self.step_index + 2 > self._step_limit:
             return False

@@ -163,6 +163,23 @@ USE_TENSOR_CORES = [True]
 LAUNCHES = [0]
 
 
+def kernel_counts() -> dict[str, int]:
+    """How often each kernel's launcher has launched in this process (a launch recorded into
+    a graph counts once, its replays do not), over the libraries that are loaded."""
+    out: dict[str, int] = {}
+    for name, lib in _libs.items():
+        names_fn = getattr(lib, f"ls_kernel_names_{name}")
+        names_fn.restype, names_fn.argtypes = ctypes.c_char_p, []
+        names = names_fn().decode("ascii").split(",")
+        counts = (ctypes.c_ulonglong * len(names))()
+        fn = getattr(lib, f"ls_kernel_launches_{name}")
+        fn.restype, fn.argtypes = c_int, [ctypes.POINTER(ctypes.c_ulonglong), c_int]
+        fn(counts, len(names))
+        for kernel, count in zip(names, counts):
+            out[kernel] = out.get(kernel, 0) + int(count)
+    return out
+
+
 def _check(status: int, what: str) -> None:
     if status == 0:
         LAUNCHES[0] += 1

@@ -187,3 +187,42 @@ def test_prefix_eviction_leaves_no_unreachable_page():
             reachable.update(idx.lookup(toks)[1])
         assert reachable == {e.page for e in idx.entries.values()}
     assert g.allocator.free_pages == 32
+
+
+def test_freed_pages_are_poisoned_and_shared_pages_are_not_written():
+    m = CacheManager([FULL], num_pages=8, page_size=4, max_live=4, max_seq_len=64, allocate=False,
+                     poison_freed_pages=True)
+    g = m.paged[0]
+    idx = PrefixIndex(page_size=4)
+    m.create("a")
+    m.reserve("a", 10)
+    m.assert_exclusive("a", 0, 9)
+    idx.insert(list(range(10)), g.seqs["a"].pages, g)
+    with pytest.raises(AuditFailure, match="holders"):
+        m.assert_exclusive("a", 4, 9)                  # its first two pages are now the index's too
+    m.assert_exclusive("a", 8, 9)
+    m.release("a")
+    assert g.poisoned == 1                             # the third page; the index keeps the other two
+    m.create("b")
+    g.adopt("b", idx.lookup(list(range(8)))[1])
+    m.lengths["b"] = 8
+    m.reserve("b", 12)
+    m.assert_exclusive("b", 8, 11)
+    with pytest.raises(AuditFailure):
+        m.assert_exclusive("b", 7, 8)                  # token 7 lies in a shared page
+    with pytest.raises(AuditFailure, match="does not hold"):
+        m.assert_exclusive("b", 8, 12)
+    m.release("b")
+    while idx.evictable(g):
+        idx.evict(idx.evictable(g)[0], g)
+    m.audit()
+    assert g.poisoned == 4 and g.allocator.free_pages == 8
+
+
+def test_constants_table_has_a_stable_digest():
+    from lockstep_b200 import constants
+
+    table = constants.table()
+    assert table["attention.split_keys"] == 256 and table["gemm_tc.share_rule.blocks_per_round"] == 148
+    assert constants.digest() == constants.digest() and len(constants.digest()) == 64
+    assert "attention.split_keys=256" in constants.describe()

@@ -23,7 +23,10 @@ pytestmark = pytest.mark.gpu
 
 ROOT = Path(__file__).resolve().parent.parent
 
-LENGTHS = {"A": [70, 300, 37, 560, 129], "B": [45, 270, 90, 33, 520], "C": [100, 290, 64, 75, 200]}
+LENGTHS = {"A": [70, 300, 37, 560, 129], "B": [45, 270, 90, 33, 520], "C": [100, 290, 64, 75, 200],
+           "D": [70, 650, 260, 37, 330], "E": [45, 270, 600, 33, 140]}
+# D and E have the sizes the tensor-core kernels take: their portions also go beyond 128 tokens
+HOT = ("D", "E")
 
 
 @pytest.fixture(scope="module")
@@ -36,10 +39,10 @@ def zoo(tmp_path_factory):
         if key not in cache:
             config, _ = H.CONFIGS[name]
             folder = H.make_model_folder(tmp_path_factory.mktemp(f"m{name}{dtype}"), config,
-                                         seed=11 + ord(name), dtype=dtype)
+                                         seed=11 + ord(name), dtype=dtype, init_std=H.INIT_STD[name])
             requests = {f"r{i}": H.random_tokens(n, config["vocab_size"], seed=100 * ord(name) + i)
                         for i, n in enumerate(LENGTHS[name])}
-            plain = {uid: H.plain_logits(folder, toks) for uid, toks in requests.items()}
+            plain = {uid: H.plain_logits(folder, toks).float() for uid, toks in requests.items()}
             cache[key] = (folder, requests, plain)
         return cache[key]
 
@@ -63,18 +66,50 @@ PLANS = {
 }
 
 
+def make_plan(mode, name, requests):
+    if name in HOT and mode in ("portions", "mixed"):
+        return PLANS[mode](requests, sizes=H.SIZES_WIDE)
+    return PLANS[mode](requests)
+
+
+# kernels that a mode must have launched on the hot configurations in bfloat16
+FIRED = {
+    "whole": ["gemm_tc_rows_pair", "attention_prefill_tc", "qk_norm_rope_store_whole"],
+    "bulk_then_single": ["gemm_tc_few", "gemm_tc_few_norm", "gemm_tc_few_qkv", "attention_decode_mma",
+                         "attention_combine"],
+    "portions": ["gemm_tc_few", "gemm_tc_few_qkv", "gemm_tc_cluster", "gemm_tc_rows_pair",
+                 "attention_prefill_tc"],
+    "mixed": ["gemm_tc_cluster", "gemm_tc_rows_pair", "attention_prefill_tc", "attention_decode_mma"],
+}
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("mode", list(PLANS))
 def test_replay_matches_plain(zoo, name, dtype, mode):
+    from lockstep_b200 import kernels as K
+
     folder, requests, plain = zoo(name, dtype)
-    steps = PLANS[mode](requests)
+    steps = make_plan(mode, name, requests)
     runner = make_runner(folder, name, dtype, steps)
+    before = K.kernel_counts()
     rows = H.run_plan(runner, steps)
+    after = K.kernel_counts()
     assert len(rows) == sum(len(t) for t in requests.values())
-    H.assert_rows_close(rows, plain, dtype, f"{name}/{dtype}/{mode}")
+    H.assert_rows_close(rows, plain, dtype, f"{name}/{dtype}/{mode}", config=name)
     runner.cache.audit()
     assert runner.cache.free_pages() == runner.cache.total_pages()
+    if name in HOT and dtype == "bfloat16":
+        idle = [k for k in FIRED[mode] if after.get(k, 0) == before.get(k, 0)]
+        assert not idle, f"{name}/{mode}: these kernels never ran: {idle}"
+        if name == "D":
+            assert after["gemm_tc_walk"] > before["gemm_tc_walk"], "the head product did not take the persistent kernel"
+        if mode == "portions":
+            assert any(len(t) > 128 for s in steps for _, t, _ in s["entries"])
+            assert any(32 < len(t) <= 128 for s in steps for _, t, _ in s["entries"])
+    if dtype == "float32":
+        used = [k for k in after if after[k] != before.get(k, 0) and ("_tc" in k or "_mma" in k)]
+        assert not used, f"a tensor-core kernel ran on the 32-bit path: {used}"
     if mode == "mixed":
         assert runner.cache.reused_pages() > 0, "the pool was too large: no page was used again"
         assert any(len(s["entries"]) > 1 and any(len(t) > 1 for _, t, _ in s["entries"])
@@ -86,13 +121,13 @@ def test_replay_matches_plain(zoo, name, dtype, mode):
         assert runner.graphs is not None and runner.graphs.replays > 50, "decode steps were not replayed from graphs"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_float32_cuttings_agree_bitwise(zoo, name):
     """In float32 every reduction's order is fixed by the row alone, so the bits agree."""
     folder, requests, _ = zoo(name, "float32")
     ref = None
-    for mode, plan in PLANS.items():
-        steps = plan(requests)
+    for mode in PLANS:
+        steps = make_plan(mode, name, requests)
         rows = H.run_plan(make_runner(folder, name, "float32", steps), steps)
         if ref is None:
             ref = rows
@@ -124,7 +159,7 @@ def test_trace_run_program(zoo, tmp_path, dtype):
             start = held.get(uid, 0)
             for w in want:
                 ref = plain[uid][start + w].float().numpy()
-                assert np.abs(got[r] - ref).max() <= H.tolerance(dtype, plain[uid]), (i, uid, start + w)
+                assert np.abs(got[r] - ref).max() <= H.tolerance(dtype, plain[uid], "B"), (i, uid, start + w)
                 r += 1
             held[uid] = start + len(toks)
         assert r == got.shape[0]
@@ -138,4 +173,42 @@ def test_long_decoding_and_first_tokens(zoo):
         steps = [{"entries": [("r1", toks[i:i + 1], [0])], "end": ["r1"] if i == len(toks) - 1 else []}
                  for i in range(len(toks))]
         rows = H.run_plan(make_runner(folder, "A", dtype, steps), steps)
-        H.assert_rows_close(rows, plain, dtype, f"token by token/{dtype}")
+        H.assert_rows_close(rows, plain, dtype, f"token by token/{dtype}", config="A")
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_bfloat16_rows_do_not_depend_on_the_neighbours(zoo, name):
+    """One request, cut the same way, alone and beside other requests of other lengths (so that
+    its products run in other kernels and its rows lie elsewhere in the batch): the same bits.
+    Every sum's order is a function of the row alone, in bfloat16 too."""
+    folder, requests, _ = zoo(name, "bfloat16")
+    uid, toks = "r2", requests["r2"]
+    cuts = [140, 30, 9] + [1] * 24                       # a long portion, shorter ones, then decoding
+    mine, at = [], 0
+    for n in cuts:
+        mine.append((uid, toks[at:at + n], list(range(n))))
+        at += n
+    alone = [{"entries": [m], "end": []} for m in mine]
+    alone[-1]["end"] = [uid]
+    others = {"r1": requests["r1"], "r4": requests["r4"], "r0": requests["r0"]}
+    # neighbours: a portion of 150 beside the first step (many-token kernel), 40 beside the second
+    # (64-token tiles), decoded tokens and small portions beside the rest
+    beside = []
+    pos = {u: 0 for u in others}
+    plan = [[("r1", 150)], [("r4", 40)], [("r0", 3), ("r1", 1)]] + [[("r1", 1), ("r4", 1), ("r0", 1)]] * 24
+    for m, extra in zip(mine, plan):
+        entries = []
+        for u, n in extra[:1]:                           # one neighbour before, the others after
+            entries.append((u, others[u][pos[u]:pos[u] + n], []))
+            pos[u] += n
+        entries.append(m)
+        for u, n in extra[1:]:
+            entries.append((u, others[u][pos[u]:pos[u] + n], []))
+            pos[u] += n
+        beside.append({"entries": entries, "end": []})
+    beside[-1]["end"] = [uid, *others]
+    rows_alone = H.run_plan(make_runner(folder, name, "bfloat16", alone), alone)
+    rows_beside = H.run_plan(make_runner(folder, name, "bfloat16", beside), beside)
+    assert len(rows_alone) == sum(cuts)
+    for key, row in rows_alone.items():
+        assert torch.equal(row, rows_beside[key]), f"position {key[1]} of {uid} changes with its neighbours"

@@ -319,3 +319,47 @@ def test_run_ahead_counts_pages_for_the_whole_step():
     assert sched.stats["preemptions"] > 0 and sched.stats["preemptions"] == plain_sched.stats["preemptions"]
     sched.cache.audit()
     assert sched.cache.free_pages() == sched.cache.total_pages()
+
+
+# -- the debugging aids: lifecycle table, trajectory record ------------------------------------
+
+def test_every_event_is_a_legal_transition_and_an_illegal_one_raises():
+    from lockstep_b200.engine.lifecycle import TRANSITIONS, IllegalTransition, Lifecycle
+
+    taken = set()
+    # plenty of room; so few pages that requests are preempted; prefix reuse with evictions; portions
+    reqs = [Request(uid=f"p{i}", prompt=[2 + i, 3, 4, 5] * (1 + i), max_new_tokens=12) for i in range(4)]
+    for kw in ({}, {"pages": 9, "page": 4}, {"pages": 14, "page": 4, "enable_prefix_cache": True},
+               {"policy": FixedChunkPolicy(3)}):
+        fresh = [Request(uid=r.uid, prompt=list(r.prompt), max_new_tokens=r.max_new_tokens) for r in reqs]
+        out, sched, _ = run(fresh, **kw)
+        assert all(out[r.uid] == expected(r.prompt, 12) for r in reqs)
+        taken |= sched.lifecycle.taken
+        assert not sched.lifecycle.state              # every request reached its end
+    shared = [Request(uid=f"s{i}", prompt=list(range(8)) + [20 + i], max_new_tokens=3) for i in range(3)]
+    out, sched, _ = run(shared, pages=5, page=4, enable_prefix_cache=True, max_running=1)
+    taken |= sched.lifecycle.taken
+    assert ("admitted", "cache_hit") in taken and ("decoding", "preempt") in taken
+    assert any(event == "evict" for _, event in taken)
+    assert taken <= set(TRANSITIONS)
+    life = Lifecycle()
+    life.observe("x", "admit")
+    with pytest.raises(IllegalTransition, match="cannot follow"):
+        life.observe("x", "finish")                   # nothing was decoded yet
+    with pytest.raises(IllegalTransition):
+        Lifecycle().observe("y", "decode")            # never admitted
+
+
+def test_trajectory_names_the_first_step_that_differs():
+    def go(prompt_of_b, **kw):
+        reqs = [Request(uid="a", prompt=[5, 6, 7, 8, 9], max_new_tokens=9),
+                Request(uid="b", prompt=prompt_of_b, max_new_tokens=6)]
+        out, sched, _ = run(reqs, trajectory=True, policy=FixedChunkPolicy(2), **kw)
+        return sched.trajectory
+
+    one, two = go([1, 2, 3, 4, 5, 6, 7]), go([1, 2, 3, 4, 5, 6, 7])
+    assert one.steps > 5 and one.hexdigest() == two.hexdigest() and one.first_divergence(two) is None
+    other = go([1, 2, 3, 4, 5, 6, 99])                # b's prompt differs in its fourth portion
+    assert other.hexdigest() != one.hexdigest() and one.first_divergence(other) == 3
+    pages = go([1, 2, 3, 4, 5, 6, 7], pages=32)      # the same tokens from another pool: the cache digest differs
+    assert one.first_divergence(pages) == 0
