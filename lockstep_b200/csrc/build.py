@@ -35,7 +35,7 @@ LIBRARIES: dict[str, list[str]] = {
     "tc": ["gemm_tc.cu", "attention_decode_mma.cu", "attention_prefill_tc.cu"],
 }
 
-_HEADERS = ["common.cuh", "no_alloc.h", "rope.cuh", "attention_fold.cuh"]
+_HEADERS = ["common.cuh", "tc_common.cuh", "no_alloc.h", "rope.cuh", "attention_fold.cuh"]
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 

@@ -37,6 +37,7 @@
 
 #include "common.cuh"
 #include "rope.cuh"
+#include "tc_common.cuh"
 
 // Into how many shares K is cut for a weight of N rows and depth K: a function of the
 // weight's shape alone.  With few tokens a block streams one share of one row tile, a block
@@ -74,125 +75,7 @@ namespace {
 constexpr int BM = 128;           // rows of W per tile (MMA M)
 constexpr int BK = 64;            // K elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr int A_BYTES = BM * BK * 2;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// bounded wait: false when the limit ran out
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
-                                            uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-
-// shared-memory matrix descriptor: K-major rows of 128 bytes with 128-byte
-// swizzle, groups of 8 rows 1024 bytes apart
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
-// instruction descriptor: D float32, A and B bfloat16, both K-major, M x N
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc,
-                                     uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// true in one lane of the (converged) warp
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "elect.sync _|p, 0xffffffff;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(pred));
-  return pred != 0;
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_wait() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void fence_before_sync() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void fence_after_sync() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
-__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
 // silu(a) * up as every epilogue of this file computes it: the exponential and the reciprocal
 // are the hardware's approximations (within 2 ulp each; the product is rounded to bfloat16 by
@@ -379,8 +262,8 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
       }
       fence_after_sync();
       const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
-      const uint64_t adesc = smem_desc(stage), udesc = smem_desc(stage + A_BYTES);
-      const uint64_t bdesc = smem_desc(stage + S::A_TILES * A_BYTES);
+      const uint64_t adesc = desc_k_major(stage), udesc = desc_k_major(stage + A_BYTES);
+      const uint64_t bdesc = desc_k_major(stage + S::A_TILES * A_BYTES);
       if (issuer) {
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -775,7 +658,7 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const uint32_t stage = base + (uint32_t)s * STAGE_BYTES;
       const uint32_t xs = NORM ? x_base + (uint32_t)(kb * BN * 128) : stage + A_TILES * A_BYTES;
       // a step of 16 elements along K is 32 bytes: 2 in the descriptor's address field
-      const uint64_t adesc = smem_desc(stage), udesc = smem_desc(stage + A_BYTES), bdesc = smem_desc(xs);
+      const uint64_t adesc = desc_k_major(stage), udesc = desc_k_major(stage + A_BYTES), bdesc = desc_k_major(xs);
       if (issuer) {
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -946,27 +829,6 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
 }
 
-// ---------------------------------------------------------------------------
-// The persistent form: a block per SM walks output tiles, and within a tile the
-// shares of K, in one stream.  Two accumulator regions in tensor memory
-// alternate share by share: while the MMA warp fills one, the epilogue warps
-// drain the other into the running sum they keep in registers
-// (((0 + p_0) + p_1) + ...), and after a tile's last share they write it out,
-// all while the next tile's products already run.
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-
 // EW epilogue warps: 4 (192 threads; up to 128 running sums per thread) or 8 (320 threads: the
 // silu-mul epilogue at 128 tokens has 256 columns, which two groups of four warps split).
 template <int BN, int EPI, typename TC, int EW>
@@ -1080,8 +942,8 @@ gemm_tc_walk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           }
           fence_after_sync();
           const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
-          const uint64_t adesc = smem_desc(stage), udesc = smem_desc(stage + A_BYTES);
-          const uint64_t bdesc = smem_desc(stage + S::A_TILES * A_BYTES);
+          const uint64_t adesc = desc_k_major(stage), udesc = desc_k_major(stage + A_BYTES);
+          const uint64_t bdesc = desc_k_major(stage + S::A_TILES * A_BYTES);
           if (issuer) {
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -1408,7 +1270,7 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
             fence_after_sync();
             const uint32_t stage = base + (uint32_t)s * S::STAGE_BYTES;
-            const uint64_t adesc = smem_desc(stage), bdesc = smem_desc(stage + S::X_BYTES);
+            const uint64_t adesc = desc_k_major(stage), bdesc = desc_k_major(stage + S::X_BYTES);
             if (issuer) {
 #pragma unroll
               for (int h = 0; h < S::STAGE_KB; ++h) {
@@ -1510,8 +1372,8 @@ gemm_tc_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if constexpr (sizeof(TC) == 4) {
               piece = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
             } else {
-              piece.x = pack2_bf16(v[0], v[1]); piece.y = pack2_bf16(v[2], v[3]);
-              piece.z = pack2_bf16(v[4], v[5]); piece.w = pack2_bf16(v[6], v[7]);
+              piece.x = pack_bf16(v[0], v[1]); piece.y = pack_bf16(v[2], v[3]);
+              piece.z = pack_bf16(v[4], v[5]); piece.w = pack_bf16(v[6], v[7]);
             }
             *reinterpret_cast<uint4*>(mine + lane * 128 + ((j ^ (lane & 7)) << 4)) = piece;
           }
