@@ -211,8 +211,12 @@ def time_e2e(engine, batch, context, steps, warmup, repeats=REPEATS):
                         max_new_tokens=steps + warmup + 4) for i in range(batch)]
         for r in reqs:
             engine.submit(r)
-        while not all(r.generated for r in reqs):       # the prompts, in portions under the step's budget
+        # the prompts go in one step (a budget for all of them), so that every request decodes
+        # at the same context in the timed steps
+        budget, sched.max_step_tokens = sched.max_step_tokens, batch * context
+        while not all(r.generated for r in reqs):
             sched.step()
+        sched.max_step_tokens = budget
         for _ in range(warmup):
             sched.step()
         sched.drain()

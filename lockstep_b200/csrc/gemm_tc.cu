@@ -829,6 +829,14 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
 }
 
+// ---------------------------------------------------------------------------
+// The persistent form: a block per SM walks output tiles, and within a tile the
+// shares of K, in one stream.  Two accumulator regions in tensor memory
+// alternate share by share: while the MMA warp fills one, the epilogue warps
+// drain the other into the running sum they keep in registers
+// (((0 + p_0) + p_1) + ...), and after a tile's last share they write it out,
+// all while the next tile's products already run.
+// ---------------------------------------------------------------------------
 // EW epilogue warps: 4 (192 threads; up to 128 running sums per thread) or 8 (320 threads: the
 // silu-mul epilogue at 128 tokens has 256 columns, which two groups of four warps split).
 template <int BN, int EPI, typename TC, int EW>
