@@ -35,7 +35,6 @@
 // own copies in flight, frees its tensor memory, returns).
 #include <cuda.h>
 
-#include "attention_fold.cuh"
 #include "common.cuh"
 #include "rope.cuh"
 #include "tc_common.cuh"
@@ -152,13 +151,6 @@ struct NormArgs {
   int gain_bf16;           // element type of gain: 1 bfloat16, 0 float32
   int src_rows;
   float eps;
-  // Or (part_acc != null) the token operand is the output of split attention, folded here from
-  // its partials instead of by a combine kernel: row t, column k is head k / d, element k % d
-  // of the token whose splits items[t] = (token, first slot, slot stride, splits) names.
-  const float* part_acc;   // [slots, nq, d]
-  const float* part_ml;    // [slots, nq, 2]
-  const int* items;        // [T, 4]
-  int nq, d;
 };
 
 template <int BN, int EPI, typename TC>
@@ -527,62 +519,6 @@ __device__ __forceinline__ void normed_rows_to_smem(const NormArgs& norm, const 
   }
 }
 
-// Row t of the token tile folded from attention partials and rounded to bfloat16, written into
-// the swizzled operand layout: the arithmetic of ls_fold_row (attention_fold.cuh) and the
-// rounding of the combine kernel's store, so the product reads the bits it would read from a
-// combined attention output in memory.  A lane takes four neighbouring columns (one head: a
-// head size is a multiple of 16), whose scales it works out once.
-template <int BN>
-__device__ __forceinline__ void folded_row_to_smem(const NormArgs& a, uint8_t* x_region, int t, int t0, int k_lo,
-                                                   int k_hi, int num_kb, int lane) {
-  const int* it = a.items + (int64_t)(t0 + t) * 4;
-  const int64_t first = it[1], stride = it[2];
-  const int n = it[3];
-  for (int k = k_lo + 4 * lane; k < k_lo + num_kb * BK; k += 128) {
-    uint2 packed = make_uint2(0u, 0u);               // columns past K: the weight's are zero there
-    if (k < k_hi) {
-      const int h = k / a.d, c = k - h * a.d;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      float m_run = -CUDART_INF_F, l_run = 0.f;
-      for (int s0 = 0; s0 < n; s0 += 8) {
-        float2 ml[8];
-        float4 part[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (s0 + j < n) {
-            const int64_t slot = first + (int64_t)(s0 + j) * stride;
-            ml[j] = *reinterpret_cast<const float2*>(a.part_ml + (slot * a.nq + h) * 2);
-            part[j] = *reinterpret_cast<const float4*>(a.part_acc + (slot * a.nq + h) * a.d + c);
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (s0 + j < n) {
-            float alpha, beta, m_new;
-            ls_fold_scales(m_run, ml[j].x, alpha, beta, m_new);
-            if (ml[j].x != -CUDART_INF_F) {
-              acc[0] = ls_fold_value(acc[0], alpha, part[j].x, beta);
-              acc[1] = ls_fold_value(acc[1], alpha, part[j].y, beta);
-              acc[2] = ls_fold_value(acc[2], alpha, part[j].z, beta);
-              acc[3] = ls_fold_value(acc[3], alpha, part[j].w, beta);
-              l_run = ls_fold_value(l_run, alpha, ml[j].y, beta);
-              m_run = m_new;
-            }
-          }
-        }
-      }
-      float o[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) o[e] = l_run > 0.f ? __fdiv_rn(acc[e], l_run) : 0.f;
-      packed.x = pack_bf16(o[0], o[1]);
-      packed.y = pack_bf16(o[2], o[3]);
-    }
-    const int kk_all = k - k_lo;
-    const int kb = kk_all >> 6, kk = kk_all & 63;
-    *reinterpret_cast<uint2*>(x_region + t * 128 + kb * (BN * 128) + (((kk >> 3) ^ (t & 7)) << 4) + (kk & 7) * 2) = packed;
-  }
-}
-
 template <int BN, int EPI, typename TC, bool NORM>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -750,7 +686,7 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int k_lo = kb_begin * BK;
     const int k_hi = kb_end * BK < K ? kb_end * BK : K;
     float4 gain_kept[GAIN_KEEP];
-    if (NORM && norm.part_acc == nullptr) {
+    if (NORM) {
 #pragma unroll
       for (int j = 0; j < GAIN_KEEP; ++j) {
         const int g = (k_lo >> 2) + lane + 32 * j;
@@ -774,14 +710,9 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     float first_old = 0.f;      // residual epilogue: the old value of the first column this block folds
     if (EPI == 1 && rank < valid && n < N) first_old = ls_to_float<TC>(C[(int64_t)(t0 + rank) * ldc + n]);
     if (NORM) {
-      if (norm.part_acc != nullptr) {
-        for (int t = warp - 2; t < valid; t += 4)
-          folded_row_to_smem<BN>(norm, aligned + lay.x_off, t, t0, k_lo, k_hi, num_kb, lane);
-      } else {
-        for (int t = warp - 2; t < valid; t += 8)
-          normed_rows_to_smem<BN>(norm, gain_kept, aligned + lay.x_off, t, t + 4 < valid ? t + 4 : -1, t0, K, k_lo,
-                                  k_hi, num_kb, lane, err);
-      }
+      for (int t = warp - 2; t < valid; t += 8)
+        normed_rows_to_smem<BN>(norm, gain_kept, aligned + lay.x_off, t, t + 4 < valid ? t + 4 : -1, t0, K, k_lo, k_hi,
+                                num_kb, lane, err);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(x_ready);
@@ -1661,8 +1592,7 @@ int launch_few(const CUtensorMap& mw, const CUtensorMap& mx, const NormArgs& nor
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = ls_dependent_launch ? 2 : 1;
-  LS_COUNT(EPI == 3 ? LS_K_GEMM_TC_FEW_QKV : !NORM ? LS_K_GEMM_TC_FEW
-           : norm.part_acc != nullptr ? LS_K_GEMM_TC_FEW_FOLD : LS_K_GEMM_TC_FEW_NORM);
+  LS_COUNT(EPI == 3 ? LS_K_GEMM_TC_FEW_QKV : NORM ? LS_K_GEMM_TC_FEW_NORM : LS_K_GEMM_TC_FEW);
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_few_kernel<BN, EPI, TC, NORM>, mw, mx, norm, heads, (TC*)C, T, N,
                                      K, ldc, plan.kb_per_share, plan.shares, lay, err);
   if (e != cudaSuccess) return (int)e;
@@ -1872,12 +1802,7 @@ int run(const void* X, const NormArgs* norm, const LsQkvStore* heads, const void
     // cluster norms all rows again, which pays only while they are few), and only while
     // the normed rows of one share fit their shared-memory budget
     if (!plan.in_cluster || bn > 32 || plan.kb_per_share * bn * 128 > NORM_X_BYTES) return LS_E_SIZE;
-    if (norm->part_acc != nullptr) {
-      if (norm->d <= 0 || (norm->d % 4) || (int64_t)norm->nq * norm->d != K) return LS_E_SIZE;
-      if (((uintptr_t)norm->part_acc & 15) || ((uintptr_t)norm->part_ml & 7)) return LS_E_ALIGN;
-    } else if ((K % 4) || ((uintptr_t)norm->h & 15) || ((uintptr_t)norm->gain & 15)) {
-      return LS_E_ALIGN;
-    }
+    if ((K % 4) || ((uintptr_t)norm->h & 15) || ((uintptr_t)norm->gain & 15)) return LS_E_ALIGN;
     mx = mw;
   }
   switch (bn) {
@@ -1940,7 +1865,7 @@ LS_API int ls_gemm_nt_tc_rmsnorm(const float* h, const int* row_index, int src_r
                                  int N, int K, int64_t ldw, int64_t ldc, int epilogue, int* err,
                                  cudaStream_t stream) {
   if (gain_dtype != LS_F32 && gain_dtype != LS_BF16) return LS_E_DTYPE;
-  NormArgs norm = {};
+  NormArgs norm;
   norm.h = h;
   norm.row_index = row_index;
   norm.gain = gain;
@@ -1949,24 +1874,6 @@ LS_API int ls_gemm_nt_tc_rmsnorm(const float* h, const int* row_index, int src_r
   norm.eps = eps;
   if (epilogue == 3) return LS_E_SIZE;
   return run(nullptr, &norm, nullptr, W, C, c_dtype, T, N, K, 0, ldw, ldc, epilogue, err, stream);
-}
-
-// The same product with the token operand folded from the partials of split attention
-// (decode rows): X[t, h * d + c] = fold over the splits that items[t] names of element c of
-// head h, bit for bit what ls_attention_combine writes and ls_gemm_nt_tc then reads.  K must
-// equal nq * d.  Few tokens only (the cluster form); LS_E_SIZE or LS_E_ALIGN, having launched
-// nothing, where it does not apply, and the caller then runs the combine and the product.
-LS_API int ls_gemm_nt_tc_fold(const float* part_acc, const float* part_ml, const int* items, int nq, int d,
-                              const void* W, void* C, int c_dtype, int T, int N, int K, int64_t ldw, int64_t ldc,
-                              int epilogue, int* err, cudaStream_t stream) {
-  if (epilogue == 3 || part_acc == nullptr || part_ml == nullptr || items == nullptr) return LS_E_SIZE;
-  NormArgs fold = {};
-  fold.part_acc = part_acc;
-  fold.part_ml = part_ml;
-  fold.items = items;
-  fold.nq = nq;
-  fold.d = d;
-  return run(nullptr, &fold, nullptr, W, C, c_dtype, T, N, K, 0, ldw, ldc, epilogue, err, stream);
 }
 
 // The q/k/v projection of few tokens with its heads finished in the epilogue: what
@@ -2010,7 +1917,7 @@ LS_API int ls_gemm_nt_tc_qkv_heads(const void* X, int64_t ldx, const float* h, c
   const int N = (nq + 2 * nkv) * d;
   if (h == nullptr) return run(X, nullptr, &heads, W, nullptr, LS_BF16, T, N, K, ldx, ldw, 0, 3, err, stream);
   if (gain_dtype != LS_F32 && gain_dtype != LS_BF16) return LS_E_DTYPE;
-  NormArgs norm = {};
+  NormArgs norm;
   norm.h = h;
   norm.row_index = row_index;
   norm.gain = gain;

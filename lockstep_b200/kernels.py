@@ -85,8 +85,6 @@ _SIGNATURES["tc"] = {
                               c_int, c_int, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p],
     "ls_gemm_nt_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                       c_int, c_void_p, c_void_p],
-    "ls_gemm_nt_tc_fold": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-                           c_int, c_int64, c_int64, c_int, c_void_p, c_void_p],
 }
 
 _libs: dict[str, ctypes.CDLL] = {}
@@ -419,30 +417,6 @@ def gemm_nt_tc_rmsnorm(h: torch.Tensor, gain: torch.Tensor, eps: float, w: torch
     if status in (-2, -3):
         return False
     _check(status, "gemm_nt_tc_rmsnorm")
-    return True
-
-
-def gemm_nt_tc_folded(part_acc: torch.Tensor, part_ml: torch.Tensor, items: torch.Tensor, nq: int, d: int,
-                      w: torch.Tensor, c: torch.Tensor, epilogue: int, err: torch.Tensor) -> bool:
-    """c = epilogue(attn @ w.T) where ``attn`` [tokens, nq * d] is the output of split attention,
-    folded from its partials inside the product's kernel instead of by ``attention_combine``:
-    row t is the token whose splits ``items[t]`` names.  The same bits as the combine followed
-    by ``gemm_nt_tc``.  Returns False, having launched nothing, where the fused form does not
-    apply (many tokens, a weight whose depth is not shared out)."""
-    if not USE_TENSOR_CORES[0] or w.dtype != torch.bfloat16:
-        return False
-    m, n = c.shape
-    k = nq * d
-    rows_w = 2 * n if epilogue == EPILOGUE_SILU_MUL else n
-    if w.shape != (rows_w, k) or items.shape != (m, 4) or part_acc.shape[1:] != (nq, d) or part_ml.shape[1:] != (nq, 2):
-        raise KernelError("gemm_nt_tc_folded: shapes do not agree")
-    status = library("tc").ls_gemm_nt_tc_fold(
-        _dev(part_acc, "part_acc", torch.float32), _dev(part_ml, "part_ml", torch.float32),
-        _dev(items, "items", torch.int32), nq, d, _dev(w, "w"), _dev(c, "c"), _code(c), m, n, k, k, n, epilogue,
-        _dev(err, "err", torch.int32), _stream())
-    if status in (-2, -3):
-        return False
-    _check(status, "gemm_nt_tc_folded")
     return True
 
 

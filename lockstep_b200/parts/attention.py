@@ -114,11 +114,6 @@ class GQAttention(Mixer):
                 K.attention_tile(q, cache.pages, None, part_acc, part_ml, plan.split_work,
                                  plan.n_split, cache.block_table, nq, nkv, d, self.window,
                                  self.scale, self.rt.err)
-            # every row of the step is a decoded token: the output product folds the splits itself
-            if (not self.exact and not plan.n_tile and plan.n_combine == t and t <= K.FEW_TOKENS
-                    and K.gemm_nt_tc_folded(part_acc, part_ml, plan.combine_items, nq, d, self.w_o, residual,
-                                            K.EPILOGUE_RESIDUAL, self.rt.err)):
-                return
             K.attention_combine(part_acc, part_ml, attn, plan.combine_items, plan.n_combine, nq, d)
         K.gemm_nt(attn, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=self.rt.err)
 

@@ -251,76 +251,3 @@ def test_qkv_heads_in_the_product_decline_what_they_do_not_cover():
     shallow = torch.zeros((nq + 2 * nkv) * d, 128, dtype=torch.bfloat16, device=dev())
     assert K.library("tc").ls_gemm_tc_k_shares(shallow.shape[0], 128) == 1
     assert not call(8, w_=shallow)
-
-
-@pytest.mark.parametrize("t,nq,d,n,splits", [(8, 16, 128, 1024, [17, 1, 3, 16, 9, 2, 5, 8]),
-                                              (1, 8, 64, 512, [4]), (19, 8, 64, 300, None), (32, 16, 128, 1024, None)])
-def test_attention_fold_inside_the_product_gives_the_same_bits(t, nq, d, n, splits):
-    """The output projection of decoded rows folds the partials of split attention itself: the
-    bits of ``attention_combine`` followed by the product, and close to the float64 fold.  Rows
-    have different numbers of splits, some partials are empty (a maximum of -inf: a split wholly
-    behind a window), and the slots lie apart."""
-    import math
-
-    from lockstep_b200 import kernels as K
-
-    g = torch.Generator().manual_seed(t * 31 + d)
-    if splits is None:
-        splits = [1 + (5 * i) % 11 for i in range(t)]
-    k = nq * d
-    n_slots = sum(splits) + 3
-    acc = torch.randn(n_slots, nq, d, generator=g)
-    ml = torch.empty(n_slots, nq, 2)
-    ml[..., 0] = torch.randn(n_slots, nq, generator=g) * 3
-    ml[..., 1] = torch.rand(n_slots, nq, generator=g) * 50 + 0.5
-    items, first = [], 2
-    for i, s in enumerate(splits):
-        items.append((i, first, 1, s))
-        if s > 2:
-            ml[first + 1, :, 0] = -math.inf                 # an empty split in the middle
-            ml[first + 1, :, 1] = 0.0
-        first += s
-    items_t = torch.tensor(items, dtype=torch.int32)
-    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16)
-    res = torch.randn(t, n, generator=g)
-    accd, mld, itd, wd = acc.to(dev()), ml.to(dev()), items_t.to(dev()), w.to(dev())
-    err = K.new_error_word(dev())
-
-    attn = torch.empty(t, k, dtype=torch.bfloat16, device=dev())
-    K.attention_combine(accd, mld, attn, itd, t, nq, d)
-    want = res.to(dev()).clone()
-    assert K.gemm_nt_tc(attn, wd, want, K.EPILOGUE_RESIDUAL, err)
-    got = res.to(dev()).clone()
-    before = K.kernel_counts()["gemm_tc_few_fold"]
-    assert K.gemm_nt_tc_folded(accd, mld, itd, nq, d, wd, got, K.EPILOGUE_RESIDUAL, err)
-    assert K.kernel_counts()["gemm_tc_few_fold"] == before + 1
-    K.raise_on_fault(err)
-    assert torch.equal(got, want)
-
-    # against the fold in float64
-    plain = torch.zeros(t, nq, d, dtype=torch.float64)
-    for i, (_, f, _, s) in enumerate(items):
-        m = ml[f:f + s, :, 0].double()
-        weight = torch.exp(m - m.max(dim=0).values)          # [s, nq]; exp(-inf) = 0
-        num = (weight[..., None] * acc[f:f + s].double()).sum(0)
-        den = (weight * ml[f:f + s, :, 1].double()).sum(0)
-        plain[i] = num / den[:, None]
-    ref = res.double() + plain.reshape(t, k).to(torch.bfloat16).double() @ w.double().T
-    assert (got.cpu().double() - ref).abs().max() <= 2e-2 * (1 + float(ref.abs().max()))
-
-
-def test_attention_fold_declines_where_it_does_not_apply():
-    from lockstep_b200 import kernels as K
-
-    err = K.new_error_word(dev())
-    nq, d = 4, 64
-    for t, n, k_ok in ((40, 256, True), (8, 256, False)):
-        k = nq * d if k_ok else nq * d
-        acc = torch.zeros(t, nq, d, device=dev())
-        ml = torch.zeros(t, nq, 2, device=dev())
-        items = torch.tensor([(i, i, 1, 1) for i in range(t)], dtype=torch.int32, device=dev())
-        # 40 tokens are too many for the few-token kernel; a depth of 256 is not shared out over a cluster
-        w = torch.zeros(n, k, dtype=torch.bfloat16, device=dev())
-        c = torch.zeros(t, n, device=dev())
-        if t > 32 or K.library("tc").ls_gemm_tc_k_shares(n, k) == 1:
-            assert not K.gemm_nt_tc_folded(acc, ml, items, nq, d, w, c, K.EPILOGUE_RESIDUAL, err)
