@@ -67,6 +67,7 @@ CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16
 REPEATS = 5
+SETTLE = 24            # untimed decode steps between the prompts' step and the warm-up of the entry-point run
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 FP32_TFLOPS_NOMINAL = 80.0        # FFMA peak of the CUDA cores: the 32-bit path's compute roof
 
@@ -206,9 +207,11 @@ def time_e2e(engine, batch, context, steps, warmup, repeats=REPEATS):
     rates = []
     sched = engine.scheduler
     for rep in range(repeats):
-        start_len = context - steps - warmup - 4
+        # (after the prompts' step the device runs its first dozen decode steps some 10 % slower:
+        # SETTLE untimed steps come before the warm-up steps)
+        start_len = context - steps - warmup - SETTLE - 4
         reqs = [Request(uid=f"e{rep}-{i}", prompt=[(11 * i + j) % 1000 for j in range(start_len)],
-                        max_new_tokens=steps + warmup + 4) for i in range(batch)]
+                        max_new_tokens=steps + warmup + SETTLE + 4) for i in range(batch)]
         for r in reqs:
             engine.submit(r)
         # the prompts go in one step (a budget for all of them), so that every request decodes
@@ -217,7 +220,7 @@ def time_e2e(engine, batch, context, steps, warmup, repeats=REPEATS):
         while not all(r.generated for r in reqs):
             sched.step()
         sched.max_step_tokens = budget
-        for _ in range(warmup):
+        for _ in range(SETTLE + warmup):
             sched.step()
         sched.drain()
         torch.cuda.synchronize()
@@ -328,17 +331,17 @@ def run_ours(args):
     pk = peaks()
     batches = sorted({args.batch, 1, 64} if not args.quick else {args.batch})
     max_batch = max(batches)
-    engine = build_engine(cfg, "bfloat16", max_batch, CONTEXT)
+    engine = build_engine(cfg, args.dtype if args.only else "bfloat16", max_batch, CONTEXT)
     runner = engine.runner
     launches = [0]
     if args.only == "decode":
         ms = time_decode(runner, engine.sampler, args.batch, args.context, args.steps, args.warmup, 1, launches)[0]
-        print(json.dumps({"only": "decode", "layers": layers, "batch": args.batch, "context": args.context,
-                          "ms_per_step": round(ms, 4), "launches": launches[0]}))
+        print(json.dumps({"only": "decode", "dtype": args.dtype, "layers": layers, "batch": args.batch,
+                          "context": args.context, "ms_per_step": round(ms, 4), "launches": launches[0]}))
         return 0
     if args.only == "prefill":
         pre = time_prefill(runner, PREFILL_TOKENS, repeats=max(1, args.steps))
-        print(json.dumps({"only": "prefill", "layers": layers, "tokens": PREFILL_TOKENS,
+        print(json.dumps({"only": "prefill", "dtype": args.dtype, "layers": layers, "tokens": PREFILL_TOKENS,
                           "ms": round(statistics.median(pre), 3)}))
         return 0
 
@@ -637,6 +640,8 @@ def main():
                     help="time only this part and print a short line (for profiling a small case)")
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
                     help="mixed: a continuous batch of 64 requests through the entry point")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="element type of the --only runs (the full line always reports both)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length of the decode steps (--only decode)")
     args = ap.parse_args()
     if args.gpus != 1:

@@ -73,7 +73,8 @@ enum LsKernelId {
   "embed_gather,rmsnorm,qk_norm_rope_store,qk_norm_rope_store_whole,silu_mul,gemm_simt,attention_tile," \
   "attention_decode,attention_combine,argmax,sample,gemm_tc_few,gemm_tc_few_norm,gemm_tc_few_qkv,"      \
   "gemm_tc_cluster,gemm_tc_walk,gemm_tc_rows,gemm_tc_rows_pair,attention_decode_mma,attention_prefill_tc"
-inline unsigned long long ls_kernel_launches[LS_K_COUNT];     // one table per library
+// one table per library: hidden, so that two libraries loaded into one process do not share it
+__attribute__((visibility("hidden"))) inline unsigned long long ls_kernel_launches[LS_K_COUNT];
 #define LS_COUNT(id) (++ls_kernel_launches[id])
 
 template <typename T>
