@@ -68,6 +68,8 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
   const int tid = threadIdx.x;
   const int m = tid >> 3, sub = tid & 7;
   const int nchunk = d >> 3;           // outputs per thread: dd = sub + 8*j
+  constexpr int VEC = 16 / (int)sizeof(T);   // elements of a 16-byte piece (a head size is a multiple of 16)
+  const int pieces = d / VEC;
   const int* table_row = block_table + (int64_t)req_row * table_stride;
 
   const int pos_last = pos0 + ntok - 1;
@@ -100,19 +102,33 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
     if (key_lo_tile > s_lo) t_first = s_lo + ((key_lo_tile - s_lo) / TILE_N) * TILE_N;
     for (int n0 = t_first; n0 < s_hi; n0 += TILE_N) {
       __syncthreads();
-      for (int i = tid; i < TILE_N * d; i += 128) {
-        const int n = i / d, c = i - n * d;
+      // the tile's keys and values, 16 bytes a load: a thread takes piece `ch` of key `n`
+      // (the page of a key is looked up once per piece, not once per element)
+      for (int i = tid; i < TILE_N * pieces; i += 128) {
+        const int n = i / pieces, ch = i - n * pieces;
         const int key = n0 + n;
-        float kv = 0.f, vv = 0.f;
+        float kf[VEC], vf[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) kf[e] = vf[e] = 0.f;
         if (key < s_hi && key >= key_lo_tile) {
           const T* kp = page_ptr<T>(pages, table_row, key, 0, kvh, nkv, page_size, d, num_pages, err);
           if (kp != nullptr) {
-            kv = ls_to_float<T>(kp[c]);
-            vv = ls_to_float<T>(kp[(int64_t)nkv * page_size * d + c]);
+            const uint4 kraw = *reinterpret_cast<const uint4*>(kp + ch * VEC);
+            const uint4 vraw = *reinterpret_cast<const uint4*>(kp + (int64_t)nkv * page_size * d + ch * VEC);
+            const T* kt = reinterpret_cast<const T*>(&kraw);
+            const T* vt = reinterpret_cast<const T*>(&vraw);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+              kf[e] = ls_to_float<T>(kt[e]);
+              vf[e] = ls_to_float<T>(vt[e]);
+            }
           }
         }
-        Ks[n * dp + c] = kv;
-        Vs[n * d + c] = vv;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          Ks[n * dp + ch * VEC + e] = kf[e];
+          Vs[n * d + ch * VEC + e] = vf[e];
+        }
       }
       __syncthreads();
 
@@ -398,6 +414,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
   if (n_work <= 0) return 0;
   if (!shape_ok(nq, nkv, d, page_size, LS_SPLIT)) return LS_E_SIZE;
   if (nq > 65535) return LS_E_SIZE;
+  if ((uintptr_t)pages & 15) return LS_E_ALIGN;      // keys and values are read 16 bytes at a time
   const size_t smem = tile_smem_bytes(d);
   dim3 grid(n_work, nq);
   cudaError_t e;

@@ -69,9 +69,11 @@ def test_rmsnorm(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("m,n,k_", [(1, 70, 45), (33, 129, 100), (130, 64, 16), (5, 500, 80)])
+@pytest.mark.parametrize("m,n,k_", [(1, 70, 45), (33, 129, 100), (130, 64, 16), (5, 500, 80), (8, 1024, 3072),
+                                    (17, 300, 200), (32, 96, 64), (9, 50, 68), (40, 33, 260)])
 def test_gemm_and_epilogues(dtype, m, n, k_):
     k = K()
+    few_before = k.kernel_counts()["gemm_simt_few"]
     g = torch.Generator().manual_seed(m * n)
     a = torch.randn(m, k_, generator=g).to(dtype)
     w = (torch.randn(2 * n, k_, generator=g) * 0.3).to(dtype)
@@ -97,6 +99,18 @@ def test_gemm_and_epilogues(dtype, m, n, k_):
     one = torch.empty(1, n, dtype=dtype, device=dev())
     k.gemm_nt(ad[m - 1:m].contiguous(), wd[:n].contiguous(), one)
     assert torch.equal(one.cpu()[0], c.cpu()[m - 1])
+    if dtype == torch.float32:
+        # and among 40 rows, which the tile kernel takes whatever the depth: the few-token kernel
+        # (up to 32 float32 rows of a depth that is a multiple of 4) keeps every sum's order
+        many = torch.cat([ad, torch.randn(40, k_, device=dev())])
+        cm = torch.empty(m + 40, n, dtype=dtype, device=dev())
+        k.gemm_nt(many, wd[:n].contiguous(), cm)
+        assert torch.equal(cm[:m], c)
+        am = torch.empty(m + 40, n, dtype=dtype, device=dev())
+        k.gemm_nt(many, wd, am, k.EPILOGUE_SILU_MUL)
+        assert torch.equal(am[:m], act)
+        ran = k.kernel_counts()["gemm_simt_few"] - few_before
+        assert (ran > 0) == (k_ % 4 == 0), "the few-token kernel serves float32 rows of a depth in fours"
 
 
 def paged_from_dense(kk, vv, page_size, num_pages, seed):
