@@ -52,12 +52,15 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
                       int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
                       int window, float scale, int* err) {
   ls_dependency_sync();
-  extern __shared__ float smem[];
-  const int dp = d + 1;
-  float* Qs = smem;                    // [TILE_M][d+1]
-  float* Ks = Qs + TILE_M * dp;        // [TILE_N][d+1]
+  extern __shared__ __align__(16) float smem[];
+  // rows of Q and K are d + 4 floats apart: 16-byte pieces stay aligned, and the eight key rows a
+  // quarter of a warp reads together (keys sub, sub + 8, ...) fall into different banks
+  const int dp = d + 4;
+  constexpr int PP = TILE_N + 4;       // pitch of a row of P
+  float* Qs = smem;                    // [TILE_M][d+4]
+  float* Ks = Qs + TILE_M * dp;        // [TILE_N][d+4]
   float* Vs = Ks + TILE_N * dp;        // [TILE_N][d]
-  float* Ps = Vs + TILE_N * d;         // [TILE_M][TILE_N+1]
+  float* Ps = Vs + TILE_N * d;         // [TILE_M][TILE_N+4]
 
   const int* w = work + (int64_t)blockIdx.x * 8;
   const int req_row = w[0], tok0 = w[1], ntok = w[2], pos0 = w[3];
@@ -67,7 +70,11 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
   const int kvh = h / (nq / nkv);
   const int tid = threadIdx.x;
   const int m = tid >> 3, sub = tid & 7;
-  const int nchunk = d >> 3;           // outputs per thread: dd = sub + 8*j
+  // Outputs of a thread: dimensions sub * 4 + e + 32 * jj (e < 4) that lie below d.  Which thread
+  // holds which key's score or which output changes no sum: a score is one chain over the head's
+  // elements in ascending order, an output one chain over the tile's keys in ascending order, the
+  // sum of a tile's weights is taken over groups of four neighbouring keys and then a tree.
+  const int ngroup = (d + 31) >> 5;
   constexpr int VEC = 16 / (int)sizeof(T);   // elements of a 16-byte piece (a head size is a multiple of 16)
   const int pieces = d / VEC;
   const int* table_row = block_table + (int64_t)req_row * table_stride;
@@ -125,58 +132,92 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
           }
         }
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-          Ks[n * dp + ch * VEC + e] = kf[e];
-          Vs[n * d + ch * VEC + e] = vf[e];
+        for (int e = 0; e < VEC; e += 4) {
+          *reinterpret_cast<float4*>(Ks + n * dp + ch * VEC + e) = make_float4(kf[e], kf[e + 1], kf[e + 2], kf[e + 3]);
+          *reinterpret_cast<float4*>(Vs + n * d + ch * VEC + e) = make_float4(vf[e], vf[e + 1], vf[e + 2], vf[e + 3]);
         }
       }
       __syncthreads();
 
-      float s[4];
+      // scores of keys sub, sub + 8, sub + 16, sub + 24 of the tile: each one chain over the
+      // head's elements in ascending order
+      float s[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
       float tile_max = -CUDART_INF_F;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int n = sub * 4 + j;
-        const int key = n0 + n;
-        float dot = 0.f;
+      if (row_valid) {
+        float dot[4] = {0.f, 0.f, 0.f, 0.f};
         const float* qr = Qs + m * dp;
-        const float* kr = Ks + n * dp;
-        for (int c = 0; c < d; ++c) dot = fmaf(qr[c], kr[c], dot);
-        const bool keep = row_valid && key < s_hi && key <= qpos && key >= row_lo;
-        s[j] = keep ? dot * scale : -CUDART_INF_F;
-        tile_max = fmaxf(tile_max, s[j]);
+        const float* kr = Ks + sub * dp;
+        for (int c = 0; c < d; c += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qr + c);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kr + j * 8 * dp + c);
+            dot[j] = fmaf(q4.x, k4.x, dot[j]);
+            dot[j] = fmaf(q4.y, k4.y, dot[j]);
+            dot[j] = fmaf(q4.z, k4.z, dot[j]);
+            dot[j] = fmaf(q4.w, k4.w, dot[j]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int key = n0 + sub + 8 * j;
+          const bool keep = key < s_hi && key <= qpos && key >= row_lo;
+          s[j] = keep ? dot[j] * scale : -CUDART_INF_F;
+          tile_max = fmaxf(tile_max, s[j]);
+        }
       }
       tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
       tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
       tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
       const float m_new = fmaxf(m_s, tile_max);
       float alpha = 1.f;
-      float psum = 0.f;
       float p[4] = {0.f, 0.f, 0.f, 0.f};
       if (m_new != -CUDART_INF_F) {
         alpha = (m_s == -CUDART_INF_F) ? 0.f : expf(m_s - m_new);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          p[j] = (s[j] == -CUDART_INF_F) ? 0.f : expf(s[j] - m_new);
-          psum += p[j];
-        }
+        for (int j = 0; j < 4; ++j) p[j] = (s[j] == -CUDART_INF_F) ? 0.f : expf(s[j] - m_new);
       }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) Ps[m * PP + sub + 8 * j] = p[j];
+      __syncwarp();
+      // the sum of the tile's weights: four neighbouring keys in order, then a tree over the
+      // eight groups
+      const float4 g4 = *reinterpret_cast<const float4*>(Ps + m * PP + sub * 4);
+      float psum = 0.f;
+      psum += g4.x;
+      psum += g4.y;
+      psum += g4.z;
+      psum += g4.w;
       psum += __shfl_xor_sync(0xffffffffu, psum, 1);
       psum += __shfl_xor_sync(0xffffffffu, psum, 2);
       psum += __shfl_xor_sync(0xffffffffu, psum, 4);
       l_s = __fmaf_rn(l_s, alpha, psum);
       m_s = m_new;
+      if (row_valid) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) Ps[m * (TILE_N + 1) + sub * 4 + j] = p[j];
-      __syncwarp();
+        for (int jj = 0; jj < MAX_D / 32; ++jj) {
+          if (jj < ngroup && sub * 4 + 32 * jj < d) {
+            float a0 = __fmul_rn(acc_s[jj * 4 + 0], alpha), a1 = __fmul_rn(acc_s[jj * 4 + 1], alpha);
+            float a2 = __fmul_rn(acc_s[jj * 4 + 2], alpha), a3 = __fmul_rn(acc_s[jj * 4 + 3], alpha);
+            const float* pr = Ps + m * PP;
+            const float* vc = Vs + sub * 4 + 32 * jj;
+            for (int n = 0; n < TILE_N; n += 4) {
+              const float4 p4 = *reinterpret_cast<const float4*>(pr + n);
+              const float pn[4] = {p4.x, p4.y, p4.z, p4.w};
 #pragma unroll
-      for (int j = 0; j < MAX_D / 8; ++j) {
-        if (j < nchunk) {
-          float a = __fmul_rn(acc_s[j], alpha);
-          const float* pr = Ps + m * (TILE_N + 1);
-          const float* vc = Vs + sub + 8 * j;
-          for (int n = 0; n < TILE_N; ++n) a = fmaf(pr[n], vc[n * d], a);
-          acc_s[j] = a;
+              for (int e = 0; e < 4; ++e) {
+                const float4 v4 = *reinterpret_cast<const float4*>(vc + (n + e) * d);
+                a0 = fmaf(pn[e], v4.x, a0);
+                a1 = fmaf(pn[e], v4.y, a1);
+                a2 = fmaf(pn[e], v4.z, a2);
+                a3 = fmaf(pn[e], v4.w, a3);
+              }
+            }
+            acc_s[jj * 4 + 0] = a0;
+            acc_s[jj * 4 + 1] = a1;
+            acc_s[jj * 4 + 2] = a2;
+            acc_s[jj * 4 + 3] = a3;
+          }
         }
       }
       __syncwarp();
@@ -187,8 +228,10 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
       if (row_valid) {
         const int64_t slot = (int64_t)slot_base + m;
 #pragma unroll
-        for (int j = 0; j < MAX_D / 8; ++j)
-          if (j < nchunk) part_acc[(slot * nq + h) * d + sub + 8 * j] = acc_s[j];
+        for (int jj = 0; jj < MAX_D / 32; ++jj)
+          if (jj < ngroup && sub * 4 + 32 * jj < d)
+            *reinterpret_cast<float4*>(part_acc + (slot * nq + h) * d + sub * 4 + 32 * jj) =
+                make_float4(acc_s[jj * 4], acc_s[jj * 4 + 1], acc_s[jj * 4 + 2], acc_s[jj * 4 + 3]);
         if (sub == 0) {
           part_ml[(slot * nq + h) * 2 + 0] = m_s;
           part_ml[(slot * nq + h) * 2 + 1] = l_s;
@@ -199,8 +242,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
       ls_fold_scales(m_run, m_s, alpha, beta, m_new);
       if (m_s != -CUDART_INF_F) {
 #pragma unroll
-        for (int j = 0; j < MAX_D / 8; ++j)
-          if (j < nchunk) acc_run[j] = ls_fold_value(acc_run[j], alpha, acc_s[j], beta);
+        for (int j = 0; j < MAX_D / 8; ++j) acc_run[j] = ls_fold_value(acc_run[j], alpha, acc_s[j], beta);
         l_run = ls_fold_value(l_run, alpha, l_s, beta);
         m_run = m_new;
       }
@@ -210,8 +252,12 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
   if (slot_base < 0 && row_valid) {
     T* o = out + ((int64_t)(tok0 + m) * nq + h) * d;
 #pragma unroll
-    for (int j = 0; j < MAX_D / 8; ++j)
-      if (j < nchunk) o[sub + 8 * j] = ls_from_float<T>(l_run > 0.f ? __fdiv_rn(acc_run[j], l_run) : 0.f);
+    for (int jj = 0; jj < MAX_D / 32; ++jj)
+      if (jj < ngroup && sub * 4 + 32 * jj < d) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          o[sub * 4 + 32 * jj + e] = ls_from_float<T>(l_run > 0.f ? __fdiv_rn(acc_run[jj * 4 + e], l_run) : 0.f);
+      }
   }
 }
 
@@ -387,8 +433,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
 }
 
 size_t tile_smem_bytes(int d) {
-  return sizeof(float) * ((size_t)TILE_M * (d + 1) + (size_t)TILE_N * (d + 1) + (size_t)TILE_N * d +
-                          (size_t)TILE_M * (TILE_N + 1));
+  return sizeof(float) * ((size_t)TILE_M * (d + 4) + (size_t)TILE_N * (d + 4) + (size_t)TILE_N * d +
+                          (size_t)TILE_M * (TILE_N + 4));
 }
 
 size_t decode_smem_bytes(int d, int group, int elem) {

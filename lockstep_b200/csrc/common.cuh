@@ -67,13 +67,13 @@ enum LsKernelId {
   LS_K_GEMM_SIMT, LS_K_ATTENTION_TILE, LS_K_ATTENTION_DECODE, LS_K_ATTENTION_COMBINE, LS_K_ARGMAX,
   LS_K_SAMPLE, LS_K_GEMM_TC_FEW, LS_K_GEMM_TC_FEW_NORM, LS_K_GEMM_TC_FEW_QKV, LS_K_GEMM_TC_CLUSTER,
   LS_K_GEMM_TC_WALK, LS_K_GEMM_TC_ROWS, LS_K_GEMM_TC_ROWS_PAIR, LS_K_ATTENTION_DECODE_MMA,
-  LS_K_ATTENTION_PREFILL_TC, LS_K_GEMM_SIMT_FEW, LS_K_COUNT
+  LS_K_ATTENTION_PREFILL_TC, LS_K_GEMM_SIMT_FEW, LS_K_GEMM_SIMT_MANY, LS_K_COUNT
 };
 #define LS_KERNEL_NAMES                                                                                  \
   "embed_gather,rmsnorm,qk_norm_rope_store,qk_norm_rope_store_whole,silu_mul,gemm_simt,attention_tile," \
   "attention_decode,attention_combine,argmax,sample,gemm_tc_few,gemm_tc_few_norm,gemm_tc_few_qkv,"      \
   "gemm_tc_cluster,gemm_tc_walk,gemm_tc_rows,gemm_tc_rows_pair,attention_decode_mma,attention_prefill_tc,"     \
-  "gemm_simt_few"
+  "gemm_simt_few,gemm_simt_many"
 // one table per library: hidden, so that two libraries loaded into one process do not share it
 __attribute__((visibility("hidden"))) inline unsigned long long ls_kernel_launches[LS_K_COUNT];
 #define LS_COUNT(id) (++ls_kernel_launches[id])

@@ -1,10 +1,12 @@
 // C[M, N] = A[M, K] * W[N, K]^T on the CUDA cores (FFMA, float32 accumulate).
 //
 // This is the true 32-bit matrix product of the engine and the fallback of the
-// bfloat16 path for shapes the tensor-core kernel refuses.  One thread block
-// owns one 64x64 output tile and walks K in ascending order with one
-// accumulator per element, so an output element's value does not depend on M
-// (the batch) or on where its row lies in the batch.  There is no split-K.
+// bfloat16 path for shapes the tensor-core kernel refuses.  An output element is
+// one accumulator and one chain of FMAs over K in ascending order, so its value
+// does not depend on M (the batch) or on where its row lies in the batch.  There
+// is no split-K.  Three kernels make that same chain: the general one below (a
+// block owns a 64x64 tile; any element type, any depth), one for up to 32
+// float32 tokens and one for many float32 tokens.
 //
 // Epilogues:
 //   0 store        C[m, n]  = acc                       (C of type TC)
@@ -248,6 +250,126 @@ bool skinny_applies(const void* A, const void* W, int a_dtype, int c_dtype, int 
          ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0;
 }
 
+// ---------------------------------------------------------------------------
+// Many tokens, float32: the prompt's products on the true 32-bit path.  A block owns 128 tokens
+// x 128 features (silu-mul: 128 x 64, the other 64 columns of its tile being the up rows of the
+// same features), a thread 8 x 8 of them as four 4 x 4 corners, so that what it reads from
+// shared memory per step of k are four 16-byte pieces for 64 FMAs.  The next k-block is on its
+// way from memory to registers while this one is multiplied.  Every element is still one
+// accumulator and one ascending chain fmaf(a, w, acc), so the bits are those of the two
+// kernels above.
+// ---------------------------------------------------------------------------
+constexpr int LM = 128, LN = 128, LK = 16, LPITCH = LM + 4;
+
+template <int EPI>
+__global__ void __launch_bounds__(256, 2)
+gemm_nt_large_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int M, int N,
+                     int K, int64_t lda, int64_t ldw, int64_t ldc) {
+  constexpr int FN = EPI == 2 ? LN / 2 : LN;          // features of the tile
+  ls_dependency_sync();
+  __shared__ __align__(16) float As[2][LK][LPITCH];
+  __shared__ __align__(16) float Ws[2][LK][LPITCH];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * LM, n0 = blockIdx.x * FN;
+  // staging: a thread fetches 4 consecutive k of rows lr and lr + 64 of both operands
+  const int lr = tid >> 2, lk = (tid & 3) * 4;
+  // row of W behind column c of the tile: silu-mul tiles hold gate rows, then the up rows
+  auto w_row = [&](int c) -> int64_t {
+    if (EPI == 2) return c < FN ? (n0 + c < N ? n0 + c : -1) : (n0 + c - FN < N ? (int64_t)N + n0 + c - FN : -1);
+    return n0 + c < N ? n0 + c : -1;
+  };
+  float4 ra[2], rw[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = m0 + lr + 64 * half;
+      const int64_t wr = w_row(lr + 64 * half);
+      const bool k_ok = k0 + lk < K;                    // K is a multiple of 4: a piece is whole or absent
+      ra[half] = (m < M && k_ok) ? *reinterpret_cast<const float4*>(A + (int64_t)m * lda + k0 + lk)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+      rw[half] = (wr >= 0 && k_ok) ? *reinterpret_cast<const float4*>(W + wr * ldw + k0 + lk)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  auto stage = [&](int buf) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = lr + 64 * half;
+      As[buf][lk + 0][r] = ra[half].x; As[buf][lk + 1][r] = ra[half].y;
+      As[buf][lk + 2][r] = ra[half].z; As[buf][lk + 3][r] = ra[half].w;
+      Ws[buf][lk + 0][r] = rw[half].x; Ws[buf][lk + 1][r] = rw[half].y;
+      Ws[buf][lk + 2][r] = rw[half].z; Ws[buf][lk + 3][r] = rw[half].w;
+    }
+  };
+
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  fetch(0);
+  stage(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += LK) {
+    const bool more = k0 + LK < K;
+    if (more) fetch(k0 + LK);
+#pragma unroll
+    for (int k = 0; k < LK; ++k) {
+      const float4 a_lo = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+      const float4 a_hi = *reinterpret_cast<const float4*>(&As[buf][k][64 + ty * 4]);
+      const float4 w_lo = *reinterpret_cast<const float4*>(&Ws[buf][k][tx * 4]);
+      const float4 w_hi = *reinterpret_cast<const float4*>(&Ws[buf][k][64 + tx * 4]);
+      const float a[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
+      const float w[8] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w, w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    if (more) {
+      stage(buf ^ 1);
+      __syncthreads();
+      buf ^= 1;
+    }
+  }
+
+  // rows ty * 4 + i and 64 + ty * 4 + i; columns tx * 4 + j and 64 + tx * 4 + j
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
+    if (m >= M) continue;
+    float* crow = C + (int64_t)m * ldc;
+    if (EPI == 2) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + tx * 4 + j;
+        const float g = acc[i][j];
+        if (n < N) crow[n] = g / (1.0f + expf(-g)) * acc[i][4 + j];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
+        if (n < N) crow[n] = EPI == 1 ? crow[n] + acc[i][j] : acc[i][j];
+      }
+    }
+  }
+}
+
+template <int EPI>
+int launch_large(const float* A, const float* W, float* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                 cudaStream_t stream) {
+  constexpr int FN = EPI == 2 ? LN / 2 : LN;
+  dim3 grid((N + FN - 1) / FN, (M + LM - 1) / LM);
+  if (grid.y > 65535) return LS_E_SIZE;
+  LS_COUNT(LS_K_GEMM_SIMT_MANY);
+  ls_launch(gemm_nt_large_kernel<EPI>, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
+  return ls_launch_status();
+}
+
 template <typename TA, typename TW, typename TC>
 int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
            int64_t ldc, int epilogue, cudaStream_t stream) {
@@ -288,6 +410,16 @@ LS_API int ls_gemm_nt_simt(const void* A, const void* W, void* C, int a_dtype, i
     if (epilogue == 2) return launch_skinny<2>(a, w, (float*)C, M, N, K, lda, ldw, ldc, stream);
     return LS_E_SIZE;
   }
+  // float32 rows that can be fetched 16 bytes at a time, more than a few of them
+  if (a_dtype == LS_F32 && c_dtype == LS_F32 && M > SK_MAX_M && K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 &&
+      ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
+    const float* a = (const float*)A;
+    const float* w = (const float*)W;
+    if (epilogue == 0) return launch_large<0>(a, w, (float*)C, M, N, K, lda, ldw, ldc, stream);
+    if (epilogue == 1) return launch_large<1>(a, w, (float*)C, M, N, K, lda, ldw, ldc, stream);
+    if (epilogue == 2) return launch_large<2>(a, w, (float*)C, M, N, K, lda, ldw, ldc, stream);
+    return LS_E_SIZE;
+  }
   if (a_dtype == LS_F32 && c_dtype == LS_F32)
     return launch<float, float, float>(A, W, C, M, N, K, lda, ldw, ldc, epilogue, stream);
   if (a_dtype == LS_BF16 && c_dtype == LS_BF16)
@@ -300,6 +432,7 @@ LS_API int ls_gemm_nt_simt(const void* A, const void* W, void* C, int a_dtype, i
 LS_API const char* ls_constants_gemm_simt() {
   static char buf[256];
   static const LsConstant c[] = {{"gemm_simt.tile_m", BM}, {"gemm_simt.tile_n", BN}, {"gemm_simt.tile_k", BK},
-                                 {"gemm_simt.few_tokens", SK_MAX_M}, {"gemm_simt.few_tokens_features", SK_BN}};
+                                 {"gemm_simt.few_tokens", SK_MAX_M}, {"gemm_simt.few_tokens_features", SK_BN},
+                                 {"gemm_simt.many_tokens_tile", LM}};
   return ls_format_constants(buf, sizeof buf, c, (int)(sizeof c / sizeof c[0]));
 }
