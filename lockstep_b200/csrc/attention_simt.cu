@@ -76,6 +76,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
   // sum of a tile's weights is taken over groups of four neighbouring keys and then a tree.
   const int ngroup = (d + 31) >> 5;
   constexpr int VEC = 16 / (int)sizeof(T);   // elements of a 16-byte piece (a head size is a multiple of 16)
+  constexpr int LOADS = 4;                   // pieces of keys (and of values) a thread has in flight
   const int pieces = d / VEC;
   const int* table_row = block_table + (int64_t)req_row * table_stride;
 
@@ -109,32 +110,42 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
     if (key_lo_tile > s_lo) t_first = s_lo + ((key_lo_tile - s_lo) / TILE_N) * TILE_N;
     for (int n0 = t_first; n0 < s_hi; n0 += TILE_N) {
       __syncthreads();
-      // the tile's keys and values, 16 bytes a load: a thread takes piece `ch` of key `n`
-      // (the page of a key is looked up once per piece, not once per element)
-      for (int i = tid; i < TILE_N * pieces; i += 128) {
-        const int n = i / pieces, ch = i - n * pieces;
-        const int key = n0 + n;
-        float kf[VEC], vf[VEC];
+      // the tile's keys and values, 16 bytes a load: a thread takes piece `ch` of key `n` (the
+      // page of a key is looked up once per piece, not once per element), LOADS pieces of each
+      // at a time so that their trips to memory overlap
+      for (int i0 = tid; i0 < TILE_N * pieces; i0 += 128 * LOADS) {
+        uint4 kraw[LOADS], vraw[LOADS];
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) kf[e] = vf[e] = 0.f;
-        if (key < s_hi && key >= key_lo_tile) {
-          const T* kp = page_ptr<T>(pages, table_row, key, 0, kvh, nkv, page_size, d, num_pages, err);
-          if (kp != nullptr) {
-            const uint4 kraw = *reinterpret_cast<const uint4*>(kp + ch * VEC);
-            const uint4 vraw = *reinterpret_cast<const uint4*>(kp + (int64_t)nkv * page_size * d + ch * VEC);
-            const T* kt = reinterpret_cast<const T*>(&kraw);
-            const T* vt = reinterpret_cast<const T*>(&vraw);
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) {
-              kf[e] = ls_to_float<T>(kt[e]);
-              vf[e] = ls_to_float<T>(vt[e]);
+        for (int b = 0; b < LOADS; ++b) {
+          const int i = i0 + 128 * b;
+          kraw[b] = vraw[b] = make_uint4(0u, 0u, 0u, 0u);          // zero bits are 0.0 in either type
+          if (i < TILE_N * pieces) {
+            const int n = i / pieces, ch = i - n * pieces;
+            const int key = n0 + n;
+            if (key < s_hi && key >= key_lo_tile) {
+              const T* kp = page_ptr<T>(pages, table_row, key, 0, kvh, nkv, page_size, d, num_pages, err);
+              if (kp != nullptr) {
+                kraw[b] = *reinterpret_cast<const uint4*>(kp + ch * VEC);
+                vraw[b] = *reinterpret_cast<const uint4*>(kp + (int64_t)nkv * page_size * d + ch * VEC);
+              }
             }
           }
         }
 #pragma unroll
-        for (int e = 0; e < VEC; e += 4) {
-          *reinterpret_cast<float4*>(Ks + n * dp + ch * VEC + e) = make_float4(kf[e], kf[e + 1], kf[e + 2], kf[e + 3]);
-          *reinterpret_cast<float4*>(Vs + n * d + ch * VEC + e) = make_float4(vf[e], vf[e + 1], vf[e + 2], vf[e + 3]);
+        for (int b = 0; b < LOADS; ++b) {
+          const int i = i0 + 128 * b;
+          if (i < TILE_N * pieces) {
+            const int n = i / pieces, ch = i - n * pieces;
+            const T* kt = reinterpret_cast<const T*>(&kraw[b]);
+            const T* vt = reinterpret_cast<const T*>(&vraw[b]);
+#pragma unroll
+            for (int e = 0; e < VEC; e += 4) {
+              *reinterpret_cast<float4*>(Ks + n * dp + ch * VEC + e) = make_float4(
+                  ls_to_float<T>(kt[e]), ls_to_float<T>(kt[e + 1]), ls_to_float<T>(kt[e + 2]), ls_to_float<T>(kt[e + 3]));
+              *reinterpret_cast<float4*>(Vs + n * d + ch * VEC + e) = make_float4(
+                  ls_to_float<T>(vt[e]), ls_to_float<T>(vt[e + 1]), ls_to_float<T>(vt[e + 2]), ls_to_float<T>(vt[e + 3]));
+            }
+          }
         }
       }
       __syncthreads();
