@@ -110,40 +110,39 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
     if (key_lo_tile > s_lo) t_first = s_lo + ((key_lo_tile - s_lo) / TILE_N) * TILE_N;
     for (int n0 = t_first; n0 < s_hi; n0 += TILE_N) {
       __syncthreads();
-      // the tile's keys and values, 16 bytes a load: a thread takes piece `ch` of key `n` (the
-      // page of a key is looked up once per piece, not once per element), LOADS pieces of each
-      // at a time so that their trips to memory overlap
-      for (int i0 = tid; i0 < TILE_N * pieces; i0 += 128 * LOADS) {
-        uint4 kraw[LOADS], vraw[LOADS];
+      // the tile's keys and values, 16 bytes a load: four threads share a key (its page is looked
+      // up once per thread and tile) and take its pieces in turn, LOADS pieces of each kind in
+      // flight at a time
+      {
+        const int n = tid >> 2, key = n0 + n;
+        const T* kp = nullptr;
+        if (key < s_hi && key >= key_lo_tile)
+          kp = page_ptr<T>(pages, table_row, key, 0, kvh, nkv, page_size, d, num_pages, err);
+        const int64_t to_v = (int64_t)nkv * page_size * d;
+        for (int ch0 = tid & 3; ch0 < pieces; ch0 += 4 * LOADS) {
+          uint4 kraw[LOADS], vraw[LOADS];
 #pragma unroll
-        for (int b = 0; b < LOADS; ++b) {
-          const int i = i0 + 128 * b;
-          kraw[b] = vraw[b] = make_uint4(0u, 0u, 0u, 0u);          // zero bits are 0.0 in either type
-          if (i < TILE_N * pieces) {
-            const int n = i / pieces, ch = i - n * pieces;
-            const int key = n0 + n;
-            if (key < s_hi && key >= key_lo_tile) {
-              const T* kp = page_ptr<T>(pages, table_row, key, 0, kvh, nkv, page_size, d, num_pages, err);
-              if (kp != nullptr) {
-                kraw[b] = *reinterpret_cast<const uint4*>(kp + ch * VEC);
-                vraw[b] = *reinterpret_cast<const uint4*>(kp + (int64_t)nkv * page_size * d + ch * VEC);
-              }
+          for (int b = 0; b < LOADS; ++b) {
+            const int ch = ch0 + 4 * b;
+            kraw[b] = vraw[b] = make_uint4(0u, 0u, 0u, 0u);        // zero bits are 0.0 in either type
+            if (kp != nullptr && ch < pieces) {
+              kraw[b] = *reinterpret_cast<const uint4*>(kp + ch * VEC);
+              vraw[b] = *reinterpret_cast<const uint4*>(kp + to_v + ch * VEC);
             }
           }
-        }
 #pragma unroll
-        for (int b = 0; b < LOADS; ++b) {
-          const int i = i0 + 128 * b;
-          if (i < TILE_N * pieces) {
-            const int n = i / pieces, ch = i - n * pieces;
-            const T* kt = reinterpret_cast<const T*>(&kraw[b]);
-            const T* vt = reinterpret_cast<const T*>(&vraw[b]);
+          for (int b = 0; b < LOADS; ++b) {
+            const int ch = ch0 + 4 * b;
+            if (ch < pieces) {
+              const T* kt = reinterpret_cast<const T*>(&kraw[b]);
+              const T* vt = reinterpret_cast<const T*>(&vraw[b]);
 #pragma unroll
-            for (int e = 0; e < VEC; e += 4) {
-              *reinterpret_cast<float4*>(Ks + n * dp + ch * VEC + e) = make_float4(
-                  ls_to_float<T>(kt[e]), ls_to_float<T>(kt[e + 1]), ls_to_float<T>(kt[e + 2]), ls_to_float<T>(kt[e + 3]));
-              *reinterpret_cast<float4*>(Vs + n * d + ch * VEC + e) = make_float4(
-                  ls_to_float<T>(vt[e]), ls_to_float<T>(vt[e + 1]), ls_to_float<T>(vt[e + 2]), ls_to_float<T>(vt[e + 3]));
+              for (int e = 0; e < VEC; e += 4) {
+                *reinterpret_cast<float4*>(Ks + n * dp + ch * VEC + e) = make_float4(
+                    ls_to_float<T>(kt[e]), ls_to_float<T>(kt[e + 1]), ls_to_float<T>(kt[e + 2]), ls_to_float<T>(kt[e + 3]));
+                *reinterpret_cast<float4*>(Vs + n * d + ch * VEC + e) = make_float4(
+                    ls_to_float<T>(vt[e]), ls_to_float<T>(vt[e + 1]), ls_to_float<T>(vt[e + 2]), ls_to_float<T>(vt[e + 3]));
+              }
             }
           }
         }

@@ -96,20 +96,18 @@ gemm_nt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restric
 // ---------------------------------------------------------------------------
 // Few tokens (up to 32), float32: the decode step's products on the true 32-bit path.
 // The tile kernel above would run a handful of blocks with most of their rows empty.  Here a
-// block takes 4 rows of W (4 more for silu-mul: the up rows of the same features) whole, into
-// shared memory, asked for in one go before the wait on the kernel before (weights do not
-// depend on it): with a block per 4 features there are enough blocks that what they have in
-// flight together keeps the memory busy.  The token rows stream through a small ring of
-// stages.  A thread owns one feature of one token, with the accumulator and the ascending
-// chain of FMAs it has in the tile kernel (fmaf(a, w, acc) from k = 0 up), so the kernels
-// give the same bits; a warp is one feature, its lanes the tokens.
+// block takes 16 rows of W (16 more for silu-mul: the up rows of the same features) and all
+// the tokens; a thread owns one feature and the tokens m, m + 8, m + 16, m + 24, each with the
+// accumulator and the ascending chain of FMAs it has in the tile kernel (fmaf(a, w, acc) from
+// k = 0 up), so the two kernels give the same bits.  W and the token rows stream through a
+// ring of shared-memory stages by 16-byte cp.async; the weights of the first stages are asked
+// for before the wait on the kernel before.
 // ---------------------------------------------------------------------------
-constexpr int SK_BN = 4;         // features per block
-constexpr int SK_BK = 64;        // depth of a stage of token rows
+constexpr int SK_BN = 16;        // features per block
+constexpr int SK_BK = 64;        // depth of a stage
 constexpr int SK_PITCH = SK_BK + 4;
 constexpr int SK_STAGES = 4;
 constexpr int SK_MAX_M = 32;
-constexpr size_t SK_MAX_SMEM = 200 * 1024;
 
 __device__ __forceinline__ void cp_async_16(float* dst, const float* src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -119,115 +117,131 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// XR: token rows staged (8, 16 or 32)
-template <typename TC, int EPI, int XR>
+// MT: tokens per thread (1, 2 or 4: up to 8, 16 or 32 tokens)
+template <typename TC, int EPI, int MT>
 __global__ void __launch_bounds__(128)
 gemm_nt_skinny_kernel(const float* __restrict__ A, const float* __restrict__ W, TC* __restrict__ C, int M, int N,
                       int K, int64_t lda, int64_t ldw, int64_t ldc) {
   constexpr int W_ROWS = EPI == 2 ? 2 * SK_BN : SK_BN;
-  constexpr int STAGE = XR * SK_PITCH;                     // floats
+  constexpr int X_ROWS = 8 * MT;
+  constexpr int STAGE = (W_ROWS + X_ROWS) * SK_PITCH;       // floats
   ls_dependency_trigger();
   extern __shared__ __align__(16) float sk_smem[];
-  float* wres = sk_smem;                                   // [W_ROWS][K]
-  float* xring = sk_smem + (size_t)W_ROWS * K;             // [SK_STAGES][XR][SK_PITCH]
   const int tid = threadIdx.x;
-  const int nl = tid >> 5, ml = tid & 31;
+  const int nl = tid >> 3, ml = tid & 7;
   const int n0 = blockIdx.x * SK_BN;
   const int stages_total = (K + SK_BK - 1) / SK_BK;
-  const int kq = K >> 2;                                   // 16-byte pieces of a row
 
-  // this block's rows of W, whole (rows past N are not fetched: their sums are never stored)
-  for (int i = tid; i < W_ROWS * kq; i += 128) {
-    const int r = i / kq, ch = i - r * kq;
-    const int feature = n0 + (r % SK_BN);
-    if (feature < N)
-      cp_async_16(wres + (size_t)r * K + ch * 4, W + ((int64_t)feature + (r >= SK_BN ? N : 0)) * ldw + ch * 4);
-  }
-  cp_async_commit();
-  auto load_x = [&](int st) {
-    float* xs = xring + (st % SK_STAGES) * STAGE;
+  // pieces of 16 bytes this thread fetches per stage: W rows, then token rows.  Rows past N or
+  // M and pieces past K are not fetched: what lies there is never stored (rows) or never
+  // multiplied (the loops below stop at K)
+  auto load_w = [&](int st) {
+    float* ws = sk_smem + (st % SK_STAGES) * STAGE;
     const int k0 = st * SK_BK;
-    for (int i = tid; i < XR * (SK_BK / 4); i += 128) {
+    for (int i = tid; i < W_ROWS * (SK_BK / 4); i += 128) {
+      const int r = i / (SK_BK / 4), ch = i - r * (SK_BK / 4);
+      const int n = n0 + (r % SK_BN) + (r >= SK_BN ? N : 0);          // up rows follow the gate rows at N
+      if (n0 + (r % SK_BN) < N && k0 + ch * 4 < K) cp_async_16(ws + r * SK_PITCH + ch * 4, W + (int64_t)n * ldw + k0 + ch * 4);
+    }
+  };
+  auto load_x = [&](int st) {
+    float* xs = sk_smem + (st % SK_STAGES) * STAGE + W_ROWS * SK_PITCH;
+    const int k0 = st * SK_BK;
+    for (int i = tid; i < X_ROWS * (SK_BK / 4); i += 128) {
       const int r = i / (SK_BK / 4), ch = i - r * (SK_BK / 4);
       if (r < M && k0 + ch * 4 < K) cp_async_16(xs + r * SK_PITCH + ch * 4, A + (int64_t)r * lda + k0 + ch * 4);
     }
   };
+
+  const int ahead = stages_total < SK_STAGES - 1 ? stages_total : SK_STAGES - 1;
+  for (int st = 0; st < ahead; ++st) load_w(st);          // weights do not depend on the kernel before
   ls_dependency_wait();
-  for (int st = 0; st < SK_STAGES - 1; ++st) {             // one group per stage, empty ones included
-    if (st < stages_total) load_x(st);
+  for (int st = 0; st < SK_STAGES - 1; ++st) {            // one group per stage, empty ones included
+    if (st < ahead) load_x(st);
     cp_async_commit();
   }
 
-  float acc = 0.f, acu = 0.f;
-  const float* wrow = wres + (size_t)nl * K;
-  const float* urow = wres + (size_t)(SK_BN + nl) * K;
-  const int mrow = ml < XR ? ml : 0;                       // lanes past the staged rows read row 0 and store nothing
+  float acc[MT], acu[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i) acc[i] = acu[i] = 0.f;
+
   for (int st = 0; st < stages_total; ++st) {
-    cp_async_wait<SK_STAGES - 2>();                        // stage st (and W, the oldest group) has landed for this thread
-    __syncthreads();                                       // ... for every thread; and stage st - 1 is read
-    if (st + SK_STAGES - 1 < stages_total) load_x(st + SK_STAGES - 1);
+    cp_async_wait<SK_STAGES - 2>();                       // stage st has landed (for this thread)
+    __syncthreads();                                      // ... for every thread; and stage st - 1 is read
+    if (st + SK_STAGES - 1 < stages_total) {
+      load_w(st + SK_STAGES - 1);
+      load_x(st + SK_STAGES - 1);
+    }
     cp_async_commit();
-    const float* xs = xring + (st % SK_STAGES) * STAGE + mrow * SK_PITCH;
-    const int k0 = st * SK_BK;
-    const int left = K - k0;
+    const float* ws = sk_smem + (st % SK_STAGES) * STAGE;
+    const float* xs = ws + W_ROWS * SK_PITCH;
+    const int left = K - st * SK_BK;
     const int groups = left >= SK_BK ? SK_BK / 4 : left / 4;
     for (int g = 0; g < groups; ++g) {
-      const float4 x4 = *reinterpret_cast<const float4*>(xs + 4 * g);
-      const float4 w4 = *reinterpret_cast<const float4*>(wrow + k0 + 4 * g);
-      acc = fmaf(x4.x, w4.x, acc);
-      acc = fmaf(x4.y, w4.y, acc);
-      acc = fmaf(x4.z, w4.z, acc);
-      acc = fmaf(x4.w, w4.w, acc);
-      if (EPI == 2) {
-        const float4 u4 = *reinterpret_cast<const float4*>(urow + k0 + 4 * g);
-        acu = fmaf(x4.x, u4.x, acu);
-        acu = fmaf(x4.y, u4.y, acu);
-        acu = fmaf(x4.z, u4.z, acu);
-        acu = fmaf(x4.w, u4.w, acu);
+      const float4 w4 = *reinterpret_cast<const float4*>(ws + nl * SK_PITCH + 4 * g);
+      float4 u4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (EPI == 2) u4 = *reinterpret_cast<const float4*>(ws + (SK_BN + nl) * SK_PITCH + 4 * g);
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        const float4 x4 = *reinterpret_cast<const float4*>(xs + (ml + 8 * i) * SK_PITCH + 4 * g);
+        acc[i] = fmaf(x4.x, w4.x, acc[i]);
+        acc[i] = fmaf(x4.y, w4.y, acc[i]);
+        acc[i] = fmaf(x4.z, w4.z, acc[i]);
+        acc[i] = fmaf(x4.w, w4.w, acc[i]);
+        if (EPI == 2) {
+          acu[i] = fmaf(x4.x, u4.x, acu[i]);
+          acu[i] = fmaf(x4.y, u4.y, acu[i]);
+          acu[i] = fmaf(x4.z, u4.z, acu[i]);
+          acu[i] = fmaf(x4.w, u4.w, acu[i]);
+        }
       }
     }
   }
   cp_async_wait<0>();
 
   const int n = n0 + nl;
-  if (n < N && ml < M) {
-    TC* c = C + (int64_t)ml * ldc + n;
-    if (EPI == 0) {
-      *c = ls_from_float<TC>(acc);
-    } else if (EPI == 1) {
-      *c = ls_from_float<TC>(ls_to_float<TC>(*c) + acc);
-    } else {
-      *c = ls_from_float<TC>(acc / (1.0f + expf(-acc)) * acu);
+  if (n < N) {
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      const int m = ml + 8 * i;
+      if (m >= M) continue;
+      TC* c = C + (int64_t)m * ldc + n;
+      if (EPI == 0) {
+        *c = ls_from_float<TC>(acc[i]);
+      } else if (EPI == 1) {
+        *c = ls_from_float<TC>(ls_to_float<TC>(*c) + acc[i]);
+      } else {
+        const float g = acc[i];
+        *c = ls_from_float<TC>(g / (1.0f + expf(-g)) * acu[i]);
+      }
     }
   }
 }
 
-template <typename TC, int EPI, int XR>
+template <typename TC, int EPI, int MT>
 int launch_skinny_as(const float* A, const float* W, TC* C, int M, int N, int K, int64_t lda, int64_t ldw,
                      int64_t ldc, cudaStream_t stream) {
   constexpr int W_ROWS = EPI == 2 ? 2 * SK_BN : SK_BN;
-  const size_t smem = ((size_t)W_ROWS * K + (size_t)SK_STAGES * XR * SK_PITCH) * sizeof(float);
-  if (smem > SK_MAX_SMEM) return LS_E_SMEM;
-  static size_t configured = 0;                            // largest size asked for so far
-  if (smem > configured) {
-    if (cudaFuncSetAttribute(gemm_nt_skinny_kernel<TC, EPI, XR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  constexpr size_t smem = (size_t)SK_STAGES * (W_ROWS + 8 * MT) * SK_PITCH * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_nt_skinny_kernel<TC, EPI, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return LS_E_SMEM;
-    configured = smem;
+    configured = true;
   }
   LS_COUNT(LS_K_GEMM_SIMT_FEW);
-  ls_launch(gemm_nt_skinny_kernel<TC, EPI, XR>, dim3((N + SK_BN - 1) / SK_BN), 128, smem, stream, A, W, C, M, N, K,
+  ls_launch(gemm_nt_skinny_kernel<TC, EPI, MT>, dim3((N + SK_BN - 1) / SK_BN), 128, smem, stream, A, W, C, M, N, K,
             lda, ldw, ldc);
   return ls_launch_status();
 }
 
-// LS_E_SMEM where a block's rows of W do not fit shared memory (the caller takes the tile kernel)
 template <int EPI>
 int launch_skinny(const float* A, const float* W, float* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                   cudaStream_t stream) {
-  if (M <= 8) return launch_skinny_as<float, EPI, 8>(A, W, C, M, N, K, lda, ldw, ldc, stream);
-  if (M <= 16) return launch_skinny_as<float, EPI, 16>(A, W, C, M, N, K, lda, ldw, ldc, stream);
-  return launch_skinny_as<float, EPI, 32>(A, W, C, M, N, K, lda, ldw, ldc, stream);
+  if (M <= 8) return launch_skinny_as<float, EPI, 1>(A, W, C, M, N, K, lda, ldw, ldc, stream);
+  if (M <= 16) return launch_skinny_as<float, EPI, 2>(A, W, C, M, N, K, lda, ldw, ldc, stream);
+  return launch_skinny_as<float, EPI, 4>(A, W, C, M, N, K, lda, ldw, ldc, stream);
 }
 
 // float32 operands of up to 32 tokens whose rows can be fetched 16 bytes at a time
@@ -391,11 +405,10 @@ LS_API int ls_gemm_nt_simt(const void* A, const void* W, void* C, int a_dtype, i
   if (skinny_applies(A, W, a_dtype, c_dtype, M, K, lda, ldw)) {
     const float* a = (const float*)A;
     const float* w = (const float*)W;
-    int status = LS_E_SIZE;
-    if (epilogue == 0) status = launch_skinny<0>(a, w, (float*)C, M, N, K, lda, ldw, ldc, stream);
-    if (epilogue == 1) status = launch_skinny<1>(a, w, (float*)C, M, N, K, lda, ldw, ldc, stream);
-    if (epilogue == 2) status = launch_skinny<2>(a, w, (float*)C, M, N, K, lda, ldw, ldc, stream);
-    if (status != LS_E_SMEM) return status;              // a depth whose rows do not fit: the tile kernel
+    if (epilogue == 0) return launch_skinny<0>(a, w, (float*)C, M, N, K, lda, ldw, ldc, stream);
+    if (epilogue == 1) return launch_skinny<1>(a, w, (float*)C, M, N, K, lda, ldw, ldc, stream);
+    if (epilogue == 2) return launch_skinny<2>(a, w, (float*)C, M, N, K, lda, ldw, ldc, stream);
+    return LS_E_SIZE;
   }
   // float32 rows that can be fetched 16 bytes at a time, more than a few of them
   if (a_dtype == LS_F32 && c_dtype == LS_F32 && M > SK_MAX_M && K % 4 == 0 && lda % 4 == 0 && ldw % 4 == 0 &&
