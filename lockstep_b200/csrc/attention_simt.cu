@@ -45,7 +45,7 @@ __device__ __forceinline__ const T* page_ptr(const T* pages, const int* table_ro
 // tile kernel: up to 16 query tokens of one request, one query head
 // --------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* __restrict__ out,
                       float* __restrict__ part_acc, float* __restrict__ part_ml,
                       const int* __restrict__ work, const int* __restrict__ block_table,

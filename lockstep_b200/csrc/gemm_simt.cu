@@ -104,9 +104,10 @@ gemm_nt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restric
 // for before the wait on the kernel before.
 // ---------------------------------------------------------------------------
 constexpr int SK_BN = 16;        // features per block
-constexpr int SK_BK = 64;        // depth of a stage
+constexpr int SK_BK = 128;       // depth of a stage
 constexpr int SK_PITCH = SK_BK + 4;
-constexpr int SK_STAGES = 4;
+constexpr int SK_STAGES = 6;     // five stages on their way while one is multiplied: a block of 16 rows has
+                                 // 40 KB of weights in flight, and the blocks of a narrow weight are few
 constexpr int SK_MAX_M = 32;
 
 __device__ __forceinline__ void cp_async_16(float* dst, const float* src) {

@@ -167,7 +167,8 @@ def kernel_counts() -> dict[str, int]:
     """How often each kernel's launcher has launched in this process (a launch recorded into
     a graph counts once, its replays do not), over the libraries that are loaded."""
     out: dict[str, int] = {}
-    for name, lib in _libs.items():
+    library("core")
+    for name, lib in list(_libs.items()):
         names_fn = getattr(lib, f"ls_kernel_names_{name}")
         names_fn.restype, names_fn.argtypes = ctypes.c_char_p, []
         names = names_fn().decode("ascii").split(",")
