@@ -67,7 +67,7 @@ CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16
 REPEATS = 5
-SETTLE = 24            # untimed decode steps between the prompts' step and the warm-up of the entry-point run
+SETTLE = 24            # untimed decode steps before the warm-up steps of every timed decode region
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 FP32_TFLOPS_NOMINAL = 80.0        # FFMA peak of the CUDA cores: the 32-bit path's compute roof
 
@@ -159,6 +159,10 @@ def time_decode(runner, sampler, batch, end_context, steps, warmup, repeats=REPE
     from lockstep_b200 import kernels as K
     from lockstep_b200.sampling import SamplingParams
 
+    # (the device runs its first dozen steps after other work some 10 % slower: `settle` more
+    # untimed steps come before the warm-up steps)
+    settle = SETTLE if end_context - steps - warmup - SETTLE >= 64 else 0
+    warmup = warmup + settle
     start_len = end_context - steps - warmup
     if start_len < 1:
         raise ValueError("more steps than the context holds")
@@ -362,10 +366,10 @@ def run_ours(args):
         point_spread[f"decode_b{b}"] = spread(ms)
     if not args.quick:
         for b in batches:
-            ms = time_decode(runner, engine.sampler, b, 768, 256 - args.warmup, args.warmup, repeats=3)
+            ms = time_decode(runner, engine.sampler, b, 768, 256 - args.warmup - SETTLE, args.warmup, repeats=3)
             med = statistics.median(ms)
             points[f"decode_b{b}_prompt512_gen256"] = round(b / med * 1e3, 1)
-            point_frac[f"decode_b{b}_prompt512_gen256"] = round(frac_of_hbm(b, 640, med), 4)
+            point_frac[f"decode_b{b}_prompt512_gen256"] = round(frac_of_hbm(b, 768 - (256 - args.warmup - SETTLE) / 2, med), 4)
 
     clocks = ClockSampler()
     clocks.start()
