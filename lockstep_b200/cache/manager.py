@@ -58,14 +58,18 @@ class PagedGroup:
         self.page_size, self.window = int(page_size), int(need.window)
         self.allocator = PageAllocator(num_pages)
         self.max_pages_per_seq = int(max_pages_per_seq)
-        self.table_host = np.full((max_live, self.max_pages_per_seq), -1, dtype=np.int32)
+        # One row and one page more than requests can hold: the padding row (index max_live) maps
+        # every position to the padding page (index num_pages, outside the allocator's range).
+        # Rows that pad a recorded decode step to its batch size write their keys there.
+        self.table_host = np.full((max_live + 1, self.max_pages_per_seq), -1, dtype=np.int32)
+        self.table_host[max_live, :] = num_pages
         self.device = device
         self.table = None
         self.pages = None
         if allocate:
-            self.table = torch.full((max_live, self.max_pages_per_seq), -1, dtype=torch.int32, device=device)
+            self.table = torch.from_numpy(self.table_host).to(device)
             self.pages = torch.zeros(
-                (len(self.entries), num_pages, 2, need.kv_heads, self.page_size, need.head_dim),
+                (len(self.entries), num_pages + 1, 2, need.kv_heads, self.page_size, need.head_dim),
                 dtype=dtype, device=device)
         self.seqs: dict[str, _Seq] = {}
         self._dirty: set[int] = set()
@@ -213,7 +217,8 @@ class StateGroup:
         self.need, self.entries = need, list(entries)
         self.state = None
         if allocate:
-            self.state = torch.zeros((len(self.entries), max_live, *need.state_shape),
+            # (one slot more than requests can hold: the padding rows of a recorded step)
+            self.state = torch.zeros((len(self.entries), max_live + 1, *need.state_shape),
                                      dtype=need.state_dtype, device=device)
 
     def clear(self, slot: int) -> None:
@@ -261,6 +266,7 @@ class CacheManager:
                 raise ValueError(f"unknown cache need {need.kind!r}")
             for i, entry in enumerate(entries):
                 self._entry[entry] = (group, i)
+        self.pad_slot = self.max_live          # the row of padding rows in every block table and state tensor
         self._free_slots = list(range(self.max_live - 1, -1, -1))
         self.slots: dict[str, int] = {}
         self.lengths: dict[str, int] = {}

@@ -3,10 +3,14 @@
 A step whose entries all bring one token launches a few hundred small kernels;
 recorded once and replayed, the host's share of the step shrinks to filling one
 pinned buffer.  A graph is keyed by (number of requests, capacity of the
-attention work list); the capacity is rounded up to a multiple of
-max(CAPACITY_STEP, 4 x requests), so that a batch records a new graph about every
-1,024 decoded tokens whatever its size, and at most MAX_GRAPHS graphs are kept
-(the least recently replayed one is dropped first).  A graph holds its input
+attention work list).  More than eight requests are padded to the next multiple of
+eight with rows that bring token 0 at position 0 of the cache manager's padding slot
+(their keys go to the padding page, their attention work is empty, their logits are
+dropped), so that a batch that shrinks as requests end does not record a graph per
+size.  The capacity is rounded up to a multiple of max(CAPACITY_STEP, 4 x rows), so
+that a batch records a new graph about every 1,024 decoded tokens whatever its size,
+and at most MAX_GRAPHS graphs are kept (the least recently replayed one is dropped
+first).  A graph holds its input
 buffer (a few KB), its activations (a few hundred KB a request) and its logits
 [requests, vocabulary] in float32, all from one memory pool shared by the graphs.  Everything that changes from step to step (token ids,
 positions, slots, wanted rows, the attention work lists) lives in one device
@@ -29,13 +33,21 @@ from .batch import AttentionPlan, plan_attention
 
 CAPACITY_STEP = 32      # the attention work list of a recorded step holds a multiple of this many items
 MAX_GRAPHS = 24         # recorded steps kept; the least recently used one goes first
+EXACT_BATCHES = 8       # up to here a step is recorded at its own size, above at the next multiple of this
+
+
+def padded_batch(n: int) -> int:
+    """Rows of the recorded step that serves ``n`` requests."""
+    return n if n <= EXACT_BATCHES else -(-n // EXACT_BATCHES) * EXACT_BATCHES
 
 
 class StaticStepContext:
     """What parts see of a recorded decode step: views into the graph's buffer."""
 
-    def __init__(self, batch: int, capacity: int, windows: list[int], device, err, split_size: int):
+    def __init__(self, batch: int, capacity: int, windows: list[int], device, err, split_size: int,
+                 pad_slot: int = 0):
         self.batch, self.capacity, self.windows = batch, capacity, list(windows)
+        self.pad_slot = pad_slot
         self.device, self.err, self.split_size = device, err, split_size
         self.num_tokens = self.n_wanted = batch
         per_window = capacity * 8 + batch * 4
@@ -76,11 +88,15 @@ class StaticStepContext:
         if self._pending:
             self.copied.synchronize()      # the last copy has read the pinned buffer
         b, h = self.batch, self.host_np
+        n = len(entries)                   # the rows n .. b - 1 pad the step: token 0 at position 0 of the padding slot
         self.entries, self.slots = entries, slots
-        start = np.fromiter((e.start for e in entries), dtype=np.int64, count=b)
-        slot = np.asarray(slots, dtype=np.int64)
-        self.portions = list(zip(slots, range(b), start.tolist(), [1] * b))
-        h[0:b] = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=b)
+        start = np.zeros(b, dtype=np.int64)
+        start[:n] = np.fromiter((e.start for e in entries), dtype=np.int64, count=n)
+        slot = np.full(b, self.pad_slot, dtype=np.int64)
+        slot[:n] = np.asarray(slots, dtype=np.int64)
+        self.portions = list(zip(slots, range(n), start[:n].tolist(), [1] * n))
+        h[0:b] = 0
+        h[0:n] = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=n)
         h[b:2 * b] = start
         h[2 * b:3 * b] = slot
         h[3 * b:4 * b] = self._arange
@@ -89,6 +105,7 @@ class StaticStepContext:
             lo = np.maximum(0, start - w + 1) if w else np.zeros(b, dtype=np.int64)
             first, last = lo // self.split_size, start // self.split_size
             count = last - first + 1
+            count[n:] = 0                  # padding rows attend to nothing: no items, an empty combine
             total = int(count.sum())
             if total > self.capacity:
                 raise ValueError("the attention work list outgrew the capacity this graph was recorded for")
@@ -139,8 +156,12 @@ class DecodeGraphs:
 
     def capacity_for(self, entries) -> int:
         n = split_items(entries, self.windows, self.runner.split_size)
-        step = max(self.round_to, 4 * len(entries))
+        step = max(self.round_to, 4 * padded_batch(len(entries)))
         return -(-n // step) * step
+
+    def key_for(self, entries) -> tuple[int, int]:
+        """(rows, capacity) of the recorded step that serves ``entries``."""
+        return padded_batch(len(entries)), self.capacity_for(entries)
 
     def ready(self, key) -> bool:
         return key in self.graphs
@@ -149,7 +170,8 @@ class DecodeGraphs:
         """Record the model's forward for ``key`` (nothing runs while recording)."""
         r = self.runner
         batch, capacity = key
-        ctx = StaticStepContext(batch, capacity, self.windows, r.device, r.err, r.split_size)
+        ctx = StaticStepContext(batch, capacity, self.windows, r.device, r.err, r.split_size,
+                                pad_slot=r.cache.pad_slot)
         if self.pool is None:
             self.pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
@@ -186,8 +208,8 @@ class DecodeGraphs:
         self.graphs.move_to_end(key)
         ctx.fill(entries, slots)
         if tokens_device is not None:
-            ctx.token_ids.copy_(tokens_device, non_blocking=True)
+            ctx.token_ids[:len(entries)].copy_(tokens_device, non_blocking=True)
         graph.replay()
         K.LAUNCHES[0] += recorded
         self.replays += 1
-        return logits
+        return logits[:len(entries)]

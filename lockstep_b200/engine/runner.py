@@ -117,7 +117,7 @@ class ModelRunner:
         device: the step is a recorded one."""
         if self.graphs is None or not all(len(e.tokens) == 1 and e.want == [0] for e in entries):
             return False
-        return self.graphs.ready((len(entries), self.graphs.capacity_for(entries)))
+        return self.graphs.ready(self.graphs.key_for(entries))
 
     @torch.no_grad()
     def step(self, entries: list[StepEntry], check: bool = True, static_logits: bool = False,
@@ -161,7 +161,7 @@ class ModelRunner:
         slots = [self.cache.slots[e.uid] for e in entries]
         logits = None
         if self.graphs is not None and all(len(e.tokens) == 1 and e.want == [0] for e in entries):
-            key = (len(entries), self.graphs.capacity_for(entries))
+            key = self.graphs.key_for(entries)
             if self.graphs.ready(key):
                 logits = self.graphs.replay(key, entries, slots, tokens_device)
                 if not static_logits:
