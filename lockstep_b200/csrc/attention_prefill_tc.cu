@@ -109,12 +109,26 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// One work item of a block: up to 128 tokens of a request (rows of the MMA tile) and one query head.
+struct Item {
+  const int* table_row;
+  int tok0, ntok, pos0, h, kvh;
+  int pos_last, key_lo, tile_first, n_tiles;
+};
+
 // HALVES = d / 64.  Shared memory: Q [HALVES][128 rows][128 B]; two stages of K and of V
 // [HALVES][128 keys][128 B]; barriers.  Tensor memory: two S buffers, O, two P buffers (bfloat16).
+//
+// The kernel is persistent: a block per SM walks the items (work item x head, longest context
+// first) in rounds, round r handing item r * blocks + b to block b, and every other round in the
+// reverse order, so that a block with a long item gets a short one next.  Barriers, stages and
+// buffers count on over the items of a block (tile counter `gt`), the producers run ahead into
+// the next item's Q and first tiles while the softmax of the last tile still runs, and the
+// tensor memory is allocated once: an item after the first does not pay a block's start again.
 template <int HALVES>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
-                            __nv_bfloat16* __restrict__ out, const int* __restrict__ work,
+                            __nv_bfloat16* __restrict__ out, const int* __restrict__ work, int n_work,
                             const int* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size,
                             int num_pages, int window, float scale_log2, int* err) {
   ls_dependency_trigger();
@@ -132,54 +146,67 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t bars_smem = v_smem + STAGES * KV_BYTES;
   uint8_t* v_ptr = aligned + (v_smem - base);
   uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (bars_smem - base));
-  uint64_t* q_full = bars;             // Q landed
+  uint64_t* q_full = bars;             // Q of an item landed
   uint64_t* k_full = bars + 1;         // [2] keys of a tile landed
   uint64_t* v_full = bars + 3;         // [2] values landed
   uint64_t* k_free = bars + 5;         // [2] S = Q K^T has read the stage
   uint64_t* v_free = bars + 7;         // [2] PV has read the stage
   uint64_t* s_full = bars + 9;         // [2] S of a tile is in tensor memory
-  uint64_t* s_free = bars + 11;        // [2] the softmax warps have read it (8 arrivals)
-  uint64_t* p_full = bars + 16;        // [2] P of a tile is in tensor memory (8 arrivals)
+  uint64_t* s_free = bars + 11;        // [2] the softmax warps have read it
+  uint64_t* q_free = bars + 13;        // the item's last S product has read Q
   uint64_t* o_full = bars + 14;        // [2] PV of a tile has been added to O (and its P may be overwritten)
+  uint64_t* p_full = bars + 16;        // [2] P of a tile is in tensor memory
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile uint32_t* failed = tmem_slot + 1;
-  float* row_max = reinterpret_cast<float*>(bars + 32);   // [2 tiles][GROUPS][128 rows], then reused for l
+  float* row_max = reinterpret_cast<float*>(bars + 32);   // [2 tiles][GROUPS][128 rows], then [GROUPS][128] for l
 
-  // blocks are handed out head-fastest, so the tiles with the longest context (listed
-  // first) start first for every head and the short ones fill the tail
-  const int* w = work + (int64_t)blockIdx.y * 8;
-  const int req_row = w[0], tok0 = w[1], ntok = w[2], pos0 = w[3];
-  if (ntok == 0) return;
-  const int h = blockIdx.x;
-  const int kvh = h / (nq / nkv);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int* table_row = block_table + (int64_t)req_row * table_stride;
+  const int total_items = n_work * nq;
+  const int blocks = (int)gridDim.x;
 
-  const int pos_last = pos0 + ntok - 1;
-  const int key_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;   // first key any row reads
-  const int tile_first = key_lo / BLOCK_N;
-  const int tile_end = pos_last / BLOCK_N + 1;
-  const int n_tiles = tile_end - tile_first;
+  // the item of this block in round `round`: 0 none is left, 1 an item, 2 a padding item (nothing to do)
+  auto get_item = [&](int round, Item& I) -> int {
+    const int idx = round * blocks + ((round & 1) ? blocks - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    if (idx >= total_items) return 0;
+    const int wi = idx / nq;
+    I.h = idx - wi * nq;
+    const int* w = work + (int64_t)wi * 8;
+    I.tok0 = w[1];
+    I.ntok = w[2];
+    I.pos0 = w[3];
+    if (I.ntok == 0) return 2;
+    I.table_row = block_table + (int64_t)w[0] * table_stride;
+    I.kvh = I.h / (nq / nkv);
+    I.pos_last = I.pos0 + I.ntok - 1;
+    I.key_lo = (window > 0 && I.pos0 - window + 1 > 0) ? I.pos0 - window + 1 : 0;   // first key any row reads
+    I.tile_first = I.key_lo / BLOCK_N;
+    I.n_tiles = I.pos_last / BLOCK_N + 1 - I.tile_first;
+    return 1;
+  };
 
   const int rows_per_box = page_size < BLOCK_N ? page_size : BLOCK_N;
   const int boxes = BLOCK_N / rows_per_box;              // at most 16: lane b fetches box b of a tile
-  // the page of this lane's box of tile `it`, looked up one tile ahead (not yet checked)
-  auto lookup = [&](int it) {
+  // the page of this lane's box of tile `it` of an item, looked up one tile ahead (not yet checked)
+  auto lookup = [&](const Item& I, int it) {
     int page = 0;
-    if (it < n_tiles && lane < boxes) {
-      int key = (tile_first + it) * BLOCK_N + lane * rows_per_box;
-      if (key > pos_last) key = pos_last;                // past the last key: any page that exists
-      if (key < key_lo) key = key_lo;                    // behind the window: pages may have been given back
-      page = table_row[key / page_size];               // checked where it is used: the load stays in flight
+    if (it < I.n_tiles && lane < boxes) {
+      int key = (I.tile_first + it) * BLOCK_N + lane * rows_per_box;
+      if (key > I.pos_last) key = I.pos_last;            // past the last key: any page that exists
+      if (key < I.key_lo) key = I.key_lo;                // behind the window: pages may have been given back
+      page = I.table_row[key / page_size];               // checked where it is used: the load stays in flight
     }
     return page;
   };
-  // the block table is the step's input, older than the kernel before this one; the look-up's trip
-  // to memory runs under the set-up below
-  int page = (warp == 0 || warp == V_WARP) ? lookup(0) : 0;
+  // the work list and the block table are the step's inputs, older than the kernel before this
+  // one: the first item's first look-up runs under the set-up below
+  Item first_item;
+  int first_page = 0;
+  const bool producer = warp == 0 || warp == V_WARP;
+  if (producer && get_item(0, first_item) == 1) first_page = lookup(first_item, 0);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_free, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&v_full[s], 1);
@@ -208,45 +235,63 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t tmem_base = *tmem_slot;
   ls_dependency_wait();                 // q and this step's keys and values come from the kernel before
 
-  if (warp == 0 || warp == V_WARP) {
-    // ---- producers ----
-    if (warp == 0 && lane == 0) {
-      mbar_expect_tx(q_full, KV_BYTES);
-#pragma unroll
-      for (int hh = 0; hh < HALVES; ++hh) tma_load_2d(q_smem + hh * HALF_BYTES, &map_q, h * D + hh * 64, tok0, q_full);
-    }
-    // warp 0 fetches the key tiles, warp 10 the value tiles: a key stage is free two tiles
-    // before the value stage of the same tile, and neither waits for the other's
+  if (producer) {
+    // ---- producers: warp 0 fetches Q and the key tiles, warp V_WARP the value tiles: a key stage
+    // is free two tiles before the value stage of the same tile, and neither waits for the other's ----
     const bool keys = warp == 0;
     uint64_t* free_bar = keys ? k_free : v_free;
     uint64_t* full_bar = keys ? k_full : v_full;
     const uint32_t dst_base = keys ? k_smem : v_smem;
-    for (int it = 0; it < n_tiles; ++it) {
-      const int s = it & 1;
-      const uint32_t phase = (uint32_t)(it >> 1) & 1u;
-      const int c0 = (tile_first + it) * BLOCK_N;
-      bool ok = *failed == 0 && mbar_wait(&free_bar[s], phase ^ 1u);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) {
-        *failed = 1;
-        if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 800 + s);
-        break;
-      }
-      if (lane == 0) mbar_expect_tx(&full_bar[s], KV_BYTES);
-      __syncwarp();
-      if (lane < boxes) {
-        if (page < 0 || page >= num_pages) {
-          ls_record_fault(err, LS_DEV_PAGE_RANGE, c0 + lane * rows_per_box);
-          page = 0;
-        }
-        const int in_page = ((c0 + lane * rows_per_box) % page_size) / rows_per_box * rows_per_box;
-        const int y = ((page * 2 + (keys ? 0 : 1)) * nkv + kvh) * page_size + in_page;
+    int gt = 0, j = 0;                  // tiles and items of this block so far
+    bool ok = true;
+    for (int round = 0; ok; ++round) {
+      Item I;
+      const int kind = get_item(round, I);
+      if (kind == 0) break;
+      if (kind == 2) continue;
+      int page = round == 0 ? first_page : lookup(I, 0);
+      if (keys && lane == 0) {
+        // Q is free once the last S product of the item before has read it
+        if (j > 0 && (*failed || !mbar_wait(q_free, (uint32_t)(j - 1) & 1u))) {
+          *failed = 1;
+          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 810);
+        } else {
+          mbar_expect_tx(q_full, KV_BYTES);
 #pragma unroll
-        for (int hh = 0; hh < HALVES; ++hh)
-          tma_load_2d(dst_base + (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + lane * rows_per_box * 128), &map_kv,
-                      hh * 64, y, &full_bar[s]);
+          for (int hh = 0; hh < HALVES; ++hh)
+            tma_load_2d(q_smem + hh * HALF_BYTES, &map_q, I.h * D + hh * 64, I.tok0, q_full);
+        }
       }
-      page = lookup(it + 1);            // after this tile's loads have gone out
+      for (int it = 0; it < I.n_tiles; ++it) {
+        const int g = gt + it;
+        const int s = g & 1;
+        const uint32_t phase = (uint32_t)(g >> 1) & 1u;
+        const int c0 = (I.tile_first + it) * BLOCK_N;
+        ok = *failed == 0 && mbar_wait(&free_bar[s], phase ^ 1u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          *failed = 1;
+          if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 800 + s);
+          break;
+        }
+        if (lane == 0) mbar_expect_tx(&full_bar[s], KV_BYTES);
+        __syncwarp();
+        if (lane < boxes) {
+          if (page < 0 || page >= num_pages) {
+            ls_record_fault(err, LS_DEV_PAGE_RANGE, c0 + lane * rows_per_box);
+            page = 0;
+          }
+          const int in_page = ((c0 + lane * rows_per_box) % page_size) / rows_per_box * rows_per_box;
+          const int y = ((page * 2 + (keys ? 0 : 1)) * nkv + I.kvh) * page_size + in_page;
+#pragma unroll
+          for (int hh = 0; hh < HALVES; ++hh)
+            tma_load_2d(dst_base + (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + lane * rows_per_box * 128), &map_kv,
+                        hh * 64, y, &full_bar[s]);
+        }
+        page = lookup(I, it + 1);       // after this tile's loads have gone out
+      }
+      gt += I.n_tiles;
+      ++j;
     }
   } else if (warp == 1) {
     // ---- MMA issue: the whole warp walks the loop and one elected lane issues, so that the
@@ -255,48 +300,61 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr uint32_t idesc_s = instr_desc(BLOCK_M, BLOCK_N, false);
     constexpr uint32_t idesc_o = instr_desc(BLOCK_M, D, true);
     const bool issuer = elect_one();
-    bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0));
-    auto issue_s = [&](int it) {       // S(it) = Q K(it)^T into S buffer it & 1
-      const int s = it & 1;
-      const uint32_t phase = (uint32_t)(it >> 1) & 1u;
-      bool got = mbar_wait(&k_full[s], phase);
-      if (it >= 2) got = got && mbar_wait(&s_free[s], (uint32_t)((it >> 1) - 1) & 1u);
-      if (!__all_sync(0xffffffffu, got)) return false;
-      fence_after_sync();
-      if (issuer) {
+    int gt = 0, j = 0;
+    bool ok = true;
+    for (int round = 0; ok; ++round) {
+      Item I;
+      const int kind = get_item(round, I);
+      if (kind == 0) break;
+      if (kind == 2) continue;
+      ok = __all_sync(0xffffffffu, mbar_wait(q_full, (uint32_t)j & 1u));
+      auto issue_s = [&](int it) {       // S(it) = Q K(it)^T into the S buffer in turn
+        const int g = gt + it;
+        const int s = g & 1;
+        const uint32_t phase = (uint32_t)(g >> 1) & 1u;
+        bool got = mbar_wait(&k_full[s], phase);
+        if (g >= 2) got = got && mbar_wait(&s_free[s], (uint32_t)((g >> 1) - 1) & 1u);
+        if (!__all_sync(0xffffffffu, got)) return false;
+        fence_after_sync();
+        if (issuer) {
 #pragma unroll
-        for (int k = 0; k < D / UMMA_K; ++k) {
-          const uint32_t koff = (uint32_t)((k >> 2) * HALF_BYTES + (k & 3) * UMMA_K * 2);
-          umma(tmem_base + S_COL + s * BLOCK_N, desc_k_major(q_smem + koff),
-               desc_k_major(k_smem + s * KV_BYTES + koff), idesc_s, k != 0 ? 1u : 0u);
+          for (int k = 0; k < D / UMMA_K; ++k) {
+            const uint32_t koff = (uint32_t)((k >> 2) * HALF_BYTES + (k & 3) * UMMA_K * 2);
+            umma(tmem_base + S_COL + s * BLOCK_N, desc_k_major(q_smem + koff),
+                 desc_k_major(k_smem + s * KV_BYTES + koff), idesc_s, k != 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[s]);
+          umma_commit(&k_free[s]);
+          if (it == I.n_tiles - 1) umma_commit(q_free);     // the item's last product with this Q
         }
-        umma_commit(&s_full[s]);
-        umma_commit(&k_free[s]);
-      }
-      __syncwarp();
-      return true;
-    };
-    if (ok) ok = issue_s(0);
-    for (int it = 0; it < n_tiles && ok; ++it) {
-      const int s = it & 1;
-      const uint32_t phase = (uint32_t)(it >> 1) & 1u;
-      if (it + 1 < n_tiles) ok = issue_s(it + 1);
-      if (!ok) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(&p_full[s], phase) && mbar_wait(&v_full[s], phase));
-      if (!ok) break;
-      fence_after_sync();
-      if (issuer) {
+        __syncwarp();
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int it = 0; it < I.n_tiles && ok; ++it) {
+        const int g = gt + it;
+        const int s = g & 1;
+        const uint32_t phase = (uint32_t)(g >> 1) & 1u;
+        if (it + 1 < I.n_tiles) ok = issue_s(it + 1);
+        if (!ok) break;
+        ok = __all_sync(0xffffffffu, mbar_wait(&p_full[s], phase) && mbar_wait(&v_full[s], phase));
+        if (!ok) break;
+        fence_after_sync();
+        if (issuer) {
 #pragma unroll
-        for (int k = 0; k < BLOCK_N / UMMA_K; ++k) {
-          // P from tensor memory: 16 keys are 8 columns; V: 16 keys are 16 rows of 128 bytes
-          const uint64_t b = desc_mn_major(v_smem + s * KV_BYTES + k * UMMA_K * 128, HALF_BYTES);
-          umma_ts(tmem_base + O_COL, tmem_base + P_COL + s * P_COLS + k * (UMMA_K / 2), b, idesc_o,
-                  (it | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < BLOCK_N / UMMA_K; ++k) {
+            // P from tensor memory: 16 keys are 8 columns; V: 16 keys are 16 rows of 128 bytes
+            const uint64_t b = desc_mn_major(v_smem + s * KV_BYTES + k * UMMA_K * 128, HALF_BYTES);
+            umma_ts(tmem_base + O_COL, tmem_base + P_COL + s * P_COLS + k * (UMMA_K / 2), b, idesc_o,
+                    (it | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&o_full[s]);
+          umma_commit(&v_free[s]);
         }
-        umma_commit(&o_full[s]);
-        umma_commit(&v_free[s]);
+        __syncwarp();
       }
-      __syncwarp();
+      gt += I.n_tiles;
+      ++j;
     }
     if (!ok) {
       *failed = 1;
@@ -313,150 +371,167 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int group = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const int pos = pos0 + row;
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
     // O = sum of P V stays in tensor memory, the MMAs of every tile adding to it, in units of
     // 2^m_ref of its row.  m_ref follows the row's maximum lazily: only when the maximum has
     // grown by more than 8 (a factor 256, which bfloat16 P and float32 sums take easily) is the
     // row of O scaled down and m_ref moved, which after the first tiles hardly ever happens.
     // The quotient O / l does not depend on m_ref.
     constexpr float LAZY = 8.f;
-    float m_ref = -CUDART_INF_F, l_run = 0.f;
     bool ok = true;
+    int gt = 0;
 
-    // A wait that runs out clears `ok`; the loop still runs to its end, skipping the work, so
-    // that every thread meets the named barrier of every tile.
-    for (int it = 0; it < n_tiles; ++it) {
-      const int s = it & 1;
-      const int c0 = (tile_first + it) * BLOCK_N + group * HC;     // first key of this thread
-      if (ok && !mbar_wait(&s_full[s], (uint32_t)(it >> 1) & 1u)) ok = false;
-      fence_after_sync();
-      // this thread's 64 scores into registers; the buffer is free once all have theirs
-      uint32_t g[HC];
+    // A wait that runs out clears `ok`; the loops still run to their ends, skipping the work, so
+    // that every thread meets the named barrier of every tile of every item.
+    for (int round = 0;; ++round) {
+      Item I;
+      const int kind = get_item(round, I);
+      if (kind == 0) break;
+      if (kind == 2) continue;
+      const int pos0 = I.pos0, pos_last = I.pos_last, tile_first = I.tile_first, n_tiles = I.n_tiles;
+      const int pos = pos0 + row;
+      const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+      const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
+      float m_ref = -CUDART_INF_F, l_run = 0.f;
+      for (int it = 0; it < n_tiles; ++it) {
+        const int g = gt + it;
+        const int s = g & 1;
+        const int c0 = (tile_first + it) * BLOCK_N + group * HC;     // first key of this thread
+        if (ok && !mbar_wait(&s_full[s], (uint32_t)(g >> 1) & 1u)) ok = false;
+        fence_after_sync();
+        // this thread's scores into registers; the buffer is free once all have theirs
+        uint32_t sc[HC];
 #pragma unroll
-      for (int q0 = 0; q0 < HC; q0 += 32) tmem_ld32(lane_base + S_COL + s * BLOCK_N + group * HC + q0, g + q0);
-      tmem_ld_wait();
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[s]);
-      // every key of the tile is seen by every row: no masks (uniform over the block)
-      const bool full_tile = (tile_first + it) * BLOCK_N + BLOCK_N - 1 <= pos0 && (tile_first + it) * BLOCK_N >= lo_last;
-      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-      if (full_tile) {
+        for (int q0 = 0; q0 < HC; q0 += 32) tmem_ld32(lane_base + S_COL + s * BLOCK_N + group * HC + q0, sc + q0);
+        tmem_ld_wait();
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[s]);
+        // every key of the tile is seen by every row: no masks (uniform over the block)
+        const bool full_tile = (tile_first + it) * BLOCK_N + BLOCK_N - 1 <= pos0 && (tile_first + it) * BLOCK_N >= lo_last;
+        float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+        if (full_tile) {
 #pragma unroll
-        for (int j = 0; j < HC; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(g[j]));
-      } else {
-        // selects, not branches: a masked score counts as -inf
+          for (int jj = 0; jj < HC; ++jj) mx[jj & 3] = fmaxf(mx[jj & 3], __uint_as_float(sc[jj]));
+        } else {
+          // selects, not branches: a masked score counts as -inf
 #pragma unroll
-        for (int j = 0; j < HC; ++j) {
-          const bool keep = (c0 + j <= pos) & (c0 + j >= lo);
-          mx[j & 3] = fmaxf(mx[j & 3], keep ? __uint_as_float(g[j]) : -CUDART_INF_F);
-        }
-      }
-      // the row's maximum is that of its two threads
-      float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      row_max[(it & 1) * ROWS + group * 128 + row] = tile_max;
-      asm volatile("bar.sync 1, %0;" ::"n"(ROWS) : "memory");
-#pragma unroll
-      for (int o = 0; o < GROUPS; ++o) tile_max = fmaxf(tile_max, row_max[(it & 1) * ROWS + o * 128 + row]);
-      // both threads of a row work out the same m_ref from the same numbers
-      const float m_new = tile_max * scale_log2;
-      const bool move = m_new > m_ref + LAZY;                      // true too for the first key a row sees
-      const float factor = move ? ((m_ref == -CUDART_INF_F) ? 0.f : ex2(m_ref - m_new)) : 1.f;
-      if (move) m_ref = m_new;
-      // this tile's P buffer was read by the PV of two tiles ago (long done); O is scaled only
-      // after the PV of the tile before has been added to it
-      if (ok && it > 1 && !mbar_wait(&o_full[s], (uint32_t)((it - 2) >> 1) & 1u)) ok = false;
-      if (it > 0 && __any_sync(0xffffffffu, move)) {
-        if (ok && !mbar_wait(&o_full[(it - 1) & 1], (uint32_t)((it - 1) >> 1) & 1u)) ok = false;
-        if (__all_sync(0xffffffffu, ok)) {
-          fence_after_sync();
-          uint32_t og[HD];
-          tmem_ld_cols<HD>(lane_base + O_COL + group * HD, og);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < HD; ++c) og[c] = __float_as_uint(__uint_as_float(og[c]) * factor);
-          tmem_st_cols<HD>(lane_base + O_COL + group * HD, og);
-        }
-      }
-      // p = exp2(s * scale - m_ref), rounded to bfloat16, two keys a column, into this thread's 32
-      // columns of the tile's P buffer in tensor memory (keys 64 * group ..), from where the PV
-      // product takes it as its A operand; the sum in four running sums, folded in a fixed order
-      float ps[4] = {0.f, 0.f, 0.f, 0.f};
-      const bool dead = m_ref == -CUDART_INF_F;          // nothing seen yet by this row
-      const float neg_m = dead ? 0.f : -m_ref;
-      uint32_t pk[HC / 2];
-      {
-        const bool plain = full_tile & !dead;             // uniform over the block but for `dead`
-#pragma unroll
-        for (int n0 = 0; n0 < HC; n0 += 8) {
-          float p[8];
-          if (plain) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) p[j] = ex2(fmaf(__uint_as_float(g[n0 + j]), scale_log2, neg_m));
-          } else {
-            // every exponential is taken, masked ones of -inf (which is 0): selects, not branches
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int key = c0 + n0 + j;
-              const bool keep = (key <= pos) & (key >= lo) & !dead;
-              p[j] = ex2(keep ? fmaf(__uint_as_float(g[n0 + j]), scale_log2, neg_m) : -CUDART_INF_F);
-            }
+          for (int jj = 0; jj < HC; ++jj) {
+            const bool keep = (c0 + jj <= pos) & (c0 + jj >= lo);
+            mx[jj & 3] = fmaxf(mx[jj & 3], keep ? __uint_as_float(sc[jj]) : -CUDART_INF_F);
           }
+        }
+        // the row's maximum is that of its threads
+        float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        row_max[(it & 1) * ROWS + group * 128 + row] = tile_max;
+        asm volatile("bar.sync 1, %0;" ::"n"(ROWS) : "memory");
 #pragma unroll
-          for (int j = 0; j < 8; ++j) ps[j & 3] += p[j];
+        for (int o = 0; o < GROUPS; ++o) tile_max = fmaxf(tile_max, row_max[(it & 1) * ROWS + o * 128 + row]);
+        // all threads of a row work out the same m_ref from the same numbers
+        const float m_new = tile_max * scale_log2;
+        const bool move = m_new > m_ref + LAZY;                      // true too for the first key a row sees
+        const float factor = move ? ((m_ref == -CUDART_INF_F) ? 0.f : ex2(m_ref - m_new)) : 1.f;
+        if (move) m_ref = m_new;
+        // this tile's P buffer was read by the PV of two tiles ago (long done); O is scaled only
+        // after the PV of the tile before has been added to it
+        if (ok && g > 1 && !mbar_wait(&o_full[s], (uint32_t)((g - 2) >> 1) & 1u)) ok = false;
+        if (it > 0 && __any_sync(0xffffffffu, move)) {
+          if (ok && !mbar_wait(&o_full[(g - 1) & 1], (uint32_t)((g - 1) >> 1) & 1u)) ok = false;
+          if (__all_sync(0xffffffffu, ok)) {
+            fence_after_sync();
+            uint32_t og[HD];
+            tmem_ld_cols<HD>(lane_base + O_COL + group * HD, og);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 4; ++j) pk[(n0 >> 1) + j] = pack_bf16(p[2 * j], p[2 * j + 1]);
+            for (int c = 0; c < HD; ++c) og[c] = __float_as_uint(__uint_as_float(og[c]) * factor);
+            tmem_st_cols<HD>(lane_base + O_COL + group * HD, og);
+          }
+        }
+        // p = exp2(s * scale - m_ref), rounded to bfloat16, two keys a column, into this thread's
+        // columns of the tile's P buffer in tensor memory, from where the PV product takes it as
+        // its A operand; the sum in four running sums, folded in a fixed order
+        float ps[4] = {0.f, 0.f, 0.f, 0.f};
+        const bool dead = m_ref == -CUDART_INF_F;          // nothing seen yet by this row
+        const float neg_m = dead ? 0.f : -m_ref;
+        uint32_t pk[HC / 2];
+        {
+          const bool plain = full_tile & !dead;             // uniform over the block but for `dead`
+#pragma unroll
+          for (int n0 = 0; n0 < HC; n0 += 8) {
+            float p[8];
+            if (plain) {
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) p[jj] = ex2(fmaf(__uint_as_float(sc[n0 + jj]), scale_log2, neg_m));
+            } else {
+              // every exponential is taken, masked ones of -inf (which is 0): selects, not branches
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) {
+                const int key = c0 + n0 + jj;
+                const bool keep = (key <= pos) & (key >= lo) & !dead;
+                p[jj] = ex2(keep ? fmaf(__uint_as_float(sc[n0 + jj]), scale_log2, neg_m) : -CUDART_INF_F);
+              }
+            }
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) ps[jj & 3] += p[jj];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) pk[(n0 >> 1) + jj] = pack_bf16(p[2 * jj], p[2 * jj + 1]);
+          }
+        }
+        tmem_st_cols<HC / 2>(lane_base + P_COL + s * P_COLS + group * (HC / 2), pk);
+        const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
+        // value rows of keys past the last position were never written: they must not be NaN,
+        // since P is zero there and the MMA multiplies all the same
+        if ((tile_first + it) * BLOCK_N + BLOCK_N - 1 > pos_last) {
+          if (ok && !mbar_wait(&v_full[s], (uint32_t)(g >> 1) & 1u)) ok = false;
+          if (ok && group < HALVES && (tile_first + it) * BLOCK_N + row > pos_last) {
+            uint4* vrow = reinterpret_cast<uint4*>(v_ptr + s * KV_BYTES + group * HALF_BYTES + row * 128);
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) vrow[q8] = make_uint4(0u, 0u, 0u, 0u);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        tmem_st_wait();
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(&p_full[s]);
+        l_run = fmaf(l_run, factor, psum);
+      }
+      // the row's sum is that of its threads (a region of its own: the next item's first tile
+      // writes its maxima while a slow thread may still read these)
+      float* l_part = row_max + 2 * ROWS;
+      l_part[group * 128 + row] = l_run;
+      asm volatile("bar.sync 1, %0;" ::"n"(ROWS) : "memory");
+      float l_row = l_part[row];                     // the same sum in the same order in each of the row's threads
+#pragma unroll
+      for (int o = 1; o < GROUPS; ++o) l_row += l_part[o * 128 + row];
+      const int g_last = gt + n_tiles - 1;
+      if (ok && !mbar_wait(&o_full[g_last & 1], (uint32_t)(g_last >> 1) & 1u)) ok = false;
+      if (ok) {
+        fence_after_sync();
+        uint32_t og[HD];
+        tmem_ld_cols<HD>(lane_base + O_COL + group * HD, og);
+        tmem_ld_wait();
+        fence_before_sync();                         // the next item's first PV overwrites O after its P
+        if (row < I.ntok) {
+          const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+          __nv_bfloat16* dst = out + ((int64_t)(I.tok0 + row) * nq + I.h) * D + group * HD;
+#pragma unroll
+          for (int c = 0; c < HD; c += 8) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(og[c]) * inv, __uint_as_float(og[c + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(og[c + 2]) * inv, __uint_as_float(og[c + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(og[c + 4]) * inv, __uint_as_float(og[c + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(og[c + 6]) * inv, __uint_as_float(og[c + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c) = v;
+          }
         }
       }
-      tmem_st_cols<HC / 2>(lane_base + P_COL + s * P_COLS + group * (HC / 2), pk);
-      const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
-      // value rows of keys past the last position were never written: they must not be NaN,
-      // since P is zero there and the MMA multiplies all the same
-      if ((tile_first + it) * BLOCK_N + BLOCK_N - 1 > pos_last) {
-        if (ok && !mbar_wait(&v_full[s], (uint32_t)(it >> 1) & 1u)) ok = false;
-        if (ok && group < HALVES && (tile_first + it) * BLOCK_N + row > pos_last) {
-          uint4* vrow = reinterpret_cast<uint4*>(v_ptr + s * KV_BYTES + group * HALF_BYTES + row * 128);
-#pragma unroll
-          for (int q8 = 0; q8 < 8; ++q8) vrow[q8] = make_uint4(0u, 0u, 0u, 0u);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      }
-      tmem_st_wait();
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0 && ok) mbar_arrive(&p_full[s]);
-      l_run = fmaf(l_run, factor, psum);
+      // (the bar.sync of the next item's first tile, or of its sums, comes before any thread
+      // writes this region again)
+      gt += n_tiles;
     }
-    // the row's sum is that of its two threads
-    row_max[group * 128 + row] = l_run;
-    asm volatile("bar.sync 1, %0;" ::"n"(ROWS) : "memory");
-    float l_row = row_max[row];                    // the same sum in the same order in each of the row's threads
-#pragma unroll
-    for (int o = 1; o < GROUPS; ++o) l_row += row_max[o * 128 + row];
-    if (ok && n_tiles > 0 && !mbar_wait(&o_full[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) >> 1) & 1u)) ok = false;
     if (!ok) {
       *failed = 1;
       if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 840 + quad);
-    } else {
-      fence_after_sync();
-      uint32_t og[HD];
-      tmem_ld_cols<HD>(lane_base + O_COL + group * HD, og);
-      tmem_ld_wait();
-      if (row < ntok) {
-        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
-        __nv_bfloat16* dst = out + ((int64_t)(tok0 + row) * nq + h) * D + group * HD;
-#pragma unroll
-        for (int c = 0; c < HD; c += 8) {
-          uint4 v;
-          v.x = pack_bf16(__uint_as_float(og[c]) * inv, __uint_as_float(og[c + 1]) * inv);
-          v.y = pack_bf16(__uint_as_float(og[c + 2]) * inv, __uint_as_float(og[c + 3]) * inv);
-          v.z = pack_bf16(__uint_as_float(og[c + 4]) * inv, __uint_as_float(og[c + 5]) * inv);
-          v.w = pack_bf16(__uint_as_float(og[c + 6]) * inv, __uint_as_float(og[c + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + c) = v;
-        }
-      }
     }
   }
   fence_before_sync();
@@ -497,12 +572,22 @@ bool encode(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, ui
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
 template <int HALVES>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const int* work, int n_work,
            const int* block_table, int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
            float scale, int* err, cudaStream_t stream) {
   constexpr int KV_BYTES = HALVES * HALF_BYTES;
-  const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 256 + 2 * 128 * GROUPS * 4 + 1024;
+  const size_t smem = (size_t)KV_BYTES * (1 + 2 * STAGES) + 256 + 3 * 128 * GROUPS * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -510,8 +595,10 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
       return LS_E_SMEM;
     configured = true;
   }
-  dim3 grid(nq, n_work);
-  LS_COUNT(LS_K_ATTENTION_PREFILL_TC), ls_launch(attention_prefill_tc_kernel<HALVES>, grid, THREADS, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work,
+  // a block per SM (its shared memory and its 512 columns of tensor memory fill one), or fewer items
+  const long long items = (long long)n_work * nq;
+  const int blocks = items < sm_count() ? (int)items : sm_count();
+  LS_COUNT(LS_K_ATTENTION_PREFILL_TC), ls_launch(attention_prefill_tc_kernel<HALVES>, dim3(blocks), THREADS, smem, stream, map_q, map_kv, (__nv_bfloat16*)out, work, n_work,
             block_table, table_stride, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
   return ls_launch_status();
 }
