@@ -40,7 +40,10 @@ class LayerSpec:
     """One layer: a block arrangement over a mixer and a feed-forward.
 
     ``prefix`` is the tensor-name prefix of the layer's weights
-    (``model.layers.3``); each part adds its own suffixes.
+    (``model.layers.3``); each part adds its own suffixes.  ``extra`` holds whatever further
+    parts the layer's block arrangement asks for, by the name it asks under (norms after the
+    mixer or the feed-forward, a second feed-forward branch, ...): the block receives the whole
+    ``LayerSpec`` and builds them, nothing else reads them.
     """
 
     prefix: str
@@ -50,6 +53,10 @@ class LayerSpec:
     mixer_norm: PartSpec       # norm in front of the mixer
     feed_forward_norm: PartSpec
     position: PartSpec         # position encoding the mixer applies
+    extra: Mapping[str, PartSpec] = field(default_factory=dict)
+
+    def __post_init__(self):
+        object.__setattr__(self, "extra", _freeze(self.extra))
 
 
 @dataclass(frozen=True)
