@@ -317,31 +317,45 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 #pragma unroll
     for (int r = 0; r < MAX_SHARES; ++r)
       asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[r]) : "r"(base), "r"(r < shares ? r : 0));
-    for (int c = (int)blockIdx.z; c < BN; c += shares) {
-      const int t = t0 + c;
-      if (t >= T) break;
-      const uint32_t off_g = (uint32_t)((c * BM + row) * 4), off_u = (uint32_t)(((BN + c) * BM + row) * 4);
-      float vg[MAX_SHARES], vu[MAX_SHARES];
+    // FOLD columns at a time: their shares' values (and the old values of a residual) are all
+    // asked for before any is used, so that a block pays a few trips through the cluster's
+    // shared memory and not one per column
+    constexpr int FOLD = 4;
+    for (int c0 = (int)blockIdx.z; c0 < BN; c0 += FOLD * shares) {
+      float vg[FOLD][MAX_SHARES], vu[FOLD][MAX_SHARES], before[FOLD];
 #pragma unroll
-      for (int r = 0; r < MAX_SHARES; ++r) {
-        vg[r] = r < shares ? ld_cluster_f32(peer[r] + off_g) : 0.f;
-        if (EPI == 2) vu[r] = r < shares ? ld_cluster_f32(peer[r] + off_u) : 0.f;
-      }
-      float g = 0.f, u = 0.f;
+      for (int f = 0; f < FOLD; ++f) {
+        const int c = c0 + f * shares;
+        const bool live = c < BN && t0 + c < T;
+        const uint32_t off_g = (uint32_t)((c * BM + row) * 4), off_u = (uint32_t)(((BN + c) * BM + row) * 4);
 #pragma unroll
-      for (int r = 0; r < MAX_SHARES; ++r) {
-        if (r < shares) {
-          g += vg[r];
-          if (EPI == 2) u += vu[r];
+        for (int r = 0; r < MAX_SHARES; ++r) {
+          vg[f][r] = (live && r < shares) ? ld_cluster_f32(peer[r] + off_g) : 0.f;
+          if (EPI == 2) vu[f][r] = (live && r < shares) ? ld_cluster_f32(peer[r] + off_u) : 0.f;
         }
+        before[f] = 0.f;
+        if (EPI == 1 && live && n < N)
+          before[f] = c == (int)blockIdx.z ? first_old : ls_to_float<TC>(C[(int64_t)(t0 + c) * ldc + n]);
       }
-      if (n < N) {
-        if (EPI == 1) {
-          TC* cp = C + (int64_t)t * ldc + n;
-          const float before = c == (int)blockIdx.z ? first_old : ls_to_float<TC>(*cp);
-          *cp = ls_from_float<TC>(before + g);
-        } else {
-          epilogue_store<EPI, TC>(C + (int64_t)t * ldc + n, g, u);
+#pragma unroll
+      for (int f = 0; f < FOLD; ++f) {
+        const int c = c0 + f * shares;
+        if (c >= BN || t0 + c >= T) break;
+        float g = 0.f, u = 0.f;
+#pragma unroll
+        for (int r = 0; r < MAX_SHARES; ++r) {
+          if (r < shares) {
+            g += vg[f][r];
+            if (EPI == 2) u += vu[f][r];
+          }
+        }
+        if (n < N) {
+          TC* cp = C + (int64_t)(t0 + c) * ldc + n;
+          if (EPI == 1) {
+            *cp = ls_from_float<TC>(before[f] + g);
+          } else {
+            epilogue_store<EPI, TC>(cp, g, u);
+          }
         }
       }
     }
