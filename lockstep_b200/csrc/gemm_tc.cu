@@ -417,9 +417,7 @@ __device__ __forceinline__ void st_async_f32(uint32_t cluster_addr, float v, uin
 // the limit is four times that of a block's own waits: a peer that ran into its own limit
 // is given up on later than that
 __device__ __forceinline__ bool mbar_wait_long(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < 4u * WAIT_LIMIT; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
+  return mbar_wait_for(bar, parity, 4 * WAIT_CYCLES);
 }
 __device__ __forceinline__ void cluster_arrive() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");

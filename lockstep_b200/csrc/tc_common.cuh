@@ -9,7 +9,8 @@
 
 namespace {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 22;     // polls of a barrier before a wait gives up
+constexpr long long WAIT_CYCLES = 4000000000LL;   // a wait gives up after this many clocks (about two seconds)
+constexpr uint32_t WAIT_HINT_NS = 20000;          // how long one try may keep the thread suspended
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -28,26 +29,32 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One try: the thread may stay suspended until the phase completes or the hint runs out, so a
+// waiting warp does not poll in a tight loop and take issue slots from the warps that work.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(WAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }
 
-// bounded wait: false when the limit ran out
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+// bounded wait (by the clock, whatever a try takes): false when the limit ran out
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, long long cycles) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  do {
     if (mbar_try_wait(bar, parity)) return true;
+  } while (clock64() - start < cycles);
   return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_for(bar, parity, WAIT_CYCLES); }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
                                             uint64_t* bar) {
