@@ -157,6 +157,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
         float dot[4] = {0.f, 0.f, 0.f, 0.f};
         const float* qr = Qs + m * dp;
         const float* kr = Ks + sub * dp;
+#pragma unroll 4
         for (int c = 0; c < d; c += 4) {
           const float4 q4 = *reinterpret_cast<const float4*>(qr + c);
 #pragma unroll

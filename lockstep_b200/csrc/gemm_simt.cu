@@ -262,14 +262,19 @@ bool skinny_applies(const void* A, const void* W, int a_dtype, int c_dtype, int 
 // ---------------------------------------------------------------------------
 constexpr int LM = 128, LN = 128, LK = 16, LPITCH = LM + 4;
 
-template <int EPI>
+// WR: rows of W in a tile: 128, or 64 where 128 would leave SMs without a tile (a narrow weight).
+// The features of a tile are WR, or WR / 2 for silu-mul (gate rows, then the up rows of the same).
+template <int EPI, int WR>
 __global__ void __launch_bounds__(256, 2)
 gemm_nt_large_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int M, int N,
                      int K, int64_t lda, int64_t ldw, int64_t ldc) {
-  constexpr int FN = EPI == 2 ? LN / 2 : LN;          // features of the tile
+  static_assert(WR == 128 || (WR == 64 && EPI != 2), "tile widths");
+  constexpr int FN = EPI == 2 ? WR / 2 : WR;           // features of the tile
+  constexpr int HALVES = WR / 64;                      // 64-row halves of W a thread fetches and multiplies
+  constexpr int WC = 4 * HALVES;                       // columns of a thread
   ls_dependency_sync();
   __shared__ __align__(16) float As[2][LK][LPITCH];
-  __shared__ __align__(16) float Ws[2][LK][LPITCH];
+  __shared__ __align__(16) float Ws[2][LK][WR + 4];
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * LM, n0 = blockIdx.x * FN;
@@ -280,15 +285,18 @@ gemm_nt_large_kernel(const float* __restrict__ A, const float* __restrict__ W, f
     if (EPI == 2) return c < FN ? (n0 + c < N ? n0 + c : -1) : (n0 + c - FN < N ? (int64_t)N + n0 + c - FN : -1);
     return n0 + c < N ? n0 + c : -1;
   };
-  float4 ra[2], rw[2];
+  float4 ra[2], rw[HALVES];
   auto fetch = [&](int k0) {
+    const bool k_ok = k0 + lk < K;                      // K is a multiple of 4: a piece is whole or absent
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int m = m0 + lr + 64 * half;
-      const int64_t wr = w_row(lr + 64 * half);
-      const bool k_ok = k0 + lk < K;                    // K is a multiple of 4: a piece is whole or absent
       ra[half] = (m < M && k_ok) ? *reinterpret_cast<const float4*>(A + (int64_t)m * lda + k0 + lk)
                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int half = 0; half < HALVES; ++half) {
+      const int64_t wr = w_row(lr + 64 * half);
       rw[half] = (wr >= 0 && k_ok) ? *reinterpret_cast<const float4*>(W + wr * ldw + k0 + lk)
                                    : make_float4(0.f, 0.f, 0.f, 0.f);
     }
@@ -299,16 +307,20 @@ gemm_nt_large_kernel(const float* __restrict__ A, const float* __restrict__ W, f
       const int r = lr + 64 * half;
       As[buf][lk + 0][r] = ra[half].x; As[buf][lk + 1][r] = ra[half].y;
       As[buf][lk + 2][r] = ra[half].z; As[buf][lk + 3][r] = ra[half].w;
+    }
+#pragma unroll
+    for (int half = 0; half < HALVES; ++half) {
+      const int r = lr + 64 * half;
       Ws[buf][lk + 0][r] = rw[half].x; Ws[buf][lk + 1][r] = rw[half].y;
       Ws[buf][lk + 2][r] = rw[half].z; Ws[buf][lk + 3][r] = rw[half].w;
     }
   };
 
-  float acc[8][8];
+  float acc[8][WC];
 #pragma unroll
   for (int i = 0; i < 8; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < WC; ++j) acc[i][j] = 0.f;
 
   fetch(0);
   stage(0);
@@ -321,14 +333,17 @@ gemm_nt_large_kernel(const float* __restrict__ A, const float* __restrict__ W, f
     for (int k = 0; k < LK; ++k) {
       const float4 a_lo = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
       const float4 a_hi = *reinterpret_cast<const float4*>(&As[buf][k][64 + ty * 4]);
-      const float4 w_lo = *reinterpret_cast<const float4*>(&Ws[buf][k][tx * 4]);
-      const float4 w_hi = *reinterpret_cast<const float4*>(&Ws[buf][k][64 + tx * 4]);
       const float a[8] = {a_lo.x, a_lo.y, a_lo.z, a_lo.w, a_hi.x, a_hi.y, a_hi.z, a_hi.w};
-      const float w[8] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w, w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+      float w[WC];
+#pragma unroll
+      for (int half = 0; half < HALVES; ++half) {
+        const float4 w4 = *reinterpret_cast<const float4*>(&Ws[buf][k][64 * half + tx * 4]);
+        w[4 * half + 0] = w4.x; w[4 * half + 1] = w4.y; w[4 * half + 2] = w4.z; w[4 * half + 3] = w4.w;
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        for (int j = 0; j < WC; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
     }
     if (more) {
       stage(buf ^ 1);
@@ -337,7 +352,7 @@ gemm_nt_large_kernel(const float* __restrict__ A, const float* __restrict__ W, f
     }
   }
 
-  // rows ty * 4 + i and 64 + ty * 4 + i; columns tx * 4 + j and 64 + tx * 4 + j
+  // rows ty * 4 + i and 64 + ty * 4 + i; columns tx * 4 + j and (128 rows of W) 64 + tx * 4 + j
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4);
@@ -348,11 +363,11 @@ gemm_nt_large_kernel(const float* __restrict__ A, const float* __restrict__ W, f
       for (int j = 0; j < 4; ++j) {
         const int n = n0 + tx * 4 + j;
         const float g = acc[i][j];
-        if (n < N) crow[n] = g / (1.0f + expf(-g)) * acc[i][4 + j];
+        if (n < N) crow[n] = g / (1.0f + expf(-g)) * acc[i][WC - 4 + j];
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < WC; ++j) {
         const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + j - 4);
         if (n < N) crow[n] = EPI == 1 ? crow[n] + acc[i][j] : acc[i][j];
       }
@@ -360,15 +375,37 @@ gemm_nt_large_kernel(const float* __restrict__ A, const float* __restrict__ W, f
   }
 }
 
-template <int EPI>
-int launch_large(const float* A, const float* W, float* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
-                 cudaStream_t stream) {
-  constexpr int FN = EPI == 2 ? LN / 2 : LN;
+int large_sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  return sms;
+}
+
+template <int EPI, int WR>
+int launch_large_as(const float* A, const float* W, float* C, int M, int N, int K, int64_t lda, int64_t ldw,
+                    int64_t ldc, cudaStream_t stream) {
+  constexpr int FN = EPI == 2 ? WR / 2 : WR;
   dim3 grid((N + FN - 1) / FN, (M + LM - 1) / LM);
   if (grid.y > 65535) return LS_E_SIZE;
   LS_COUNT(LS_K_GEMM_SIMT_MANY);
-  ls_launch(gemm_nt_large_kernel<EPI>, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
+  ls_launch(gemm_nt_large_kernel<EPI, WR>, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
   return ls_launch_status();
+}
+
+template <int EPI>
+int launch_large(const float* A, const float* W, float* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                 cudaStream_t stream) {
+  if constexpr (EPI != 2) {
+    // two blocks an SM: tiles of 64 features where 128 would not give every slot one (the tile's
+    // width changes no sum)
+    const long long wide = (long long)((N + 127) / 128) * ((M + LM - 1) / LM);
+    if (wide < 2LL * large_sm_count()) return launch_large_as<EPI, 64>(A, W, C, M, N, K, lda, ldw, ldc, stream);
+  }
+  return launch_large_as<EPI, 128>(A, W, C, M, N, K, lda, ldw, ldc, stream);
 }
 
 template <typename TA, typename TW, typename TC>
