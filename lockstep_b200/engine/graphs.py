@@ -184,10 +184,12 @@ class DecodeGraphs:
         collecting = gc.isenabled()
         gc.collect()
         gc.disable()
+        r.rt.exact_sizes = True
         try:
             with torch.cuda.graph(graph, pool=self.pool):
                 logits = r.forward(ctx)
         finally:
+            r.rt.exact_sizes = False
             if collecting:
                 gc.enable()
         recorded = K.LAUNCHES[0] - before

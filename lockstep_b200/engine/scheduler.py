@@ -27,10 +27,12 @@ from .policy import DefaultPolicy, Policy, SchedulerState
 from .trajectory import Trajectory
 
 
-@dataclass
+@dataclass(eq=False)
 class Request:
     """r = (uid, prompt, sampling parameters, seed); names as in LockStep
-    (engine/sched/scheduler.py:19-28)."""
+    (engine/sched/scheduler.py:19-28).  A request is itself, not its fields: two requests
+    are equal only if they are the same object, so membership in the scheduler's lists is a
+    comparison of identities."""
 
     uid: str
     prompt: list[int]

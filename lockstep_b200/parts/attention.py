@@ -64,9 +64,8 @@ class GQAttention(Mixer):
 
     def forward(self, x, ctx, cache, residual):
         nq, nkv, d = self.nq, self.nkv, self.d
-        dev, dt = residual.device, self.rt.dtype
         t = residual.shape[0]
-        q = torch.empty((t, nq * d), dtype=dt, device=dev)
+        q = self.rt.rows(t, nq * d)
         rot = self.position.rotary()
         cos, sin, rot_dim = rot if rot is not None else (None, None, 0)
         heads = (q, cache.pages, self.q_gain, self.k_gain, cos, sin, ctx.positions, ctx.token_slot,
@@ -80,13 +79,13 @@ class GQAttention(Mixer):
                                            self.w_qkv, *heads,
                                            normed=(x.h, x.gain, x.eps, x.row_index) if pending else None)
         if not fused:
-            qkv = torch.empty((t, (nq + 2 * nkv) * d), dtype=dt, device=dev)
+            qkv = self.rt.rows(t, (nq + 2 * nkv) * d)
             if isinstance(x, NormedRows):
                 x.linear(self.w_qkv, qkv, K.EPILOGUE_STORE, self.rt.err)
             else:
                 K.gemm_nt(x, self.w_qkv, qkv, err=self.rt.err)
             K.qk_norm_rope_store(qkv, *heads)
-        attn = torch.empty((t, nq * d), dtype=dt, device=dev)
+        attn = self.rt.rows(t, nq * d)
         plan, done = None, False
         if not self.exact and d in (64, 128):
             plan = ctx.attention_plan(self.window, K.attention_prefill_tc_tile_tokens())
@@ -99,8 +98,8 @@ class GQAttention(Mixer):
                 K.attention_tile(q, cache.pages, attn, None, None, plan.tile_work, plan.n_tile,
                                  cache.block_table, nq, nkv, d, self.window, self.scale, self.rt.err)
         if plan.n_split:
-            part_acc = torch.empty((plan.n_slots, nq, d), dtype=torch.float32, device=dev)
-            part_ml = torch.empty((plan.n_slots, nq, 2), dtype=torch.float32, device=dev)
+            part_acc = self.rt.rows(plan.n_slots, nq, d, dtype=torch.float32)
+            part_ml = self.rt.rows(plan.n_slots, nq, 2, dtype=torch.float32)
             done = False
             if not self.exact:
                 done = K.attention_decode_mma(q, cache.pages, part_acc, part_ml, plan.split_work,

@@ -62,6 +62,28 @@ class Runtime:
     max_positions: int
     err: torch.Tensor            # int32[2] device error word
     options: dict = field(default_factory=dict)
+    # True while a step is recorded into a CUDA graph: buffers then have exactly the rows asked
+    # for (they are kept for the graph's life, and their sizes never change).
+    exact_sizes: bool = False
+
+    def rows(self, rows: int, *tail: int, dtype: torch.dtype | None = None) -> torch.Tensor:
+        """An uninitialised [rows, *tail] buffer of a step's activations (``dtype``: the
+        engine's element type unless given).
+
+        The number of tokens in a step changes from step to step, and with it the size of
+        every activation.  torch's caching allocator keeps freed blocks by size, and a block
+        of more than a few MB serves only requests of nearly its own size, so a step with a
+        few more rows than any step before it asks the driver for new memory: a call that
+        waits for the device, tens of milliseconds in the middle of serving.  So the buffer
+        is cut from an allocation whose row count is rounded up (to 8 up to 64 rows, to 64
+        above): steps of nearly equal size then ask for equal sizes, and the allocator's
+        blocks are used again.  The rows beyond ``rows`` are never read or written.
+        """
+        dtype = self.dtype if dtype is None else dtype
+        if self.exact_sizes or rows <= 8:
+            return torch.empty((rows, *tail), dtype=dtype, device=self.device)
+        step = 8 if rows <= 64 else 64
+        return torch.empty((-(-rows // step) * step, *tail), dtype=dtype, device=self.device)[:rows]
 
 
 class Part:

@@ -27,7 +27,7 @@ class TokenEmbedding(Part):
         """The float32 residual stream [tokens, width] of the step's tokens.  An
         embedding that encodes absolute positions would add them here (``ctx.positions``)."""
         ids = ctx.token_ids
-        h = torch.empty((ids.numel(), self.width), dtype=torch.float32, device=ids.device)
+        h = self.rt.rows(ids.numel(), self.width, dtype=torch.float32)
         K.embed_gather(ids, self.table, h, self.rt.err)
         return h
 
@@ -46,7 +46,7 @@ class LinearHead(Part):
         self.weight = tensors["weight"]
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
-        logits = torch.empty((y.shape[0], self.vocab), dtype=torch.float32, device=y.device)
+        logits = self.rt.rows(y.shape[0], self.vocab, dtype=torch.float32)
         K.gemm_nt(y, self.weight, logits, err=self.rt.err)
         return logits
 

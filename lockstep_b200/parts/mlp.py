@@ -32,7 +32,7 @@ class SwiGLU(FeedForward):
         self.w_down = tensors["down_proj.weight"]
 
     def forward(self, x, ctx, residual):
-        act = torch.empty((residual.shape[0], self.i), dtype=self.rt.dtype, device=residual.device)
+        act = self.rt.rows(residual.shape[0], self.i)
         if isinstance(x, NormedRows):
             x.linear(self.w_gate_up, act, K.EPILOGUE_SILU_MUL, self.rt.err)
         else:

@@ -55,7 +55,7 @@ class RMSNorm(Norm):
 
     def forward(self, h, row_index=None):
         rows = h.shape[0] if row_index is None else row_index.numel()
-        out = torch.empty((rows, self.width), dtype=self.rt.dtype, device=h.device)
+        out = self.rt.rows(rows, self.width)
         K.rmsnorm(h, self.gain, out, self.eps, self.rt.err, row_index)
         return out
 
