@@ -18,7 +18,9 @@ buffer that is refilled before each replay; work lists are padded to the
 capacity with null items, which the kernels skip.  Nothing about the
 arithmetic changes: the same kernels run on the same values.
 
-Only models whose parts are all ``graph_safe`` are recorded.
+A model whose parts are all ``graph_safe`` is one graph.  Where some are not (a mixer that
+reads the step's portions on the host), the runs of graph-safe steps between them are
+recorded, one graph each, and the other steps are called between the replays.
 """
 
 from __future__ import annotations
@@ -167,14 +169,19 @@ class DecodeGraphs:
         return key in self.graphs
 
     def record(self, key) -> None:
-        """Record the model's forward for ``key`` (nothing runs while recording)."""
+        """Record the model's forward for ``key`` (nothing runs while recording).
+
+        The program's runs of graph-safe steps become one graph each; a step that is not
+        graph-safe (a part that reads host-side values of the context) is kept as it is and
+        called between the replays, on the same residual stream: the buffer that the recorded
+        embedding made.  Such steps are not called here, so a mixer's state is not touched by
+        recording."""
         r = self.runner
         batch, capacity = key
         ctx = StaticStepContext(batch, capacity, self.windows, r.device, r.err, r.split_size,
                                 pad_slot=r.cache.pad_slot)
         if self.pool is None:
             self.pool = torch.cuda.graph_pool_handle()
-        graph = torch.cuda.CUDAGraph()
         torch.cuda.synchronize()
         from .. import kernels as K
 
@@ -185,16 +192,29 @@ class DecodeGraphs:
         gc.collect()
         gc.disable()
         r.rt.exact_sizes = True
+        pieces, h, stream = [], None, None
         try:
-            with torch.cuda.graph(graph, pool=self.pool):
-                logits = r.forward(ctx)
+            for safe, fns in _runs(r.program):
+                if not safe:
+                    pieces.append((None, fns))
+                    continue
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, pool=self.pool):
+                    for fn in fns:
+                        h = fn(h, ctx)
+                        if stream is None:
+                            stream = h       # what the embedding made: the residual stream
+                pieces.append((graph, None))
         finally:
             r.rt.exact_sizes = False
             if collecting:
                 gc.enable()
         recorded = K.LAUNCHES[0] - before
         K.LAUNCHES[0] = before               # recording launches nothing
-        self.graphs[key] = (graph, ctx, logits, recorded)
+        # the last step's result is the logits: the graph's own buffer when that step is
+        # recorded, else what the step returns at every replay
+        logits = h if pieces[-1][0] is not None else None
+        self.graphs[key] = (pieces, ctx, stream, logits, recorded)
         while len(self.graphs) > self.max_graphs:
             # nothing of the dropped graph is in flight: record() synchronised above
             self.graphs.popitem(last=False)
@@ -206,12 +226,28 @@ class DecodeGraphs:
         after the host's values and before the replay."""
         from .. import kernels as K
 
-        graph, ctx, logits, recorded = self.graphs[key]
+        pieces, ctx, h, logits, recorded = self.graphs[key]
         self.graphs.move_to_end(key)
         ctx.fill(entries, slots)
         if tokens_device is not None:
             ctx.token_ids[:len(entries)].copy_(tokens_device, non_blocking=True)
-        graph.replay()
+        for graph, fns in pieces:
+            if graph is not None:
+                graph.replay()
+            else:
+                for fn in fns:
+                    h = fn(h, ctx)
         K.LAUNCHES[0] += recorded
         self.replays += 1
-        return logits[:len(entries)]
+        return (h if logits is None else logits)[:len(entries)]
+
+
+def _runs(program):
+    """``program`` [(graph_safe, fn)] as runs [(graph_safe, [fn, ...])] of equal safety."""
+    out: list[tuple[bool, list]] = []
+    for safe, fn in program:
+        if out and out[-1][0] == safe:
+            out[-1][1].append(fn)
+        else:
+            out.append((safe, [fn]))
+    return out

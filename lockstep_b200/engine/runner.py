@@ -65,10 +65,12 @@ class ModelRunner:
         # request's new tokens, the pages they go to are checked to be that request's alone
         self.check_exclusive = bool(check_exclusive or poison_freed_pages)
         self.steps_run = 0
-        # decode steps are recorded as CUDA graphs when every part allows it
+        self.program = self._program()
+        # decode steps are recorded as CUDA graphs: the runs of graph-safe steps of the program
+        # are recorded, the other steps are called between the replays.  (The embedding has to
+        # be graph-safe: what it returns is the buffer every later step works on.)
         self.graphs = None
-        if use_graphs and all(part.graph_safe for part in
-                              [self.model.embedding, self.model.final_norm, self.model.head, *self.model.blocks]):
+        if use_graphs and self.program[0][0] and any(safe for safe, _ in self.program[1:]):
             from .graphs import DecodeGraphs
 
             self.graphs = DecodeGraphs(self)
@@ -99,17 +101,41 @@ class ModelRunner:
         self.cache.advance(uid, tokens)
 
     # -- the step -----------------------------------------------------------
+    def _program(self) -> list[tuple[bool, object]]:
+        """The model as steps ``(graph_safe, fn)`` that run one after the other:
+        ``fn(h, ctx)`` returns the residual stream for the next step (the embedding makes
+        it, the layers' steps change it in place) and the last one returns the logits."""
+        model = self.model
+
+        def embed(h, ctx):
+            return model.embedding.forward(ctx)
+
+        def layer_step(fn, run):
+            def call(h, ctx):
+                fn(h, ctx, self.cache.view(run.cache, run.writes_cache))
+                return h
+            return call
+
+        def finish(h, ctx):
+            if ctx.n_wanted:
+                return model.head.forward(model.final_norm.forward(h, ctx.wanted_rows))
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+
+        program = [(bool(model.embedding.graph_safe), embed)]
+        for run in self.spec.schedule:
+            for safe, fn in model.blocks[run.layer].steps():
+                program.append((bool(safe), layer_step(fn, run)))
+        program.append((bool(model.final_norm.graph_safe and model.head.graph_safe), finish))
+        return program
+
     @torch.no_grad()
     def forward(self, ctx) -> torch.Tensor:
         """The model on one packed batch: embedding, the scheduled layers, final norm
         and head at the wanted rows.  Launches kernels only; no host synchronisation."""
-        model = self.model
-        h = model.embedding.forward(ctx)
-        for run in self.spec.schedule:
-            model.blocks[run.layer].forward(h, ctx, self.cache.view(run.cache, run.writes_cache))
-        if ctx.n_wanted:
-            return model.head.forward(model.final_norm.forward(h, ctx.wanted_rows))
-        return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        h = None
+        for _, fn in self.program:
+            h = fn(h, ctx)
+        return h
 
     @torch.no_grad()
     def can_step_ahead(self, entries: list[StepEntry]) -> bool:

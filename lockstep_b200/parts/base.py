@@ -93,7 +93,10 @@ class Part:
     # tensors of the step context and shapes that depend on the batch's token
     # count alone: such a part may be recorded in a CUDA graph and replayed with
     # new contents in the same buffers.  A part that reads host-side values of the
-    # context (``ctx.portions``) in ``forward`` must leave it False.
+    # context (``ctx.portions``) in ``forward`` must leave it False: it is then called as
+    # it is between the recorded runs of the other parts.  Whether recorded or not, a part
+    # takes token ids from ``ctx.token_ids`` (on the device) only: a decode step may be
+    # launched before the host has seen the tokens it brings.
     graph_safe = False
 
     # True for a mixer or feed-forward whose ``forward`` takes ``x`` either as a tensor or
@@ -149,6 +152,14 @@ class Block(Part):
     def forward(self, h: torch.Tensor, ctx, cache) -> None:
         """Run the layer on the residual stream ``h`` in place."""
         raise NotImplementedError
+
+    def steps(self) -> list[tuple[bool, Callable]]:
+        """The layer's work cut into steps that run one after the other: pairs
+        ``(graph_safe, fn)`` with ``fn(h, ctx, cache)`` changing ``h`` in place.  Running all
+        of them is ``forward``.  A recorded decode step records runs of graph-safe steps and
+        calls the others as they are, so an arrangement that names its mixer and its
+        feed-forward as steps of their own keeps the one in a graph when the other cannot be."""
+        return [(bool(self.graph_safe), self.forward)]
 
 
 # ---------------------------------------------------------------------------

@@ -59,9 +59,19 @@ class PreNormBlock(Block):
             return norm.lazy(h)
         return norm.forward(h)
 
-    def forward(self, h, ctx, cache):
+    def _mix(self, h, ctx, cache):
         self.mixer.forward(self._normed(self.mixer_norm, self.mixer, h), ctx, cache, h)
+
+    def _feed_forward(self, h, ctx, cache):
         self.feed_forward.forward(self._normed(self.feed_forward_norm, self.feed_forward, h), ctx, h)
+
+    def steps(self):
+        return [(bool(self.mixer_norm.graph_safe and self.mixer.graph_safe and self.position.graph_safe), self._mix),
+                (bool(self.feed_forward_norm.graph_safe and self.feed_forward.graph_safe), self._feed_forward)]
+
+    def forward(self, h, ctx, cache):
+        self._mix(h, ctx, cache)
+        self._feed_forward(h, ctx, cache)
 
 
 @register_part("block", "pre_norm")

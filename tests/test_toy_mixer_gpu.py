@@ -145,3 +145,39 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
             H.assert_rows_close(rows, want, dtype, "toy")   # slot reuse: "d" takes a used slot
     finally:
         unregister_toy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_of_the_toy_model_are_recorded_around_its_mixer(tmp_path, dtype):
+    """The toy mixer reads the step's portions on the host, so it cannot be part of a recorded
+    step.  The steps around it can: the decode steps replay graphs of the attention layer, the
+    feed-forwards and the head, call the toy mixer between them, and give the bits of a runner
+    that records nothing."""
+    from lockstep_b200 import ModelRunner
+    from lockstep_b200.weights import write_random_model
+
+    register_toy()
+    try:
+        raw = {"architectures": ["ToyStateForCausalLM"], "width": 48, "heads": 3, "head_dim": 16,
+               "ffn": 72, "vocab": 150, "layers": 3, "eps": 1e-5}
+        folder = write_random_model(tmp_path / "toy", raw, seed=2, dtype=dtype, init_std=0.3, gain_std=0.1)
+        requests = {"a": H.random_tokens(60, 150, 1), "b": H.random_tokens(47, 150, 2)}
+        want = {u: plain_toy(folder, t) for u, t in requests.items()}
+        rows = {}
+        for graphs in (True, False):
+            runner = ModelRunner(folder, dtype=dtype, num_pages=16, page_size=16, max_live=3, max_seq_len=256,
+                                 use_graphs=graphs)
+            assert (runner.graphs is not None) == graphs
+            rows[graphs] = H.run_plan(runner, H.plan_bulk_then_single(requests, tail=32))
+            if graphs:
+                assert runner.graphs.replays >= 25
+                pieces = next(iter(runner.graphs.graphs.values()))[0]
+                kinds = [graph is not None for graph, _ in pieces]
+                # embedding | toy | ffn, attention layer, ffn | toy | ffn | toy | ffn, head
+                assert kinds == [True, False, True, False, True, False, True]
+        H.assert_rows_close(rows[True], want, dtype, "toy, recorded around the mixer")
+        assert rows[True].keys() == rows[False].keys()
+        for key in rows[True]:
+            assert torch.equal(rows[True][key], rows[False][key]), key
+    finally:
+        unregister_toy()

@@ -193,7 +193,9 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
                "inner": 48, "ffn": 112, "vocab": 210, "layers": 3, "eps": 1e-5, "step": 0.013}
         folder = write_random_model(tmp_path / "toy", raw, seed=4, dtype=dtype, init_std=0.3, gain_std=0.1)
         runner = ModelRunner(folder, dtype=dtype, num_pages=24, page_size=8, max_live=3, max_seq_len=256)
-        assert runner.graphs is None            # the routed part reads values on the host: no recorded steps
+        # the routed part reads values on the host, so it is called as it is between the recorded
+        # runs of the other steps of a decode step
+        assert runner.graphs is not None
         requests, want = {}, {}
         # sequences whose every token has a clear winner among the experts (a near tie may go
         # either way in reduced precision, which is a property of routing, not a fault)
@@ -205,8 +207,12 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
             if margin > (1e-3 if dtype == "float32" else 0.05):
                 uid = "abcd"[len(requests)]
                 requests[uid], want[uid] = tokens, logits
-        for plan in (H.plan_whole, H.plan_portions, lambda r: H.plan_mixed(r, max_live=3)):
+        for plan in (H.plan_whole, H.plan_portions, lambda r: H.plan_mixed(r, max_live=3),
+                     lambda r: H.plan_bulk_then_single({u: r[u] for u in "ac"}, tail=16)):
             rows = H.run_plan(runner, plan(requests))
             H.assert_rows_close(rows, want, dtype, "toy parts")
+        assert runner.graphs.replays >= 14
+        pieces = next(iter(runner.graphs.graphs.values()))[0]
+        assert [graph is not None for graph, _ in pieces].count(False) == 2     # the routed parts of layers 0 and 2
     finally:
         unregister_toys()
