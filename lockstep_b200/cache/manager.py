@@ -76,6 +76,10 @@ class PagedGroup:
         self.pinned: dict[int, int] = {}
         self.poison = bool(poison_freed_pages)
         self.poisoned = 0
+        # True (prefix reuse is on): a windowed group keeps what the last whole-page boundary's
+        # window reads, not only what the next position's does, so that a finished request's
+        # whole pages can be adopted by a request that goes on from that boundary
+        self.keep_boundary_window = False
 
     def _give_back(self, page: int) -> None:
         """Drop one reference on ``page``; a page nobody holds any more is poisoned (debug option)."""
@@ -133,7 +137,8 @@ class PagedGroup:
         if not self.window:
             return 0
         seq = self.seqs[uid]
-        first = self.first_needed_page(kv_len)
+        first = self.first_needed_page(kv_len // self.page_size * self.page_size if self.keep_boundary_window
+                                       else kv_len)
         freed = 0
         for logical in range(min(first, len(seq.pages))):
             page = seq.pages[logical]
@@ -154,8 +159,9 @@ class PagedGroup:
         seq = self.seqs[uid]
         if seq.pages:
             raise AuditFailure("adopt expects a request that holds no pages yet")
-        for page in pages:
-            self.allocator.retain(page)
+        for page in pages:                    # -1: a page behind the window, which nobody reads any more
+            if page >= 0:
+                self.allocator.retain(page)
             self.table_host[seq.slot, len(seq.pages)] = page
             seq.pages.append(page)
         seq.shared = len(pages)
@@ -302,9 +308,15 @@ class CacheManager:
         for g in self.paged:
             need = -(-total_tokens // self.page_size)
             if g.window and total_tokens > max_portion:
-                need = min(need, -(-(g.window - 1 + max_portion) // self.page_size) + 1)
+                need = min(need, -(-(g.window - 1 + max_portion) // self.page_size) + 1 + g.keep_boundary_window)
             worst = max(worst, need)
         return worst
+
+    def keep_boundary_windows(self, on: bool = True) -> None:
+        """Windowed groups keep the pages that the window of the last whole-page boundary reads
+        (at most one page more per request): what a request that adopts the whole pages needs."""
+        for g in self.paged:
+            g.keep_boundary_window = bool(on)
 
     def pages_short(self, uid: str, total_tokens: int) -> int:
         """The most new pages any group needs to hold ``total_tokens`` of ``uid``."""

@@ -109,9 +109,11 @@ class Scheduler:
         self._step_limit = 1 << 62
         self.prefix = None
         if enable_prefix_cache:
-            if len(self.cache.paged) != 1 or self.cache.paged[0].window or self.cache.states:
-                raise ValueError("prefix reuse needs a cache of one paged group that keeps all keys")
+            if self.cache.states or not self.cache.paged:
+                raise ValueError("prefix reuse shares pages of keys and values: a model that keeps a "
+                                 "fixed-size state per request cannot take part")
             self.prefix = PrefixIndex(page_size=self.cache.page_size)
+            self.cache.keep_boundary_windows()
 
     # -- bookkeeping ----------------------------------------------------------
     def _event(self, name: str, uid: str, detail=()):
@@ -122,7 +124,12 @@ class Scheduler:
         return self.cache.peak_pages(tokens, min(tokens, self.max_step_tokens))
 
     def _reclaimable(self) -> int:
-        return self.prefix.reclaimable(self.cache.paged[0]) if self.prefix else 0
+        """How many more pages evictions can add to ``cache.free_pages()`` (the scarcest group's count)."""
+        if not self.prefix:
+            return 0
+        groups = self.cache.paged
+        gain = self.prefix.reclaimable(groups)
+        return min(g.allocator.free_pages + n for g, n in zip(groups, gain)) - self.cache.free_pages()
 
     def _state(self) -> SchedulerState:
         return SchedulerState(
@@ -150,14 +157,12 @@ class Scheduler:
         request.cache_hit_tokens = 0
         self._event("resume" if request.preempt_count else "admit", request.uid)
         if self.prefix is not None:
-            group = self.cache.paged[0]
             context = request.context()
-            hit, pages = self.prefix.lookup(context)
-            if hit >= len(context) and pages:       # keep something to compute
-                hit -= self.cache.page_size
-                pages = pages[:-1]
+            # (at most all but the last token: something is left to compute)
+            hit, pages = self.prefix.lookup(context, self.cache.paged, limit=len(context) - 1)
             if hit and self.policy.honor_cache_hit(state, request.uid, hit):
-                group.adopt(request.uid, pages)
+                for group, held in zip(self.cache.paged, pages):
+                    group.adopt(request.uid, held)
                 request.kv_len = request.cache_hit_tokens = hit
                 self.cache.lengths[request.uid] = hit
                 self._event("cache_hit", request.uid, (hit,))
@@ -179,13 +184,12 @@ class Scheduler:
                 self.cache.reserve(request.uid, tokens)
                 return True
             if self.prefix is not None:
-                group = self.cache.paged[0]
-                candidates = self.prefix.evictable(group)
+                candidates = self.prefix.evictable(self.cache.paged)
                 if candidates:
                     victim = self.policy.evict_victim(self._state(), tuple(candidates))
                     if victim not in candidates:
                         raise ValueError(f"policy {self.policy.name} chose page {victim}, which is not evictable")
-                    self.prefix.evict(victim, group)
+                    self.prefix.evict(victim, self.cache.paged)
                     self.stats["evictions"] += 1
                     self._event("evict", request.uid, (victim,))
                     continue
@@ -336,9 +340,7 @@ class Scheduler:
                 self.running.remove(request)
                 self.done.append(request)
                 if self.prefix is not None:
-                    group = self.cache.paged[0]
-                    self.prefix.insert(request.context()[:request.kv_len],
-                                       group.seqs[request.uid].pages, group)
+                    self.prefix.insert(request.context()[:request.kv_len], self.cache.paged, request.uid)
                 self.cache.release(request.uid)
                 self._event("finish", request.uid)
 

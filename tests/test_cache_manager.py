@@ -133,14 +133,15 @@ def test_prefix_index_shares_whole_pages():
     toks = list(range(11))
     m.create("a")
     m.reserve("a", 11)
-    assert idx.insert(toks, g.seqs["a"].pages, g) == 2      # two whole pages
+    assert idx.insert(toks, g, "a") == 2                    # two whole pages
     m.release("a")
     m.audit()
-    assert g.allocator.free_pages == 14 and idx.evictable(g) == [1] and idx.reclaimable(g) == 2
-    hit, pages = idx.lookup(toks[:9] + [99, 98])
-    assert hit == 8 and pages == [0, 1]
+    assert g.allocator.free_pages == 14 and idx.evictable(g) == [1] and idx.reclaimable(g) == [2]
+    hit, pages = idx.lookup(toks[:9] + [99, 98], g)
+    assert hit == 8 and pages == [[0, 1]]
+    assert idx.lookup(toks[:8], g, limit=7)[0] == 4          # something is left to compute
     m.create("b")
-    g.adopt("b", pages)
+    g.adopt("b", pages[0])
     m.reserve("b", 11)
     m.audit()
     assert idx.evictable(g) == []                          # a running request holds them
@@ -150,7 +151,7 @@ def test_prefix_index_shares_whole_pages():
     assert idx.evict(1, g) and idx.evictable(g) == [0] and idx.evict(0, g)
     m.audit()
     assert g.allocator.free_pages == 16
-    assert idx.lookup(toks)[0] == 0
+    assert idx.lookup(toks, g)[0] == 0
 
 
 def test_prefix_eviction_leaves_no_unreachable_page():
@@ -165,14 +166,14 @@ def test_prefix_eviction_leaves_no_unreachable_page():
     for i, toks in enumerate(chains):
         uid = f"r{i}"
         m.create(uid)
-        hit, pages = idx.lookup(toks)
-        g.adopt(uid, pages)
+        hit, pages = idx.lookup(toks, g)
+        g.adopt(uid, pages[0])
         m.lengths[uid] = hit
         m.reserve(uid, len(toks))
-        idx.insert(toks, g.seqs[uid].pages, g)
+        idx.insert(toks, g, uid)
         m.release(uid)
     idx.audit()
-    assert len(idx.entries) == 2 + 3 * 2 and idx.reclaimable(g) == 8
+    assert len(idx.entries) == 2 + 3 * 2 and idx.reclaimable(g) == [8]
     while idx.entries:
         offered = idx.evictable(g)
         assert offered, "pages are indexed but none is offered"
@@ -180,13 +181,62 @@ def test_prefix_eviction_leaves_no_unreachable_page():
         idx.audit()
         m.audit()
         for toks in chains:                 # what lookup finds is exactly what is still indexed
-            hit, pages = idx.lookup(toks)
-            assert len(pages) == hit // 4
+            hit, pages = idx.lookup(toks, g)
+            assert len(pages[0]) == hit // 4
         reachable = set()
         for toks in chains:
-            reachable.update(idx.lookup(toks)[1])
+            reachable.update(idx.lookup(toks, g)[1][0])
         assert reachable == {e.page for e in idx.entries.values()}
     assert g.allocator.free_pages == 32
+
+
+def test_prefix_index_over_a_group_that_keeps_all_keys_and_one_with_a_window():
+    win = CacheNeed("paged_kv", kv_heads=1, head_dim=16, window=8)
+    m = manager([FULL, win], pages=16, page=4)
+    full, windowed = m.paged
+    idx = PrefixIndex(page_size=4)
+    toks = list(range(100, 141))
+    m.create("a")
+    for n in range(4, 42, 4):                       # grows by a page a step; the window lets pages go
+        m.reserve("a", min(n, 41))
+        m.advance("a", min(n, 41))
+    m.reserve("a", 41)
+    m.advance("a", 41)
+    assert windowed.seqs["a"].pages[:8] == [-1] * 8 and min(windowed.seqs["a"].pages[8:]) >= 0
+    assert idx.insert(toks, m.paged, "a") == 10     # ten whole pages; the windowed group has two of them
+    m.release("a")
+    m.audit()
+    idx.audit()
+    assert idx.reclaimable(m.paged) == [10, 2]
+    hit, pages = idx.lookup(toks + [7], m.paged)
+    assert hit == 40 and min(pages[0]) >= 0
+    assert pages[1][:8] == [-1] * 8 and min(pages[1][8:]) >= 0      # keys 33.. are what position 40 reads
+    # one page less: position 36 reads keys 29.., that is page 7, which was given back
+    assert idx.lookup(toks[:36] + [1, 2, 3, 4, 5], m.paged)[0] == 0
+    assert idx.lookup(toks, m.paged, limit=39)[0] == 0
+    # the all-keys group alone could use any of it
+    assert idx.lookup(toks[:22], [full])[0] == 20
+    m.create("b")
+    for g, held in zip(m.paged, pages):
+        g.adopt("b", held)
+    m.lengths["b"] = hit
+    m.reserve("b", 50)
+    m.advance("b", 50)                              # gives back the adopted pages behind its window
+    m.audit()
+    assert idx.evictable(m.paged) == []             # "b" holds the chain's last page in the first group
+    assert idx.insert(toks + list(range(9)), m.paged, "b") == 2     # pages 10 and 11 are new
+    m.release("b")
+    m.audit()
+    idx.audit()
+    order = []
+    while idx.entries:
+        offered = idx.evictable(m.paged)
+        assert len(offered) == 1                    # one chain: only its end
+        order.append(offered[0])
+        idx.evict(offered[0], m.paged)
+        m.audit()
+    assert len(order) == 12
+    assert full.allocator.free_pages == windowed.allocator.free_pages == 16
 
 
 def test_freed_pages_are_poisoned_and_shared_pages_are_not_written():
@@ -197,14 +247,14 @@ def test_freed_pages_are_poisoned_and_shared_pages_are_not_written():
     m.create("a")
     m.reserve("a", 10)
     m.assert_exclusive("a", 0, 9)
-    idx.insert(list(range(10)), g.seqs["a"].pages, g)
+    idx.insert(list(range(10)), g, "a")
     with pytest.raises(AuditFailure, match="holders"):
         m.assert_exclusive("a", 4, 9)                  # its first two pages are now the index's too
     m.assert_exclusive("a", 8, 9)
     m.release("a")
     assert g.poisoned == 1                             # the third page; the index keeps the other two
     m.create("b")
-    g.adopt("b", idx.lookup(list(range(8)))[1])
+    g.adopt("b", idx.lookup(list(range(8)), g)[1][0])
     m.lengths["b"] = 8
     m.reserve("b", 12)
     m.assert_exclusive("b", 8, 11)

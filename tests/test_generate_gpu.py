@@ -137,6 +137,41 @@ def test_windowed_layers_through_the_entry_point_reuse_pages_behind_the_window(t
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefix_reuse_with_windowed_layers_serves_the_next_turn(tmp_path, dtype):
+    """Configuration C (a group that keeps all keys, a group with a window of 40) with prefix
+    reuse: the next turn of a finished conversation adopts the whole prefix (in the windowed
+    group only the window's pages are left, and only they are needed), pages that were freed
+    are poisoned, and the tokens are those of a run without reuse."""
+    from lockstep_b200 import Engine, Request
+
+    folder = H.make_model_folder(tmp_path, H.TINY_C, seed=31, dtype=dtype)
+    vocab = H.TINY_C["vocab_size"]
+    first = H.random_tokens(150, vocab, 120)
+
+    def run(**kw):
+        engine = Engine(folder, dtype=dtype, num_pages=40, page_size=H.PAGE_C, max_running=2, max_step_tokens=64,
+                        max_seq_len=320, audit=True, **kw)
+        a = engine.generate([Request(uid="turn1", prompt=first, max_new_tokens=30)])["turn1"]
+        follow = first + a + H.random_tokens(21, vocab, 121)
+        b = engine.generate([Request(uid="turn2", prompt=follow, max_new_tokens=30)])["turn2"]
+        return a, follow, b, engine
+
+    a0, follow0, b0, _ = run()
+    a1, follow1, b1, engine = run(enable_prefix_cache=True, poison_freed_pages=True)
+    hits = [e for e in engine.scheduler.events if e[1] == "cache_hit"]
+    assert len(hits) == 1 and hits[0][2] == "turn2"
+    held = (len(first) + 30 - 1) // H.PAGE_C * H.PAGE_C          # whole pages of what turn 1 fed
+    assert hits[0][3] == (held,)
+    windowed = [g for g in engine.cache.paged if g.window][0]
+    assert windowed.poisoned > 0
+    if dtype == "float32":
+        assert (a1, b1) == (a0, b0)                              # the same bits however a row was reached
+    assert follow1[:len(first)] == first
+    check_tokens(folder, first, a1, dtype, config="C")
+    check_tokens(folder, follow1, b1, dtype, config="C")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_command_line_runs_a_workload(tmp_path, dtype):
     """``bin/lockstep run --workload``: a model folder and a file of requests in, token ids out."""
     import json

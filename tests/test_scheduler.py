@@ -23,9 +23,9 @@ def next_token(context):
 
 
 class FakeBackend:
-    def __init__(self, pages=64, page=4, live=8, seq=4096, window=0):
-        need = CacheNeed("paged_kv", kv_heads=1, head_dim=16, window=window)
-        self.cache = CacheManager([need], num_pages=pages, page_size=page, max_live=live,
+    def __init__(self, pages=64, page=4, live=8, seq=4096, window=0, windows=None):
+        needs = [CacheNeed("paged_kv", kv_heads=1, head_dim=16, window=w) for w in (windows or [window])]
+        self.cache = CacheManager(needs, num_pages=pages, page_size=page, max_live=live,
                                   max_seq_len=seq, allocate=False)
         self.history: dict[str, list[int]] = {}
         self.steps: list[list[tuple[str, int, int]]] = []
@@ -55,7 +55,7 @@ class FakeBackend:
 
 
 def run(requests, **kw):
-    backend_kw = {k: kw.pop(k) for k in ("pages", "page", "live", "seq", "window") if k in kw}
+    backend_kw = {k: kw.pop(k) for k in ("pages", "page", "live", "seq", "window", "windows") if k in kw}
     backend = FakeBackend(**backend_kw)
     sched = Scheduler(backend, audit=True, **kw)
     backend._context = {}
@@ -198,6 +198,56 @@ def test_prefix_reuse_skips_shared_pages_and_evicts_under_pressure():
     sched.cache.audit()
 
 
+@pytest.mark.parametrize("new", [11, 14])       # the first turn ends on a page's edge, or three tokens past it
+def test_prefix_reuse_with_a_windowed_group_serves_the_next_turn(new):
+    """Layers that keep every key beside layers that keep a window of 12: a finished request's
+    pages are indexed in both groups, the windowed one only has its last pages left.  The next
+    turn of the same conversation adopts the whole prefix (all pages of the one group, the
+    window's pages of the other); a request that shares only the beginning gets nothing, since
+    the window's pages at that point were given back long ago."""
+    first = Request("a", list(range(30)), max_new_tokens=new)
+    out, sched, backend = run([first], pages=24, page=4, windows=[0, 12], seq=256, enable_prefix_cache=True)
+    full, win = sched.cache.paged
+    assert full.window == 0 and win.window == 12
+    held = first.kv_len // 4                                    # whole pages of the 40 or 43 tokens it fed
+    assert held == 10
+    assert sched.prefix.reclaimable(sched.cache.paged) == [held, 3]   # keys 28.. of the window: pages 7, 8, 9
+    turn = Request("b", first.context() + [70, 71, 72], max_new_tokens=5)
+    backend._context["b"] = turn.context
+    sched.submit(turn)
+    sched.run()
+    assert turn.cache_hit_tokens == held * 4
+    starts = [start for step in backend.steps for u, start, _ in step if u == "b"]
+    assert starts[0] == held * 4 and turn.generated == expected(turn.prompt, 5)
+    other = Request("c", list(range(20)) + [80, 81], max_new_tokens=3)
+    backend._context["c"] = other.context
+    sched.submit(other)
+    sched.run()
+    assert other.cache_hit_tokens == 0 and other.generated == expected(other.prompt, 3)
+    # under pressure the index gives everything back, in both groups
+    big = Request("d", [9] * 70, max_new_tokens=8)
+    backend._context["d"] = big.context
+    sched.submit(big)
+    sched.run()
+    assert sched.stats["evictions"] > 0 and big.generated == expected(big.prompt, 8)
+    sched.cache.audit()
+    sched.prefix.audit()
+    while sched.prefix.evictable(sched.cache.paged):
+        sched.prefix.evict(sched.prefix.evictable(sched.cache.paged)[0], sched.cache.paged)
+    assert not sched.prefix.entries
+    assert full.allocator.free_pages == win.allocator.free_pages == 24
+
+
+def test_prefix_reuse_is_refused_for_a_model_with_state_slots():
+    backend = FakeBackend()
+    backend.cache = CacheManager([CacheNeed("paged_kv", kv_heads=1, head_dim=16),
+                                  CacheNeed("state", state_shape=(4,))], num_pages=8, page_size=4, max_live=2,
+                                 max_seq_len=64, allocate=False)
+    with pytest.raises(ValueError, match="fixed-size state"):
+        Scheduler(backend, enable_prefix_cache=True)
+    Scheduler(backend)
+
+
 def test_windowed_group_frees_pages_while_decoding():
     r = Request("a", list(range(30)), max_new_tokens=60)
     out, sched, backend = run([r], pages=8, page=4, window=12, seq=128, max_step_tokens=16)
@@ -247,7 +297,7 @@ class FakeAsyncBackend(FakeBackend):
 
 
 def run_ahead(requests, late=(), **kw):
-    backend_kw = {k: kw.pop(k) for k in ("pages", "page", "live", "seq", "window") if k in kw}
+    backend_kw = {k: kw.pop(k) for k in ("pages", "page", "live", "seq", "window", "windows") if k in kw}
     backend = FakeAsyncBackend(**backend_kw)
     sched = Scheduler(backend, **kw)
     for r in requests:
