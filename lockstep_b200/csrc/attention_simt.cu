@@ -50,7 +50,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
                       float* __restrict__ part_acc, float* __restrict__ part_ml,
                       const int* __restrict__ work, const int* __restrict__ block_table,
                       int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
-                      int window, float scale, int* err) {
+                      int window, float scale, const float* __restrict__ slopes, int* err) {
   ls_dependency_sync();
   extern __shared__ __align__(16) float smem[];
   // rows of Q and K are d + 4 floats apart: 16-byte pieces stay aligned, and the eight key rows a
@@ -68,6 +68,9 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
   const int split_begin = w[4], split_end = w[5], slot_base = w[6];
   const int h = blockIdx.y;
   const int kvh = h / (nq / nkv);
+  // slopes (or null): a score gets slopes[head] x (key position - query position) added,
+  // a position encoding that biases the scores instead of rotating queries and keys
+  const float slope = slopes != nullptr ? slopes[h] : 0.f;
   const int tid = threadIdx.x;
   const int m = tid >> 3, sub = tid & 7;
   // Outputs of a thread: dimensions sub * 4 + e + 32 * jj (e < 4) that lie below d.  Which thread
@@ -173,7 +176,8 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
         for (int j = 0; j < 4; ++j) {
           const int key = n0 + sub + 8 * j;
           const bool keep = key < s_hi && key <= qpos && key >= row_lo;
-          s[j] = keep ? dot[j] * scale : -CUDART_INF_F;
+          s[j] = !keep ? -CUDART_INF_F
+                 : slopes != nullptr ? fmaf(slope, (float)(key - qpos), dot[j] * scale) : dot[j] * scale;
           tile_max = fmaxf(tile_max, s[j]);
         }
       }
@@ -285,7 +289,7 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
                         float* __restrict__ part_acc, float* __restrict__ part_ml,
                         const int* __restrict__ work, const int* __restrict__ block_table,
                         int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
-                        int window, float scale, int slot_limit, int* err) {
+                        int window, float scale, const float* __restrict__ slopes, int slot_limit, int* err) {
   ls_dependency_sync();
   extern __shared__ __align__(16) unsigned char dsm[];
   constexpr int VEC = 16 / sizeof(T);        // elements per 16-byte chunk
@@ -364,7 +368,8 @@ attention_decode_kernel(const T* __restrict__ q, const T* __restrict__ pages,
         for (int x = 0; x < VEC; ++x) dot = fmaf(qr[c + x], ls_to_float<T>(e[x]), dot);
       }
       const bool keep = key < s_hi && key >= row_lo;
-      Ss[u] = keep ? dot * scale : -CUDART_INF_F;
+      Ss[u] = !keep ? -CUDART_INF_F
+              : slopes != nullptr ? fmaf(slopes[kvh * group + g], (float)(key - pos), dot * scale) : dot * scale;
     }
     __syncthreads();
 
@@ -466,8 +471,8 @@ LS_API int ls_attention_split_size() { return LS_SPLIT; }
 LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float* part_acc,
                              float* part_ml, int dtype, const int* work, int n_work,
                              const int* block_table, int table_stride, int nq, int nkv, int d,
-                             int page_size, int num_pages, int window, float scale, int* err,
-                             cudaStream_t stream) {
+                             int page_size, int num_pages, int window, float scale,
+                             const float* slopes, int* err, cudaStream_t stream) {
   if (n_work <= 0) return 0;
   if (!shape_ok(nq, nkv, d, page_size, LS_SPLIT)) return LS_E_SIZE;
   if (nq > 65535) return LS_E_SIZE;
@@ -483,7 +488,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
     if (smem > set_f32) set_f32 = smem;
     LS_COUNT(LS_K_ATTENTION_TILE), ls_launch(attention_tile_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, (float*)out, part_acc, part_ml, work, block_table,
-        table_stride, nq, nkv, d, page_size, num_pages, window, scale, err);
+        table_stride, nq, nkv, d, page_size, num_pages, window, scale, slopes, err);
   } else if (dtype == LS_BF16) {
     e = smem <= set_bf16 ? cudaSuccess
                          : cudaFuncSetAttribute(attention_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -492,7 +497,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
     LS_COUNT(LS_K_ATTENTION_TILE), ls_launch(attention_tile_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, part_acc,
         part_ml, work, block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale,
-        err);
+        slopes, err);
   } else {
     return LS_E_DTYPE;
   }
@@ -505,8 +510,8 @@ namespace {
 int launch_attention_decode(const void* q, const void* pages, float* part_acc, float* part_ml,
                             int dtype, const int* work, int n_work, const int* block_table,
                             int table_stride, int nq, int nkv, int d, int page_size,
-                            int num_pages, int window, float scale, int slot_limit, int* err,
-                            cudaStream_t stream) {
+                            int num_pages, int window, float scale, const float* slopes, int slot_limit,
+                            int* err, cudaStream_t stream) {
   if (n_work <= 0) return 0;
   if (!shape_ok(nq, nkv, d, page_size, DEC_TILE)) return LS_E_SIZE;
   const int group = nq / nkv;
@@ -522,7 +527,7 @@ int launch_attention_decode(const void* q, const void* pages, float* part_acc, f
     if (smem > set_f32) set_f32 = smem;
     LS_COUNT(LS_K_ATTENTION_DECODE), ls_launch(attention_decode_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, part_acc, part_ml, work, block_table, table_stride,
-        nq, nkv, d, page_size, num_pages, window, scale, slot_limit, err);
+        nq, nkv, d, page_size, num_pages, window, scale, slopes, slot_limit, err);
   } else if (dtype == LS_BF16) {
     const size_t smem = decode_smem_bytes(d, group, 2);
     e = smem <= set_bf16 ? cudaSuccess
@@ -531,7 +536,7 @@ int launch_attention_decode(const void* q, const void* pages, float* part_acc, f
     if (smem > set_bf16) set_bf16 = smem;
     LS_COUNT(LS_K_ATTENTION_DECODE), ls_launch(attention_decode_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, part_acc, part_ml, work,
-        block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, slot_limit, err);
+        block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale, slopes, slot_limit, err);
   } else {
     return LS_E_DTYPE;
   }
@@ -561,10 +566,10 @@ int launch_attention_combine(const float* part_acc, const float* part_ml, void* 
 LS_API int ls_attention_decode(const void* q, const void* pages, float* part_acc, float* part_ml,
                                int dtype, const int* work, int n_work, const int* block_table,
                                int table_stride, int nq, int nkv, int d, int page_size,
-                               int num_pages, int window, float scale, int* err,
+                               int num_pages, int window, float scale, const float* slopes, int* err,
                                cudaStream_t stream) {
   return launch_attention_decode(q, pages, part_acc, part_ml, dtype, work, n_work, block_table, table_stride, nq,
-                                 nkv, d, page_size, num_pages, window, scale, 0, err, stream);
+                                 nkv, d, page_size, num_pages, window, scale, slopes, 0, err, stream);
 }
 
 LS_API int ls_attention_combine(const float* part_acc, const float* part_ml, void* out, int dtype,
@@ -627,7 +632,7 @@ LS_API int ls_attention_decode_noalloc(const void* q, const void* pages, void* o
   // in the error word (LS_DEV_ROW_RANGE) and skipped, it cannot write outside the array
   const int status = launch_attention_decode(q, pages, part_acc, part_ml, dtype, work, n_work,
                                              block_table, table_stride, nq, nkv, d, page_size,
-                                             num_pages, window, scale, n_slots, err, stream);
+                                             num_pages, window, scale, nullptr, n_slots, err, stream);
   if (status != 0) return status;
   return launch_attention_combine(part_acc, part_ml, out, dtype, combine, n_combine, nq, d, n_slots, err, stream);
 }

@@ -309,8 +309,8 @@ LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int 
                                  const int* positions, const int* token_req,
                                  const int* block_table, int table_stride, int tokens, int nq,
                                  int nkv, int d, int rot_dim, int page_size, int num_pages,
-                                 int max_positions, float eps, int write_cache, int* err,
-                                 cudaStream_t stream) {
+                                 int max_positions, float eps, int write_cache, int interleaved,
+                                 int* err, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return LS_E_SIZE;
   const int heads = nq + 2 * nkv;
@@ -353,8 +353,9 @@ LS_API int ls_qk_norm_rope_store(const void* qkv, void* q_out, void* pages, int 
   args.max_positions = max_positions;
   args.write_cache = write_cache;
   args.eps = eps;
-  // whole heads of 64 or 128 bfloat16, rows and targets on 16-byte boundaries: the short kernel
-  const bool whole = dtype == LS_BF16 && (d == 64 || d == 128) && rot_dim == d && (q_gain == nullptr) == (k_gain == nullptr) &&
+  args.interleaved = interleaved ? 1 : 0;
+  // whole heads of 64 or 128 bfloat16 in the half layout, rows and targets on 16-byte boundaries: the short kernel
+  const bool whole = dtype == LS_BF16 && (d == 64 || d == 128) && rot_dim == d && !interleaved && (q_gain == nullptr) == (k_gain == nullptr) &&
                      (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pages) & 15) == 0 && smem <= 48 * 1024;
   if (whole) {
     if (d == 64)

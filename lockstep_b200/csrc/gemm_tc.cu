@@ -1926,6 +1926,7 @@ LS_API int ls_gemm_nt_tc_qkv_heads(const void* X, int64_t ldx, const float* h, c
   heads.max_positions = max_positions;
   heads.write_cache = write_cache;
   heads.eps = head_eps;
+  heads.interleaved = 0;     // the caller takes rotations of neighbouring pairs to the kernel of their own
   const int N = (nq + 2 * nkv) * d;
   if (h == nullptr) return run(X, nullptr, &heads, W, nullptr, LS_BF16, T, N, K, ldx, ldw, 0, 3, err, stream);
   if (gain_dtype != LS_F32 && gain_dtype != LS_BF16) return LS_E_DTYPE;

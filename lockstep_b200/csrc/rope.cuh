@@ -1,7 +1,9 @@
 // Per-head RMSNorm (optional) and rotary position encoding of one head by one
 // warp, shared by every kernel that does it, so that all of them produce the
-// same bits.  Half rotation: out[i] = x[i] c_i - x[i+h] s_i, out[i+h] = x[i+h] c_i
-// + x[i] s_i for i < h = rot_dim / 2; dimensions past rot_dim are only normed.
+// same bits.  Pair i < h = rot_dim / 2 of a head is (x[i], x[i+h]) in the half layout and
+// (x[2i], x[2i+1]) in the interleaved one; with (lo, hi) the pair, out_lo = lo c_i - hi s_i
+// and out_hi = hi c_i + lo s_i, written back where they came from.  Dimensions past
+// rot_dim are only normed.
 // Products and sums are rounded one by one (no fused multiply-add), so the
 // result does not depend on how a compiler contracts the expression.
 #pragma once
@@ -12,7 +14,8 @@
 template <typename T, typename TG, typename Store>
 __device__ __forceinline__ void ls_norm_rope_head(const T* __restrict__ src, const TG* __restrict__ gain,
                                                   const float* __restrict__ cs, const float* __restrict__ sn,
-                                                  int d, int rot_dim, float eps, int lane, Store store) {
+                                                  int d, int rot_dim, float eps, int lane, Store store,
+                                                  bool interleaved = false) {
   float rstd = 1.f;
   if (gain != nullptr) {
     float ss = 0.f;
@@ -25,15 +28,16 @@ __device__ __forceinline__ void ls_norm_rope_head(const T* __restrict__ src, con
   }
   const int half = rot_dim >> 1;
   for (int i = lane; i < half; i += 32) {
-    float lo = __fmul_rn(ls_to_float<T>(src[i]), rstd);
-    float hi = __fmul_rn(ls_to_float<T>(src[i + half]), rstd);
+    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+    float lo = __fmul_rn(ls_to_float<T>(src[a]), rstd);
+    float hi = __fmul_rn(ls_to_float<T>(src[b]), rstd);
     if (gain != nullptr) {
-      lo = __fmul_rn(lo, ls_to_float<TG>(gain[i]));
-      hi = __fmul_rn(hi, ls_to_float<TG>(gain[i + half]));
+      lo = __fmul_rn(lo, ls_to_float<TG>(gain[a]));
+      hi = __fmul_rn(hi, ls_to_float<TG>(gain[b]));
     }
     const float c = cs[i], s = sn[i];
-    store(i, __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, s)));
-    store(i + half, __fadd_rn(__fmul_rn(hi, c), __fmul_rn(lo, s)));
+    store(a, __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, s)));
+    store(b, __fadd_rn(__fmul_rn(hi, c), __fmul_rn(lo, s)));
   }
   for (int i = rot_dim + lane; i < d; i += 32) {
     float v = __fmul_rn(ls_to_float<T>(src[i]), rstd);
@@ -59,6 +63,7 @@ struct LsQkvStore {
   int gain_bf16;            // element type of the gains: 1 bfloat16, 0 float32
   int table_stride, nq, nkv, d, rot_dim, page_size, num_pages, max_positions, write_cache;
   float eps;
+  int interleaved;          // 1: a rotated pair is two neighbouring elements; 0: halves of the rotated part
 };
 
 // Where head `head` (q heads, then k heads, then v heads) of token t goes.  It depends on the
@@ -119,7 +124,7 @@ __device__ __forceinline__ void ls_qkv_head_write_as(const LsQkvStore& a, const 
   const int half = a.rot_dim >> 1;
   ls_norm_rope_head<T, TG>(src, gain, a.cos_table + (int64_t)target.pos * half,
                            a.sin_table + (int64_t)target.pos * half, d, a.rot_dim, a.eps, lane,
-                           [&](int i, float v) { dst[i] = ls_from_float<T>(v); });
+                           [&](int i, float v) { dst[i] = ls_from_float<T>(v); }, a.interleaved != 0);
 }
 
 template <typename T>

@@ -49,7 +49,7 @@ _SIGNATURES = {
                        c_float, c_void_p, c_void_p],
         "ls_qk_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                   c_void_p, c_void_p],
         "ls_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "ls_gemm_nt_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -57,10 +57,10 @@ _SIGNATURES = {
         "ls_attention_split_size": [],
         "ls_attention_tile": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                               c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_float, c_void_p, c_void_p],
+                              c_float, c_void_p, c_void_p, c_void_p],
         "ls_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                c_void_p, c_void_p],
+                                c_void_p, c_void_p, c_void_p],
         "ls_attention_combine": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                  c_void_p],
         "ls_argmax": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -236,8 +236,10 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor, eps: float, 
 
 def qk_norm_rope_store(qkv, q_out, pages, q_gain, k_gain, cos, sin, positions, token_req,
                        block_table, nq: int, nkv: int, d: int, rot_dim: int, eps: float,
-                       write_cache: bool, err) -> None:
-    """pages: [num_pages, 2, nkv, page_size, d] of one cache layer (may be None if not written)."""
+                       write_cache: bool, err, interleaved: bool = False) -> None:
+    """pages: [num_pages, 2, nkv, page_size, d] of one cache layer (may be None if not written).
+    ``interleaved``: a rotated pair is elements (2i, 2i + 1) of the head instead of
+    (i, i + rot_dim / 2)."""
     tokens = qkv.shape[0]
     if qkv.shape[1] != (nq + 2 * nkv) * d or q_out.shape != (tokens, nq * d):
         raise KernelError("qk_norm_rope_store: shapes do not agree")
@@ -264,7 +266,8 @@ def qk_norm_rope_store(qkv, q_out, pages, q_gain, k_gain, cos, sin, positions, t
         _dev(positions, "positions", torch.int32), _dev(token_req, "token_req", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.shape[-1], tokens, nq, nkv, d,
         rot_dim, page_size, num_pages, cos.shape[0] if rot_dim else 0, float(eps),
-        1 if write_cache else 0, _dev(err, "err", torch.int32), _stream()), "qk_norm_rope_store")
+        1 if write_cache else 0, 1 if interleaved else 0, _dev(err, "err", torch.int32), _stream()),
+        "qk_norm_rope_store")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -287,25 +290,33 @@ def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
         _stream()), "gemm_nt_simt")
 
 
+def _slopes(slopes, nq: int) -> int:
+    if slopes is not None and slopes.numel() != nq:
+        raise KernelError(f"a score bias needs one slope per query head: {slopes.numel()} for {nq} heads")
+    return _opt(slopes, "slopes", torch.float32)
+
+
 def attention_tile(q, pages, out, part_acc, part_ml, work, n_work, block_table, nq, nkv, d,
-                   window, scale, err) -> None:
+                   window, scale, err, slopes=None) -> None:
+    """``slopes`` (float32 [nq] or None): slopes[head] x (key position - query position) is added
+    to every score."""
     _check(library().ls_attention_tile(
         _dev(q, "q"), _dev(pages, "pages", q.dtype), _opt(out, "out", q.dtype),
         _opt(part_acc, "part_acc", torch.float32), _opt(part_ml, "part_ml", torch.float32), _code(q),
         _dev(work, "work", torch.int32), n_work, _dev(block_table, "block_table", torch.int32),
         block_table.shape[-1], nq, nkv, d, pages.shape[3], pages.shape[0], int(window), float(scale),
-        _dev(err, "err", torch.int32), _stream()), "attention_tile")
+        _slopes(slopes, nq), _dev(err, "err", torch.int32), _stream()), "attention_tile")
 
 
 def attention_decode(q, pages, part_acc, part_ml, work, n_work, block_table, nq, nkv, d, window,
-                     scale, err) -> bool:
+                     scale, err, slopes=None) -> bool:
     """Returns False (and launches nothing) for shapes the decode kernel does not take."""
     status = library().ls_attention_decode(
         _dev(q, "q"), _dev(pages, "pages", q.dtype), _dev(part_acc, "part_acc", torch.float32),
         _dev(part_ml, "part_ml", torch.float32), _code(q), _dev(work, "work", torch.int32), n_work,
         _dev(block_table, "block_table", torch.int32), block_table.shape[-1], nq, nkv, d,
-        pages.shape[3], pages.shape[0], int(window), float(scale), _dev(err, "err", torch.int32),
-        _stream())
+        pages.shape[3], pages.shape[0], int(window), float(scale), _slopes(slopes, nq),
+        _dev(err, "err", torch.int32), _stream())
     if status == -2:
         return False
     _check(status, "attention_decode")

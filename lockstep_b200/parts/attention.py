@@ -32,7 +32,7 @@ class GQAttention(Mixer):
         self.scale, self.window = float(scale), int(window or 0)
         self.qk_norm_eps = qk_norm_eps
         self.position, self.rt = position, runtime
-        self.w_qkv = self.w_o = self.q_gain = self.k_gain = None
+        self.w_qkv = self.w_o = self.q_gain = self.k_gain = self.slopes = None
         # in float32 every row takes the tile kernel, so that a row's bits do not
         # depend on whether it was decoded or part of a prompt
         self.exact = runtime.dtype == torch.float32
@@ -59,6 +59,7 @@ class GQAttention(Mixer):
         self.w_qkv = torch.cat(
             [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0).contiguous()
         self.w_o = tensors["o_proj.weight"]
+        self.slopes = self.position.score_slopes(self.nq)      # asked once: a step allocates nothing for it
         if self.qk_norm_eps is not None:
             self.q_gain, self.k_gain = tensors["q_norm.weight"], tensors["k_norm.weight"]
 
@@ -70,10 +71,14 @@ class GQAttention(Mixer):
         cos, sin, rot_dim = rot if rot is not None else (None, None, 0)
         heads = (q, cache.pages, self.q_gain, self.k_gain, cos, sin, ctx.positions, ctx.token_slot,
                  cache.block_table, nq, nkv, d, rot_dim, self.qk_norm_eps or 0.0, cache.writes, self.rt.err)
+        interleaved = bool(rot_dim and self.position.rotary_interleaved)
+        # a bias on the scores is known to the CUDA-core attention kernels only
+        slopes = self.slopes
+        tensor_core_attention = not self.exact and slopes is None
         # few tokens: the product finishes its heads itself (norm, rotation, cache write); else
         # the projection goes through memory and a second kernel does that
         fused = False
-        if t <= K.FEW_TOKENS and not self.exact:
+        if t <= K.FEW_TOKENS and not self.exact and not interleaved:
             pending = isinstance(x, NormedRows) and x.pending()
             fused = K.gemm_nt_tc_qkv_heads(None if pending else (x.materialize() if isinstance(x, NormedRows) else x),
                                            self.w_qkv, *heads,
@@ -84,10 +89,10 @@ class GQAttention(Mixer):
                 x.linear(self.w_qkv, qkv, K.EPILOGUE_STORE, self.rt.err)
             else:
                 K.gemm_nt(x, self.w_qkv, qkv, err=self.rt.err)
-            K.qk_norm_rope_store(qkv, *heads)
+            K.qk_norm_rope_store(qkv, *heads, interleaved=interleaved)
         attn = self.rt.rows(t, nq * d)
         plan, done = None, False
-        if not self.exact and d in (64, 128):
+        if tensor_core_attention and d in (64, 128):
             plan = ctx.attention_plan(self.window, K.attention_prefill_tc_tile_tokens())
             done = not plan.n_tile or K.attention_prefill_tc(
                 q, cache.pages, attn, plan.tile_work, plan.n_tile, cache.block_table, nq, nkv, d,
@@ -96,23 +101,23 @@ class GQAttention(Mixer):
             plan = ctx.attention_plan(self.window)
             if plan.n_tile:
                 K.attention_tile(q, cache.pages, attn, None, None, plan.tile_work, plan.n_tile,
-                                 cache.block_table, nq, nkv, d, self.window, self.scale, self.rt.err)
+                                 cache.block_table, nq, nkv, d, self.window, self.scale, self.rt.err, slopes)
         if plan.n_split:
             part_acc = self.rt.rows(plan.n_slots, nq, d, dtype=torch.float32)
             part_ml = self.rt.rows(plan.n_slots, nq, 2, dtype=torch.float32)
             done = False
-            if not self.exact:
+            if tensor_core_attention:
                 done = K.attention_decode_mma(q, cache.pages, part_acc, part_ml, plan.split_work,
                                               plan.n_split, cache.block_table, nq, nkv, d, self.window,
                                               self.scale, self.rt.err)
             if not done and not self.exact:
                 done = K.attention_decode(q, cache.pages, part_acc, part_ml, plan.split_work,
                                           plan.n_split, cache.block_table, nq, nkv, d, self.window,
-                                          self.scale, self.rt.err)
+                                          self.scale, self.rt.err, slopes)
             if not done:
                 K.attention_tile(q, cache.pages, None, part_acc, part_ml, plan.split_work,
                                  plan.n_split, cache.block_table, nq, nkv, d, self.window,
-                                 self.scale, self.rt.err)
+                                 self.scale, self.rt.err, slopes)
             K.attention_combine(part_acc, part_ml, attn, plan.combine_items, plan.n_combine, nq, d)
         K.gemm_nt(attn, self.w_o, residual, K.EPILOGUE_RESIDUAL, err=self.rt.err)
 

@@ -124,9 +124,22 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    """How a mixer learns where its tokens are.  A position encoding may do any of three
+    things (an absolute table that is added to the embedding belongs to the embedding part,
+    which sees ``ctx.positions``):"""
+
+    # rotated pairs are elements (2i, 2i + 1) of a head instead of (i, i + rot_dim / 2)
+    rotary_interleaved = False
+
     def rotary(self):
         """(cos, sin, rot_dim) tables [max_positions, rot_dim/2] for a mixer that
         rotates its queries and keys, or None."""
+        return None
+
+    def score_slopes(self, num_heads: int):
+        """float32 [num_heads] on the device, or None: the score of a query at position p
+        with a key at position j gets slopes[head] x (j - p) added before the softmax (a
+        bias that grows with distance, in place of or beside a rotation)."""
         return None
 
 

@@ -172,7 +172,80 @@ def test_qk_norm_rope_store(dtype, nq, nkv, d, rot, page):
         assert torch.equal(got[p, 1, :, s, :], vv[i].to(dtype))
 
 
-def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel):
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rot,page", [(6, 3, 48, 48, 8), (4, 1, 32, 16, 16), (16, 8, 128, 128, 32), (3, 3, 128, 64, 8)])
+def test_qk_norm_rope_store_rotates_neighbouring_pairs(dtype, nq, nkv, d, rot, page):
+    """The interleaved layout: pair i of a head is elements (2i, 2i + 1)."""
+    k = K()
+    g = torch.Generator().manual_seed(d + 1)
+    t = 9
+    qkv = torch.randn(t, (nq + 2 * nkv) * d, generator=g).to(dtype)
+    qg = (1 + 0.1 * torch.randn(d, generator=g)).to(dtype)
+    kg = (1 + 0.1 * torch.randn(d, generator=g)).to(dtype)
+    positions = torch.tensor([3 + 5 * i for i in range(t)], dtype=torch.int32)
+    cos, sin = plain.rope_tables(range(64), rot, 10000.0, torch.float32)
+    table = torch.arange(8, dtype=torch.int32).flip(0).view(1, 8).contiguous()
+    pages = torch.zeros(8, 2, nkv, page, d, dtype=dtype, device=dev())
+    q_out = torch.empty(t, nq * d, dtype=dtype, device=dev())
+    err = k.new_error_word(dev())
+    k.qk_norm_rope_store(qkv.to(dev()), q_out, pages, qg.to(dev()), kg.to(dev()), cos.to(dev()).contiguous(),
+                         sin.to(dev()).contiguous(), positions.to(dev()), torch.zeros(t, dtype=torch.int32, device=dev()),
+                         table.to(dev()), nq, nkv, d, rot, 1e-6, True, err, interleaved=True)
+    k.raise_on_fault(err)
+    x = qkv.double()
+    c, s_ = cos.double()[positions.long()][:, None, :], sin.double()[positions.long()][:, None, :]
+
+    def norm_turn(z, gain):
+        z = plain.rms_norm(z, gain.double(), 1e-6)
+        lo, hi = z[..., 0:rot:2], z[..., 1:rot:2]
+        out = z.clone()
+        out[..., 0:rot:2] = lo * c - hi * s_
+        out[..., 1:rot:2] = hi * c + lo * s_
+        return out
+
+    want_q = norm_turn(x[:, :nq * d].view(t, nq, d), qg)
+    want_k = norm_turn(x[:, nq * d:(nq + nkv) * d].view(t, nkv, d), kg)
+    assert (q_out.cpu().double().view(t, nq, d) - want_q).abs().max() <= tol(dtype) * 4
+    got = pages.cpu()
+    for i in range(t):
+        pos = int(positions[i])
+        if pos // page >= 8:
+            continue
+        assert (got[int(table[0, pos // page]), 0, :, pos % page, :].double() - want_k[i]).abs().max() <= tol(dtype) * 4
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page", [(6, 3, 48, 8), (8, 2, 64, 16), (5, 1, 128, 32)])
+def test_attention_with_a_slope_per_head_on_the_distance(dtype, nq, nkv, d, page):
+    """score += slopes[head] x (key position - query position): a portion and single tokens."""
+    k = K()
+    g = torch.Generator().manual_seed(nq + d)
+    total = 600
+    q = torch.randn(total, nq, d, generator=g).to(dtype)
+    kk = torch.randn(total, nkv, d, generator=g).to(dtype)
+    vv = torch.randn(total, nkv, d, generator=g).to(dtype)
+    slopes = torch.tensor([0.02 * (h + 1) * (-1) ** h for h in range(nq)], dtype=torch.float32)   # some favour far keys
+    scale = 1 / math.sqrt(d)
+    pos = torch.arange(total, dtype=torch.float64)
+    distance = pos[None, :] - pos[:, None]
+    want = torch.empty(total, nq, d, dtype=torch.float64)
+    for h in range(nq):
+        sc = q[:, h].double() @ kk[:, h // (nq // nkv)].double().T * scale + slopes[h].double() * distance
+        sc = sc.masked_fill(distance > 0, float("-inf"))
+        want[:, h] = torch.softmax(sc, dim=-1) @ vv[:, h // (nq // nkv)].double()
+    want = want.float()
+    pages, ids = paged_from_dense(kk, vv, page, 128, seed=6)
+    bound = 2e-5 if dtype == torch.float32 else 2e-2
+    got = run_attention(k, q[450:], pages, ids, 450, 0, scale, False, slopes=slopes)
+    assert (got - want[450:]).abs().max() <= bound
+    for p in [0, 1, 255, 256, 511, 512, 599]:
+        for decode_kernel in (False, True):
+            got = run_attention(k, q[p:p + 1], pages, ids, p, 0, scale, decode_kernel, slopes=slopes)
+            assert (got[0] - want[p]).abs().max() <= bound, (p, decode_kernel)
+    assert (want[599] - plain.causal_attention(q.double(), kk.double(), vv.double(), scale).float()[599]).abs().max() > 0.05
+
+
+def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel, slopes=None):
     """q [n, nq, d] at positions start..; returns out [n, nq, d] (float32, cpu)."""
     from lockstep_b200.engine.batch import plan_attention
 
@@ -186,6 +259,7 @@ def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel):
     tile, sp, comb, n_slots = plan_attention([(1, 0, start, n)], window, split, tile_tokens)
     D = dev()
     err = k.new_error_word(D)
+    slopes = None if slopes is None else slopes.to(D)
     qd, pd, td = q.reshape(n, nq * d).contiguous().to(D), pages.to(D), table.to(D)
     out = torch.empty(n, nq * d, dtype=q.dtype, device=D)
     if len(tile) and prefill_tc:
@@ -193,7 +267,7 @@ def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel):
                                       window, scale, err)
     elif len(tile):
         k.attention_tile(qd, pd, out, None, None, torch.from_numpy(tile).to(D), len(tile), td, nq, nkv, d,
-                         window, scale, err)
+                         window, scale, err, slopes)
     if len(sp):
         acc = torch.empty(n_slots, nq, d, dtype=torch.float32, device=D)
         ml = torch.empty(n_slots, nq, 2, dtype=torch.float32, device=D)
@@ -203,10 +277,10 @@ def run_attention(k, q, pages, table_row, start, window, scale, decode_kernel):
             done = k.attention_decode_mma(qd, pd, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err)
             assert done
         elif decode_kernel and not prefill_tc:
-            done = k.attention_decode(qd, pd, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err)
+            done = k.attention_decode(qd, pd, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err, slopes)
             assert done
         if not done:
-            k.attention_tile(qd, pd, None, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err)
+            k.attention_tile(qd, pd, None, acc, ml, w, len(sp), td, nq, nkv, d, window, scale, err, slopes)
         k.attention_combine(acc, ml, out, torch.from_numpy(comb).to(D), len(comb), nq, d)
     k.raise_on_fault(err)
     return out.cpu().float().view(n, nq, d)
