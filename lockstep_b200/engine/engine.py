@@ -88,6 +88,10 @@ class Engine:
         return self.runner.step(entries, check=False, static_logits=True, tokens_device=pending["tokens"])
 
     # -- generation -------------------------------------------------------------
+    def weight_cast_report(self) -> dict:
+        """What the cast of the model folder's tensors to the engine's element types cost."""
+        return self.runner.weight_cast_report()
+
     def submit(self, request: Request) -> None:
         self.scheduler.submit(request)
 

@@ -55,8 +55,9 @@ class ModelRunner:
         self.rt = Runtime(device=self.device, dtype=self.dtype, page_size=self.page_size,
                           max_positions=self.max_seq_len, err=self.err)
         self.model = Model(self.spec, self.rt)
+        self._cast_report: dict = {}
         tensors = load_weights(Path(model_dir), self.model.weight_specs(), self.dtype, self.device,
-                               aliases=self.model.aliases())
+                               aliases=self.model.aliases(), report=self._cast_report)
         self.model.bind(tensors)
         self.cache = CacheManager(self.model.cache_needs(), num_pages=num_pages, page_size=page_size,
                                   max_live=max_live, max_seq_len=self.max_seq_len, dtype=self.dtype,
@@ -74,6 +75,12 @@ class ModelRunner:
             from .graphs import DecodeGraphs
 
             self.graphs = DecodeGraphs(self)
+
+    def weight_cast_report(self) -> dict:
+        """What reading the model folder's tensors into the engine's element types cost: elements
+        by stored and by kept type, how many changed in the cast, the largest absolute and
+        relative error (LockStep: engine/model/qwen3.py:205-220)."""
+        return dict(self._cast_report)
 
     # -- requests -----------------------------------------------------------
     def open(self, uid: str) -> int:

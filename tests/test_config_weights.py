@@ -117,6 +117,38 @@ def test_loader_keeps_dtypes_as_stored(tmp_path):
     assert torch.equal(wide["model.embed_tokens.weight"], tensors["model.embed_tokens.weight"].float())
 
 
+def test_cast_report_measures_what_the_rounding_cost(tmp_path):
+    """A float32 folder read by the bfloat16 engine: the report counts the elements that changed
+    and the largest errors; read by the float32 engine, or stored in bfloat16, nothing changes."""
+    from lockstep_b200.engine.model import Model
+    from lockstep_b200.parts import Runtime
+
+    folder = write_random_model(tmp_path / "m", H.TINY_A, seed=3, dtype="float32")
+    spec = config_from_dict(H.TINY_A).model_spec()
+    model = Model(spec, Runtime(torch.device("cpu"), torch.float32, 16, 8, torch.zeros(2, dtype=torch.int32)))
+    tensors = read_tensors(folder)
+    tensors["model.layers.0.mlp.down_proj.weight"][0, 0] = 1.0 + 2.0 ** -9      # needs 9 bits: rounds to 1.0
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()      # the tied head stored as well
+    save_file(tensors, str(folder / "model.safetensors"))
+    expected = model.weight_specs()
+    report: dict = {}
+    got = load_weights(folder, expected, torch.bfloat16, "cpu", aliases=model.aliases(), report=report)
+    total = sum(t.numel() for n, t in tensors.items() if n != "lm_head.weight")
+    assert report["distinct_elements"] == total and report["stored_elements_by_dtype"] == {"torch.float32": total}
+    gains = sum(t.numel() for n, t in tensors.items() if n.endswith("norm.weight"))
+    assert report["kept_elements_by_dtype"] == {"torch.bfloat16": total - gains, "torch.float32": gains}
+    assert report["tied_names_dropped"] == ["lm_head.weight"]
+    assert report["duplicate_elements_dropped"] == tensors["lm_head.weight"].numel()
+    changed = sum(int((t != t.bfloat16().float()).sum()) for n, t in tensors.items()
+                  if n != "lm_head.weight" and not n.endswith("norm.weight"))
+    assert report["elements_not_exactly_representable"] == changed > 0
+    assert 2.0 ** -9 <= report["max_abs_error"] < 2.0 ** -6 and 2.0 ** -10 < report["max_rel_error"] <= 2.0 ** -8
+    assert got["model.layers.0.mlp.down_proj.weight"][0, 0] == 1.0
+    exact: dict = {}
+    load_weights(folder, expected, torch.float32, "cpu", aliases=model.aliases(), report=exact)
+    assert exact["elements_not_exactly_representable"] == 0 and exact["max_abs_error"] == 0.0
+
+
 def test_tied_head_stored_twice_must_agree(tmp_path):
     from lockstep_b200.engine.model import Model
     from lockstep_b200.parts import Runtime
