@@ -42,7 +42,12 @@ __device__ __forceinline__ const T* page_ptr(const T* pages, const int* table_ro
 }
 
 // --------------------------------------------------------------------------
-// tile kernel: up to 16 query tokens of one request, one query head
+// tile kernel: up to 16 rows: query tokens of one request x query heads of one key head.
+// A block has `hb` heads (a divisor of the group size): row m is token m / hb and head
+// blockIdx.y * hb + m % hb, so that a single decoded token fills the tile's rows with the heads
+// that share its keys and values, which are then loaded once for all of them.  An item with more
+// tokens than fit beside `hb` heads takes its heads one after the other.  A row's arithmetic
+// does not depend on what the other rows of its tile are.
 // --------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128, 4)
@@ -50,7 +55,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
                       float* __restrict__ part_acc, float* __restrict__ part_ml,
                       const int* __restrict__ work, const int* __restrict__ block_table,
                       int table_stride, int nq, int nkv, int d, int page_size, int num_pages,
-                      int window, float scale, const float* __restrict__ slopes, int* err) {
+                      int window, float scale, const float* __restrict__ slopes, int hb, int* err) {
   ls_dependency_sync();
   extern __shared__ __align__(16) float smem[];
   // rows of Q and K are d + 4 floats apart: 16-byte pieces stay aligned, and the eight key rows a
@@ -66,13 +71,11 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
   const int req_row = w[0], tok0 = w[1], ntok = w[2], pos0 = w[3];
   if (ntok == 0) return;                     // padding item of a recorded launch
   const int split_begin = w[4], split_end = w[5], slot_base = w[6];
-  const int h = blockIdx.y;
-  const int kvh = h / (nq / nkv);
-  // slopes (or null): a score gets slopes[head] x (key position - query position) added,
-  // a position encoding that biases the scores instead of rotating queries and keys
-  const float slope = slopes != nullptr ? slopes[h] : 0.f;
+  const int kvh = ((int)blockIdx.y * hb) / (nq / nkv);
+  const int heads_at_once = ntok * hb <= TILE_M ? hb : 1;      // heads that share the tile's rows
   const int tid = threadIdx.x;
   const int m = tid >> 3, sub = tid & 7;
+  const int m_tok = m / heads_at_once;                         // this row's token of the item
   // Outputs of a thread: dimensions sub * 4 + e + 32 * jj (e < 4) that lie below d.  Which thread
   // holds which key's score or which output changes no sum: a score is one chain over the head's
   // elements in ascending order, an output one chain over the tile's keys in ascending order, the
@@ -85,13 +88,22 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
 
   const int pos_last = pos0 + ntok - 1;
   const int key_lo_tile = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-  const int qpos = pos0 + m;
-  const bool row_valid = m < ntok;
+  const int qpos = pos0 + m_tok;
+  const bool row_valid = m < ntok * heads_at_once;
   const int row_lo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
 
+  for (int h_first = (int)blockIdx.y * hb; h_first < ((int)blockIdx.y + 1) * hb; h_first += heads_at_once) {
+  const int h = h_first + m - m_tok * heads_at_once;           // this row's head
+  // slopes (or null): a score gets slopes[head] x (key position - query position) added,
+  // a position encoding that biases the scores instead of rotating queries and keys
+  const float slope = slopes != nullptr && row_valid ? slopes[h] : 0.f;
+  __syncthreads();                                             // the heads before are done with Q
   for (int i = tid; i < TILE_M * d; i += 128) {
     const int r = i / d, c = i - r * d;
-    Qs[r * dp + c] = r < ntok ? ls_to_float<T>(q[((int64_t)(tok0 + r) * nq + h) * d + c]) : 0.f;
+    const int r_tok = r / heads_at_once;
+    Qs[r * dp + c] = r < ntok * heads_at_once
+                         ? ls_to_float<T>(q[((int64_t)(tok0 + r_tok) * nq + h_first + r - r_tok * heads_at_once) * d + c])
+                         : 0.f;
   }
 
   float acc_run[MAX_D / 8], acc_s[MAX_D / 8];
@@ -241,7 +253,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
     if (slot_base >= 0) {
       // parallel mode: this block covers one split; write the partial
       if (row_valid) {
-        const int64_t slot = (int64_t)slot_base + m;
+        const int64_t slot = (int64_t)slot_base + m_tok;
 #pragma unroll
         for (int jj = 0; jj < MAX_D / 32; ++jj)
           if (jj < ngroup && sub * 4 + 32 * jj < d)
@@ -265,7 +277,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
   }
 
   if (slot_base < 0 && row_valid) {
-    T* o = out + ((int64_t)(tok0 + m) * nq + h) * d;
+    T* o = out + ((int64_t)(tok0 + m_tok) * nq + h) * d;
 #pragma unroll
     for (int jj = 0; jj < MAX_D / 32; ++jj)
       if (jj < ngroup && sub * 4 + 32 * jj < d) {
@@ -274,6 +286,7 @@ attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ pages, T* _
           o[sub * 4 + 32 * jj + e] = ls_from_float<T>(l_run > 0.f ? __fdiv_rn(acc_run[jj * 4 + e], l_run) : 0.f);
       }
   }
+  }   // heads of this block
 }
 
 // --------------------------------------------------------------------------
@@ -478,7 +491,13 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
   if (nq > 65535) return LS_E_SIZE;
   if ((uintptr_t)pages & 15) return LS_E_ALIGN;      // keys and values are read 16 bytes at a time
   const size_t smem = tile_smem_bytes(d);
-  dim3 grid(n_work, nq);
+  // split partials (decoded tokens: one row an item): the heads of a key head share a block,
+  // as many of them as divide the group and fit the tile's rows
+  int hb = 1;
+  if (part_acc != nullptr)
+    for (int c = 2; c <= TILE_M && c <= nq / nkv; ++c)
+      if ((nq / nkv) % c == 0) hb = c;
+  dim3 grid(n_work, nq / hb);
   cudaError_t e;
   static size_t set_f32 = 0, set_bf16 = 0;     // largest size configured so far
   if (dtype == LS_F32) {
@@ -488,7 +507,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
     if (smem > set_f32) set_f32 = smem;
     LS_COUNT(LS_K_ATTENTION_TILE), ls_launch(attention_tile_kernel<float>, grid, 128, smem, stream, 
         (const float*)q, (const float*)pages, (float*)out, part_acc, part_ml, work, block_table,
-        table_stride, nq, nkv, d, page_size, num_pages, window, scale, slopes, err);
+        table_stride, nq, nkv, d, page_size, num_pages, window, scale, slopes, hb, err);
   } else if (dtype == LS_BF16) {
     e = smem <= set_bf16 ? cudaSuccess
                          : cudaFuncSetAttribute(attention_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -497,7 +516,7 @@ LS_API int ls_attention_tile(const void* q, const void* pages, void* out, float*
     LS_COUNT(LS_K_ATTENTION_TILE), ls_launch(attention_tile_kernel<__nv_bfloat16>, grid, 128, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, part_acc,
         part_ml, work, block_table, table_stride, nq, nkv, d, page_size, num_pages, window, scale,
-        slopes, err);
+        slopes, hb, err);
   } else {
     return LS_E_DTYPE;
   }
