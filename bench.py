@@ -248,7 +248,7 @@ def time_e2e(engine, batch, context, steps, warmup, repeats=REPEATS):
     # lists: the recorded step's whole input), sampled ids and the error word out
     graphs = engine.runner.graphs
     if graphs is not None and graphs.graphs:
-        h2d = max(ctx.size for _, ctx, _, _ in graphs.graphs.values()) * 4
+        h2d = graphs.input_bytes()
     else:
         h2d = batch * 4 * 4 + batch * (context // 256 + 1) * 8 * 4 + batch * 16
     return rates, h2d, batch * 4 + 8

@@ -168,6 +168,10 @@ class DecodeGraphs:
     def ready(self, key) -> bool:
         return key in self.graphs
 
+    def input_bytes(self) -> int:
+        """Bytes that go from the host to the device before a replay of the largest recorded step."""
+        return 4 * max((entry[1].size for entry in self.graphs.values()), default=0)
+
     def record(self, key) -> None:
         """Record the model's forward for ``key`` (nothing runs while recording).
 
