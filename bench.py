@@ -65,6 +65,7 @@ SIZES = {
 }
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+LONG_PREFILL_TOKENS = 8192      # an extra point: a prompt four times the headline's
 PAGE = 16
 REPEATS = 5
 SETTLE = 24            # untimed decode steps before the warm-up steps of every timed decode region
@@ -335,7 +336,8 @@ def run_ours(args):
     pk = peaks()
     batches = sorted({args.batch, 1, 64} if not args.quick else {args.batch})
     max_batch = max(batches)
-    engine = build_engine(cfg, args.dtype if args.only else "bfloat16", max_batch, CONTEXT)
+    engine = build_engine(cfg, args.dtype if args.only else "bfloat16", max_batch,
+                          max(CONTEXT, args.prefill_tokens + 64) if args.only == "prefill" else CONTEXT)
     runner = engine.runner
     launches = [0]
     if args.only == "decode":
@@ -344,8 +346,8 @@ def run_ours(args):
                           "context": args.context, "ms_per_step": round(ms, 4), "launches": launches[0]}))
         return 0
     if args.only == "prefill":
-        pre = time_prefill(runner, PREFILL_TOKENS, repeats=max(1, args.steps))
-        print(json.dumps({"only": "prefill", "dtype": args.dtype, "layers": layers, "tokens": PREFILL_TOKENS,
+        pre = time_prefill(runner, args.prefill_tokens, repeats=max(1, args.steps))
+        print(json.dumps({"only": "prefill", "dtype": args.dtype, "layers": layers, "tokens": args.prefill_tokens,
                           "ms": round(statistics.median(pre), 3)}))
         return 0
 
@@ -384,10 +386,22 @@ def run_ours(args):
     bytes_step = step_bytes(cfg, layers, args.batch, CONTEXT - args.steps / 2)
     achieved = bytes_step / (ms * 1e-3) / 1e9
 
+    if not args.quick:
+        # a longer prompt in one step: attention is most of its work
+        engine = runner = None
+        torch.cuda.empty_cache()
+        engine_long = build_engine(cfg, "bfloat16", 1, LONG_PREFILL_TOKENS + 64)
+        pre_long = statistics.median(time_prefill(engine_long.runner, LONG_PREFILL_TOKENS, repeats=3))
+        points[f"prefill_{LONG_PREFILL_TOKENS}"] = round(LONG_PREFILL_TOKENS / pre_long * 1e3, 1)
+        point_frac[f"prefill_{LONG_PREFILL_TOKENS}"] = round(
+            prefill_flops(cfg, layers, LONG_PREFILL_TOKENS) / (pre_long * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+        del engine_long
+        torch.cuda.empty_cache()
+
     fp32 = None
     if not args.quick and not args.no_fp32:
         # the true 32-bit path (FFMA products): decode at the headline's batch and context, and the prefill
-        del engine, runner
+        engine = runner = None
         torch.cuda.empty_cache()
         engine32 = build_engine(cfg, "float32", args.batch, CONTEXT)
         ms32 = time_decode(engine32.runner, engine32.sampler, args.batch, CONTEXT, max(4, min(args.steps, 12)),
@@ -647,6 +661,8 @@ def main():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
                     help="element type of the --only runs (the full line always reports both)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length of the decode steps (--only decode)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="tokens of the prompt that --only prefill runs in one step")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this engine")

@@ -543,6 +543,450 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Two query heads of one key head in a block (group sizes that are even).  The two heads'
+// tiles Q_A and Q_B (the same 128 tokens) share every key and value tile, which is loaded
+// once, and each has a team of eight softmax warps (two threads a row, 64 keys each, read
+// from tensor memory in pieces of 32).  Tensor memory: S_A, S_B, O_A, O_B, 128 columns each;
+// P (bfloat16, two keys a column) is written over the S it came from, keys 0..63 into the
+// first 32 columns and keys 64..127 into columns 64..95, so that a thread only writes over
+// scores it has already taken.  The MMAs of one team run while the other team's softmax
+// does: S_A, S_B | PV_A, S_A', PV_B, S_B' | ... in this order on the tensor pipe, which
+// executes them as issued, so PV_X has read P_X before the next S_X overwrites it.
+// A row's arithmetic is that of the kernel above with two threads a row; it depends on the
+// row's own position only.
+// ---------------------------------------------------------------------------
+constexpr int PAIR_THREADS = 19 * 32;
+constexpr int PAIR_V_WARP = 18;
+
+template <int HALVES>
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                                 __nv_bfloat16* __restrict__ out, const int* __restrict__ work, int n_work,
+                                 const int* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size,
+                                 int num_pages, int window, float scale_log2, int* err) {
+  ls_dependency_trigger();
+  constexpr int D = HALVES * 64;
+  constexpr int KV_BYTES = HALVES * HALF_BYTES;          // K (or V) of one tile; also one head's Q
+  constexpr uint32_t S_COL = 0, O_COL = 2 * BLOCK_N;     // S_X at S_COL + 128 X, O_X at O_COL + 128 X
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base;                          // [2 heads]
+  const uint32_t k_smem = q_smem + 2 * KV_BYTES;         // [STAGES]
+  const uint32_t v_smem = k_smem + STAGES * KV_BYTES;    // [STAGES]
+  const uint32_t bars_smem = v_smem + STAGES * KV_BYTES;
+  uint8_t* v_ptr = aligned + (v_smem - base);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (bars_smem - base));
+  uint64_t* q_full = bars;             // both heads' Q of an item landed
+  uint64_t* k_full = bars + 1;         // [2] keys of a tile landed
+  uint64_t* v_full = bars + 3;         // [2] values landed
+  uint64_t* k_free = bars + 5;         // [2] both S products have read the stage
+  uint64_t* v_free = bars + 7;         // [2] both PV products have read the stage
+  uint64_t* s_full = bars + 9;         // [2 teams] S of a tile is in tensor memory
+  uint64_t* p_full = bars + 11;        // [2 teams] P of a tile is in tensor memory
+  uint64_t* o_full = bars + 13;        // [2 teams] PV of a tile has been added to O
+  uint64_t* q_free = bars + 15;        // the item's last S product has read Q
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile uint32_t* failed = tmem_slot + 1;
+  float* team_mem = reinterpret_cast<float*>(bars + 32);   // per team: maxima [2][2][128], then sums [4][128]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pairs = nq >> 1;
+  const int total_items = n_work * pairs;
+  const int blocks = (int)gridDim.x;
+
+  // the item of this block in round `round`: 0 none is left, 1 an item, 2 a padding item (nothing to do);
+  // I.h is the first head of the pair
+  auto get_item = [&](int round, Item& I) -> int {
+    const int idx = round * blocks + ((round & 1) ? blocks - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    if (idx >= total_items) return 0;
+    const int wi = idx / pairs;
+    I.h = 2 * (idx - wi * pairs);
+    const int* w = work + (int64_t)wi * 8;
+    I.tok0 = w[1];
+    I.ntok = w[2];
+    I.pos0 = w[3];
+    if (I.ntok == 0) return 2;
+    I.table_row = block_table + (int64_t)w[0] * table_stride;
+    I.kvh = I.h / (nq / nkv);
+    I.pos_last = I.pos0 + I.ntok - 1;
+    I.key_lo = (window > 0 && I.pos0 - window + 1 > 0) ? I.pos0 - window + 1 : 0;
+    I.tile_first = I.key_lo / BLOCK_N;
+    I.n_tiles = I.pos_last / BLOCK_N + 1 - I.tile_first;
+    return 1;
+  };
+
+  const int rows_per_box = page_size < BLOCK_N ? page_size : BLOCK_N;
+  const int boxes = BLOCK_N / rows_per_box;
+  auto lookup = [&](const Item& I, int it) {
+    int page = 0;
+    if (it < I.n_tiles && lane < boxes) {
+      int key = (I.tile_first + it) * BLOCK_N + lane * rows_per_box;
+      if (key > I.pos_last) key = I.pos_last;
+      if (key < I.key_lo) key = I.key_lo;
+      page = I.table_row[key / page_size];
+    }
+    return page;
+  };
+  Item first_item;
+  int first_page = 0;
+  const bool producer = warp == 0 || warp == PAIR_V_WARP;
+  if (producer && get_item(0, first_item) == 1) first_page = lookup(first_item, 0);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(q_free, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&k_free[s], 1);
+      mbar_init(&v_free[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 8);
+      mbar_init(&o_full[s], 1);
+    }
+    *failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kv) : "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  ls_dependency_wait();
+
+  if (producer) {
+    // ---- producers: warp 0 fetches both heads' Q and the key tiles, warp PAIR_V_WARP the value tiles ----
+    const bool keys = warp == 0;
+    uint64_t* free_bar = keys ? k_free : v_free;
+    uint64_t* full_bar = keys ? k_full : v_full;
+    const uint32_t dst_base = keys ? k_smem : v_smem;
+    int gt = 0, j = 0;
+    bool ok = true;
+    for (int round = 0; ok; ++round) {
+      Item I;
+      const int kind = get_item(round, I);
+      if (kind == 0) break;
+      if (kind == 2) continue;
+      int page = round == 0 ? first_page : lookup(I, 0);
+      if (keys && lane == 0) {
+        if (j > 0 && (*failed || !mbar_wait(q_free, (uint32_t)(j - 1) & 1u))) {
+          *failed = 1;
+          ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 910);
+        } else {
+          mbar_expect_tx(q_full, 2 * KV_BYTES);
+#pragma unroll
+          for (int x = 0; x < 2; ++x)
+#pragma unroll
+            for (int hh = 0; hh < HALVES; ++hh)
+              tma_load_2d(q_smem + x * KV_BYTES + hh * HALF_BYTES, &map_q, (I.h + x) * D + hh * 64, I.tok0, q_full);
+        }
+      }
+      for (int it = 0; it < I.n_tiles; ++it) {
+        const int g = gt + it;
+        const int s = g & 1;
+        const uint32_t phase = (uint32_t)(g >> 1) & 1u;
+        const int c0 = (I.tile_first + it) * BLOCK_N;
+        ok = *failed == 0 && mbar_wait(&free_bar[s], phase ^ 1u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          *failed = 1;
+          if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 900 + s);
+          break;
+        }
+        if (lane == 0) mbar_expect_tx(&full_bar[s], KV_BYTES);
+        __syncwarp();
+        if (lane < boxes) {
+          if (page < 0 || page >= num_pages) {
+            ls_record_fault(err, LS_DEV_PAGE_RANGE, c0 + lane * rows_per_box);
+            page = 0;
+          }
+          const int in_page = ((c0 + lane * rows_per_box) % page_size) / rows_per_box * rows_per_box;
+          const int y = ((page * 2 + (keys ? 0 : 1)) * nkv + I.kvh) * page_size + in_page;
+#pragma unroll
+          for (int hh = 0; hh < HALVES; ++hh)
+            tma_load_2d(dst_base + (uint32_t)(s * KV_BYTES + hh * HALF_BYTES + lane * rows_per_box * 128), &map_kv,
+                        hh * 64, y, &full_bar[s]);
+        }
+        page = lookup(I, it + 1);
+      }
+      gt += I.n_tiles;
+      ++j;
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue (the whole warp walks the loop, one elected lane issues) ----
+    constexpr uint32_t idesc_s = instr_desc(BLOCK_M, BLOCK_N, false);
+    constexpr uint32_t idesc_o = instr_desc(BLOCK_M, D, true);
+    const bool issuer = elect_one();
+    int gt = 0, j = 0;
+    bool ok = true;
+    for (int round = 0; ok; ++round) {
+      Item I;
+      const int kind = get_item(round, I);
+      if (kind == 0) break;
+      if (kind == 2) continue;
+      ok = __all_sync(0xffffffffu, mbar_wait(q_full, (uint32_t)j & 1u));
+      // S_x(it) = Q_x K(it)^T; the keys are waited for by the first head's product
+      auto issue_s = [&](int x, int it) {
+        const int g = gt + it;
+        const int s = g & 1;
+        if (x == 0) {
+          if (!__all_sync(0xffffffffu, mbar_wait(&k_full[s], (uint32_t)(g >> 1) & 1u))) return false;
+          fence_after_sync();
+        }
+        if (issuer) {
+#pragma unroll
+          for (int k = 0; k < D / UMMA_K; ++k) {
+            const uint32_t koff = (uint32_t)((k >> 2) * HALF_BYTES + (k & 3) * UMMA_K * 2);
+            umma(tmem_base + S_COL + x * BLOCK_N, desc_k_major(q_smem + x * KV_BYTES + koff),
+                 desc_k_major(k_smem + s * KV_BYTES + koff), idesc_s, k != 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[x]);
+          if (x == 1) {
+            umma_commit(&k_free[s]);
+            if (it == I.n_tiles - 1) umma_commit(q_free);
+          }
+        }
+        __syncwarp();
+        return true;
+      };
+      // O_x += P_x(it) V(it); the values are waited for by the first head's product
+      auto issue_pv = [&](int x, int it) {
+        const int g = gt + it;
+        const int s = g & 1;
+        bool got = mbar_wait(&p_full[x], (uint32_t)g & 1u);
+        if (x == 0) got = got && mbar_wait(&v_full[s], (uint32_t)(g >> 1) & 1u);
+        if (!__all_sync(0xffffffffu, got)) return false;
+        fence_after_sync();
+        if (issuer) {
+#pragma unroll
+          for (int k = 0; k < BLOCK_N / UMMA_K; ++k) {
+            // 16 keys are 8 columns of P: keys 0..63 at columns 0..31 of S_x, keys 64..127 at 64..95
+            const uint32_t pcol = (uint32_t)(k < 4 ? k * 8 : 64 + (k - 4) * 8);
+            const uint64_t b = desc_mn_major(v_smem + s * KV_BYTES + k * UMMA_K * 128, HALF_BYTES);
+            umma_ts(tmem_base + O_COL + x * 128, tmem_base + S_COL + x * BLOCK_N + pcol, b, idesc_o,
+                    (it | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&o_full[x]);
+          if (x == 1) umma_commit(&v_free[s]);
+        }
+        __syncwarp();
+        return true;
+      };
+      if (ok) ok = issue_s(0, 0);
+      if (ok) ok = issue_s(1, 0);
+      for (int it = 0; it < I.n_tiles && ok; ++it) {
+        ok = issue_pv(0, it);
+        if (ok && it + 1 < I.n_tiles) ok = issue_s(0, it + 1);
+        if (ok) ok = issue_pv(1, it);
+        if (ok && it + 1 < I.n_tiles) ok = issue_s(1, it + 1);
+      }
+      gt += I.n_tiles;
+      ++j;
+    }
+    if (!ok) {
+      *failed = 1;
+      if (issuer) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 920);
+    }
+  } else if (warp < PAIR_V_WARP) {
+    // ---- softmax: team x = (warp - 2) / 8 has head I.h + x; two threads a row: `sub` has keys
+    // 64 sub .. 64 sub + 63 of a tile (read in pieces of 32) and half of the head's dimensions ----
+    constexpr int HC = 32;                        // scores in registers at a time
+    const int team = (warp - 2) >> 3;
+    const int sub = ((warp - 2) >> 2) & 1;
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t s_col = lane_base + S_COL + team * BLOCK_N;
+    const uint32_t o_col = lane_base + O_COL + team * 128 + sub * (D / 2);
+    float* tmax = team_mem + team * 1024;         // [parity][sub][128]: the two threads of a row exchange their maxima
+    float* l_part = tmax + 512;                   // [quarter][128]
+    constexpr float LAZY = 8.f;
+    bool ok = true;
+    int gt = 0;
+    // A wait that runs out clears `ok`; the loops still run to their ends, skipping the work, so
+    // that every thread meets the named barriers of every tile of every item.
+    for (int round = 0;; ++round) {
+      Item I;
+      const int kind = get_item(round, I);
+      if (kind == 0) break;
+      if (kind == 2) continue;
+      const int pos0 = I.pos0, pos_last = I.pos_last, tile_first = I.tile_first, n_tiles = I.n_tiles;
+      const int pos = pos0 + row;
+      const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+      const int lo_last = (window > 0 && pos_last - window + 1 > 0) ? pos_last - window + 1 : 0;
+      // the sum of a row's weights is kept per quarter of a tile's keys (32 sub .. + 31), as the
+      // kernel with four threads a row keeps it, so that both give the same bits
+      float m_ref = -CUDART_INF_F, l_run[2] = {0.f, 0.f};
+      for (int it = 0; it < n_tiles; ++it) {
+        const int g = gt + it;
+        const int s = g & 1;                       // stage of the tile's keys and values
+        const int c0 = (tile_first + it) * BLOCK_N + sub * 64;        // first key of this thread
+        if (ok && !mbar_wait(&s_full[team], (uint32_t)g & 1u)) ok = false;
+        fence_after_sync();
+        const bool full_tile = (tile_first + it) * BLOCK_N + BLOCK_N - 1 <= pos0 && (tile_first + it) * BLOCK_N >= lo_last;
+        // ---- the row's maximum over the tile ----
+        float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int piece = 0; piece < 2; ++piece) {
+          uint32_t sc[HC];
+          tmem_ld32(s_col + sub * 64 + piece * HC, sc);
+          tmem_ld_wait();
+          if (full_tile) {
+#pragma unroll
+            for (int jj = 0; jj < HC; ++jj) mx[jj & 3] = fmaxf(mx[jj & 3], __uint_as_float(sc[jj]));
+          } else {
+            // selects, not branches: a masked score counts as -inf
+#pragma unroll
+            for (int jj = 0; jj < HC; ++jj) {
+              const int key = c0 + piece * HC + jj;
+              const bool keep = (key <= pos) & (key >= lo);
+              mx[jj & 3] = fmaxf(mx[jj & 3], keep ? __uint_as_float(sc[jj]) : -CUDART_INF_F);
+            }
+          }
+        }
+        float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        const int par = it & 1;
+        tmax[par * 256 + sub * 128 + row] = tile_max;
+        if (team == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+        else asm volatile("bar.sync 2, 256;" ::: "memory");
+        tile_max = fmaxf(tmax[par * 256 + row], tmax[par * 256 + 128 + row]);
+        // both threads of a row work out the same m_ref from the same numbers
+        const float m_new = tile_max * scale_log2;
+        const bool move = m_new > m_ref + LAZY;                      // true too for the first key a row sees
+        const float factor = move ? ((m_ref == -CUDART_INF_F) ? 0.f : ex2(m_ref - m_new)) : 1.f;
+        if (move) m_ref = m_new;
+        // O is scaled only after the PV of the tile before has been added to it (and before this
+        // tile's P is announced, so before the PV of this tile)
+        if (it > 0 && __any_sync(0xffffffffu, move)) {
+          if (ok && !mbar_wait(&o_full[team], (uint32_t)(g - 1) & 1u)) ok = false;
+          if (__all_sync(0xffffffffu, ok)) {
+            fence_after_sync();
+#pragma unroll
+            for (int piece = 0; piece < D / 64; ++piece) {            // this thread's half of the row, 32 columns at a time
+              uint32_t og[32];
+              tmem_ld32(o_col + piece * 32, og);
+              tmem_ld_wait();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) og[c] = __float_as_uint(__uint_as_float(og[c]) * factor);
+              tmem_st32(o_col + piece * 32, og);
+            }
+          }
+        }
+        // ---- p = exp2(s * scale - m_ref), rounded to bfloat16, two keys a column, written over
+        // scores this thread has already taken ----
+        const bool dead = m_ref == -CUDART_INF_F;          // nothing seen yet by this row
+        const float neg_m = dead ? 0.f : -m_ref;
+        const bool plain = full_tile & !dead;               // uniform over the block but for `dead`
+#pragma unroll
+        for (int piece = 0; piece < 2; ++piece) {
+          uint32_t sc[HC];
+          tmem_ld32(s_col + sub * 64 + piece * HC, sc);
+          tmem_ld_wait();
+          uint32_t pk[HC / 2];
+          float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int n0 = 0; n0 < HC; n0 += 8) {
+            float p[8];
+            if (plain) {
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) p[jj] = ex2(fmaf(__uint_as_float(sc[n0 + jj]), scale_log2, neg_m));
+            } else {
+              // every exponential is taken, masked ones of -inf (which is 0): selects, not branches
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) {
+                const int key = c0 + piece * HC + n0 + jj;
+                const bool keep = (key <= pos) & (key >= lo) & !dead;
+                p[jj] = ex2(keep ? fmaf(__uint_as_float(sc[n0 + jj]), scale_log2, neg_m) : -CUDART_INF_F);
+              }
+            }
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) ps[jj & 3] += p[jj];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) pk[(n0 >> 1) + jj] = pack_bf16(p[2 * jj], p[2 * jj + 1]);
+          }
+          tmem_st16(s_col + sub * 64 + piece * (HC / 2), pk);
+          l_run[piece] = fmaf(l_run[piece], factor, (ps[0] + ps[1]) + (ps[2] + ps[3]));
+        }
+        // value rows of keys past the last position were never written: they must not be NaN,
+        // since P is zero there and the MMA multiplies all the same
+        if ((tile_first + it) * BLOCK_N + BLOCK_N - 1 > pos_last) {
+          if (ok && !mbar_wait(&v_full[s], (uint32_t)(g >> 1) & 1u)) ok = false;
+          if (ok && sub < HALVES && (tile_first + it) * BLOCK_N + row > pos_last) {
+            uint4* vrow = reinterpret_cast<uint4*>(v_ptr + s * KV_BYTES + sub * HALF_BYTES + row * 128);
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) vrow[q8] = make_uint4(0u, 0u, 0u, 0u);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        tmem_st_wait();
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(&p_full[team]);
+      }
+      // ---- the item's end: the row's sum is that of its four quarters in order; each thread
+      // writes half of the row out ----
+      l_part[(sub * 2) * 128 + row] = l_run[0];
+      l_part[(sub * 2 + 1) * 128 + row] = l_run[1];
+      if (team == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 2, 256;" ::: "memory");
+      float l_row = l_part[row];
+#pragma unroll
+      for (int o = 1; o < 4; ++o) l_row += l_part[o * 128 + row];
+      const int g_last = gt + n_tiles - 1;
+      if (ok && !mbar_wait(&o_full[team], (uint32_t)g_last & 1u)) ok = false;
+      if (ok) {
+        fence_after_sync();
+        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+        __nv_bfloat16* dst = out + ((int64_t)(I.tok0 + row) * nq + I.h + team) * D + sub * (D / 2);
+#pragma unroll
+        for (int piece = 0; piece < D / 64; ++piece) {
+          uint32_t og[32];
+          tmem_ld32(o_col + piece * 32, og);
+          tmem_ld_wait();
+          if (row < I.ntok) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(og[c]) * inv, __uint_as_float(og[c + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(og[c + 2]) * inv, __uint_as_float(og[c + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(og[c + 4]) * inv, __uint_as_float(og[c + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(og[c + 6]) * inv, __uint_as_float(og[c + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + piece * 32 + c) = v;
+            }
+          }
+        }
+        fence_before_sync();                         // the next item's first PV overwrites O after its P
+      }
+      // the sums are read before any thread writes them for the next item
+      if (team == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+      else asm volatile("bar.sync 2, 256;" ::: "memory");
+      gt += n_tiles;
+    }
+    if (!ok) {
+      *failed = 1;
+      if (lane == 0) ls_record_fault(err, LS_DEV_WAIT_TIMEOUT, 940 + quad);
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                 CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -582,6 +1026,9 @@ int sm_count() {
   return sms;
 }
 
+// 0: a head a block always; 1: two heads of a key head a block where that pays; 2: wherever the group is even
+int pair_heads = 1;
+
 template <int HALVES>
 int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const int* work, int n_work,
            const int* block_table, int table_stride, int nq, int nkv, int page_size, int num_pages, int window,
@@ -595,6 +1042,26 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
       return LS_E_SMEM;
     configured = true;
   }
+  // two heads of a key head in a block where the group size is even and there are items enough
+  // to fill the device one and a half times over (with fewer, the longest item would set the
+  // time: a prompt of 2,048 tokens and 16 heads is 128 pairs, the longest of 16 double tiles)
+  if (pair_heads && (nq / nkv) % 2 == 0 &&
+      (pair_heads > 1 || 2LL * n_work * (nq / 2) >= 3LL * sm_count())) {
+    const size_t pair_smem = (size_t)KV_BYTES * (2 + 2 * STAGES) + 256 + 2 * 1024 * 4 + 1024;
+    static bool pair_configured = false;
+    if (!pair_configured) {
+      if (cudaFuncSetAttribute(attention_prefill_tc_pair_kernel<HALVES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)pair_smem) != cudaSuccess)
+        return LS_E_SMEM;
+      pair_configured = true;
+    }
+    const long long pair_items = (long long)n_work * (nq / 2);
+    const int pair_blocks = pair_items < sm_count() ? (int)pair_items : sm_count();
+    LS_COUNT(LS_K_ATTENTION_PREFILL_TC), ls_launch(attention_prefill_tc_pair_kernel<HALVES>, dim3(pair_blocks), PAIR_THREADS, pair_smem, stream, map_q, map_kv,
+              (__nv_bfloat16*)out, work, n_work, block_table, table_stride, nq, nkv, page_size, num_pages, window,
+              scale * 1.4426950408889634f, err);
+    return ls_launch_status();
+  }
   // a block per SM (its shared memory and its 512 columns of tensor memory fill one), or fewer items
   const long long items = (long long)n_work * nq;
   const int blocks = items < sm_count() ? (int)items : sm_count();
@@ -606,6 +1073,7 @@ int launch(const CUtensorMap& map_q, const CUtensorMap& map_kv, void* out, const
 }  // namespace
 
 LS_API int ls_attention_prefill_tc_tile_tokens() { return BLOCK_M; }
+LS_API void ls_set_attention_prefill_pairs(int mode) { pair_heads = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 
 // q, out: [tokens, nq * d] bfloat16; pages [num_pages, 2, nkv, page_size, d]; d 64 or 128; page
 // sizes 8, 16, 32, 64, 128.  Work items as for ls_attention_tile with up to 128 tokens each

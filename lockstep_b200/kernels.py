@@ -112,6 +112,15 @@ def set_gemm_tc_pairs(on: bool) -> None:
     fn(1 if on else 0)
 
 
+def set_attention_prefill_pairs(mode: int) -> None:
+    """How the tensor-core attention of prompt portions takes the heads of a key head: 0 one
+    head a block; 1 (the default) two heads a block, sharing the key and value tiles, where the
+    group size is even and the items fill the device twice over; 2 wherever the group is even."""
+    fn = library("tc").ls_set_attention_prefill_pairs
+    fn.argtypes, fn.restype = [c_int], None
+    fn(int(mode))
+
+
 def set_dependent_launch(on: bool) -> None:
     """Programmatic dependent launch of all kernels (on by default): a kernel is
     scheduled while its predecessor drains and waits for it before it touches memory."""

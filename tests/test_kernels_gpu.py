@@ -313,6 +313,14 @@ def test_attention_prefix_portion_and_decode(dtype, nq, nkv, d, page, window):
             for lo, hi in [(0, 700), (550, 700), (0, 1), (63, 65), (640, 642), (100, 229), (127, 130), (0, 129)]:
                 got = run_attention(k, q[lo:hi], pages, ids, lo, window, scale, kernel)
                 assert (got - want[lo:hi]).abs().max() <= bound, (kernel, lo, hi)
+                if (nq // nkv) % 2 == 0:
+                    # two heads of a key head in a block: another kernel, the same sums, the same bits
+                    k.set_attention_prefill_pairs(2)
+                    try:
+                        paired = run_attention(k, q[lo:hi], pages, ids, lo, window, scale, kernel)
+                    finally:
+                        k.set_attention_prefill_pairs(1)
+                    assert torch.equal(paired, got), (kernel, lo, hi)
     # single tokens at telling places: first, page edges, split edges, last
     for pos in [0, 1, page - 1, page, 255, 256, 257, 511, 512, 699]:
         sub_pages, sub_ids = pages, ids

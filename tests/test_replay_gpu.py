@@ -177,6 +177,28 @@ def test_long_decoding_and_first_tokens(zoo):
 
 
 @pytest.mark.parametrize("name", ["D", "E"])
+def test_prompt_attention_with_two_heads_a_block_gives_the_same_bits(zoo, name):
+    """The tensor-core attention of prompts has a kernel with one query head a block and one with
+    the two heads of a key head a block (taken where a launch has items enough); which one runs
+    depends on the batch, so both must give every row the same bits."""
+    from lockstep_b200 import kernels as K
+
+    folder, requests, plain = zoo(name, "bfloat16")
+    rows = {}
+    try:
+        for mode in (0, 2):
+            K.set_attention_prefill_pairs(mode)
+            steps = make_plan("portions", name, requests)
+            rows[mode] = H.run_plan(make_runner(folder, name, "bfloat16", steps), steps)
+    finally:
+        K.set_attention_prefill_pairs(1)
+    H.assert_rows_close(rows[2], plain, "bfloat16", f"{name}/two heads a block", config=name)
+    assert rows[0].keys() == rows[2].keys()
+    for key in rows[0]:
+        assert torch.equal(rows[0][key], rows[2][key]), key
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
 def test_bfloat16_rows_do_not_depend_on_the_neighbours(zoo, name):
     """One request, cut the same way, alone and beside other requests of other lengths (so that
     its products run in other kernels and its rows lie elsewhere in the batch): the same bits.
