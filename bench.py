@@ -335,7 +335,7 @@ def run_ours(args):
     layers = cfg["num_hidden_layers"]
     pk = peaks()
     batches = sorted({args.batch, 1, 64} if not args.quick else {args.batch})
-    max_batch = max(batches)
+    max_batch = 1 if args.only == "prefill" else max(batches)      # (the cache pool is sized for batch x context)
     engine = build_engine(cfg, args.dtype if args.only else "bfloat16", max_batch,
                           max(CONTEXT, args.prefill_tokens + 64) if args.only == "prefill" else CONTEXT)
     runner = engine.runner

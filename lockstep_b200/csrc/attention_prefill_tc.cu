@@ -109,6 +109,32 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Two float32 lanes an instruction (sm_100: fma / add on pairs of registers) and the maximum of
+// three: the softmax warps are short of issue slots, and each of these halves an instruction
+// count without changing a result (every lane is rounded as the single instruction rounds it).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// (x, y) = (a x + c, a y + c)
+__device__ __forceinline__ void fma2(float& x, float& y, float a, float c) {
+  uint64_t xy, aa, cc, r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(xy) : "f"(x), "f"(y));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(aa) : "f"(a));
+  asm("mov.b64 %0, {%1, %1};" : "=l"(cc) : "f"(c));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(xy), "l"(aa), "l"(cc));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(r));
+}
+// (x, y) += (a, b)
+__device__ __forceinline__ void add2(float& x, float& y, float a, float b) {
+  uint64_t xy, ab, r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(xy) : "f"(x), "f"(y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ab) : "f"(a), "f"(b));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(xy), "l"(ab));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(r));
+}
+
 // One work item of a block: up to 128 tokens of a request (rows of the MMA tile) and one query head.
 struct Item {
   const int* table_row;
@@ -411,7 +437,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
         if (full_tile) {
 #pragma unroll
-          for (int jj = 0; jj < HC; ++jj) mx[jj & 3] = fmaxf(mx[jj & 3], __uint_as_float(sc[jj]));
+          for (int jj = 0; jj < HC; jj += 2)
+            mx[(jj >> 1) & 3] = max3(mx[(jj >> 1) & 3], __uint_as_float(sc[jj]), __uint_as_float(sc[jj + 1]));
         } else {
           // selects, not branches: a masked score counts as -inf
 #pragma unroll
@@ -460,7 +487,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             float p[8];
             if (plain) {
 #pragma unroll
-              for (int jj = 0; jj < 8; ++jj) p[jj] = ex2(fmaf(__uint_as_float(sc[n0 + jj]), scale_log2, neg_m));
+              for (int jj = 0; jj < 8; jj += 2) {
+                p[jj] = __uint_as_float(sc[n0 + jj]);
+                p[jj + 1] = __uint_as_float(sc[n0 + jj + 1]);
+                fma2(p[jj], p[jj + 1], scale_log2, neg_m);
+                p[jj] = ex2(p[jj]);
+                p[jj + 1] = ex2(p[jj + 1]);
+              }
             } else {
               // every exponential is taken, masked ones of -inf (which is 0): selects, not branches
 #pragma unroll
@@ -470,8 +503,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 p[jj] = ex2(keep ? fmaf(__uint_as_float(sc[n0 + jj]), scale_log2, neg_m) : -CUDART_INF_F);
               }
             }
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) ps[jj & 3] += p[jj];
+            add2(ps[0], ps[1], p[0], p[1]);
+            add2(ps[2], ps[3], p[2], p[3]);
+            add2(ps[0], ps[1], p[4], p[5]);
+            add2(ps[2], ps[3], p[6], p[7]);
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) pk[(n0 >> 1) + jj] = pack_bf16(p[2 * jj], p[2 * jj + 1]);
           }
@@ -844,7 +879,8 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
           tmem_ld_wait();
           if (full_tile) {
 #pragma unroll
-            for (int jj = 0; jj < HC; ++jj) mx[jj & 3] = fmaxf(mx[jj & 3], __uint_as_float(sc[jj]));
+            for (int jj = 0; jj < HC; jj += 2)
+              mx[(jj >> 1) & 3] = max3(mx[(jj >> 1) & 3], __uint_as_float(sc[jj]), __uint_as_float(sc[jj + 1]));
           } else {
             // selects, not branches: a masked score counts as -inf
 #pragma unroll
@@ -900,7 +936,13 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
             float p[8];
             if (plain) {
 #pragma unroll
-              for (int jj = 0; jj < 8; ++jj) p[jj] = ex2(fmaf(__uint_as_float(sc[n0 + jj]), scale_log2, neg_m));
+              for (int jj = 0; jj < 8; jj += 2) {
+                p[jj] = __uint_as_float(sc[n0 + jj]);
+                p[jj + 1] = __uint_as_float(sc[n0 + jj + 1]);
+                fma2(p[jj], p[jj + 1], scale_log2, neg_m);
+                p[jj] = ex2(p[jj]);
+                p[jj + 1] = ex2(p[jj + 1]);
+              }
             } else {
               // every exponential is taken, masked ones of -inf (which is 0): selects, not branches
 #pragma unroll
@@ -910,8 +952,10 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 p[jj] = ex2(keep ? fmaf(__uint_as_float(sc[n0 + jj]), scale_log2, neg_m) : -CUDART_INF_F);
               }
             }
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) ps[jj & 3] += p[jj];
+            add2(ps[0], ps[1], p[0], p[1]);
+            add2(ps[2], ps[3], p[2], p[3]);
+            add2(ps[0], ps[1], p[4], p[5]);
+            add2(ps[2], ps[3], p[6], p[7]);
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) pk[(n0 >> 1) + jj] = pack_bf16(p[2 * jj], p[2 * jj + 1]);
           }
