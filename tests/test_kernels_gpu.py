@@ -338,6 +338,53 @@ def test_attention_prefix_portion_and_decode(dtype, nq, nkv, d, page, window):
         assert torch.equal(one[0], whole[140])
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,n,window", [(16, 8, 128, 16, 8192, 0), (8, 2, 64, 8, 5000, 0),
+                                                     (32, 8, 128, 32, 4096, 1000), (4, 1, 128, 16, 12000, 0)])
+def test_the_two_prompt_attention_kernels_agree_bit_for_bit_on_long_prompts(nq, nkv, d, page, n, window):
+    """One head a block against the two heads of a key head a block, on prompts long enough that a
+    launch would take the second by itself, five runs each: the same bits every time (the second
+    kernel writes P over the scores it came from and relies on the order of the MMAs; a race
+    would show as a run that differs)."""
+    from lockstep_b200.engine.batch import plan_attention
+
+    k = K()
+    g = torch.Generator(device=dev()).manual_seed(n)
+    q = torch.randn(n, nq * d, generator=g, device=dev()).bfloat16()
+    num_pages = -(-n // page)
+    pages = torch.randn(num_pages, 2, nkv, page, d, generator=g, device=dev()).bfloat16()
+    table = torch.randperm(num_pages, generator=g, device=dev()).to(torch.int32).view(1, -1).contiguous()
+    tile, _, _, _ = plan_attention([(0, 0, 0, n)], window, k.attention_split_size(), 128)
+    work = torch.from_numpy(tile).to(dev())
+    err = k.new_error_word(dev())
+    outs = {0: [], 2: []}
+    try:
+        for mode in (0, 2):
+            k.set_attention_prefill_pairs(mode)
+            for _ in range(1 if mode == 0 else 5):
+                out = torch.full_like(q, float("nan"))
+                assert k.attention_prefill_tc(q, pages, out, work, len(tile), table, nq, nkv, d, window,
+                                              1 / math.sqrt(d), err)
+                outs[mode].append(out)
+    finally:
+        k.set_attention_prefill_pairs(1)
+    k.raise_on_fault(err)
+    assert bool(torch.isfinite(outs[0][0].float()).all())
+    for out in outs[2]:
+        assert torch.equal(out, outs[0][0])
+    # spot rows against plain attention
+    qf = q.double().cpu().view(n, nq, d)
+    for r in (0, 127, 128, n // 2 + 3, n - 1):
+        keys = torch.arange(max(0, r - window + 1) if window else 0, r + 1)
+        want = torch.empty(nq, d, dtype=torch.float64)
+        for h in range(nq):
+            kv = h // (nq // nkv)
+            pg, off = table[0, (keys // page).to(dev())].cpu().long(), keys % page
+            kk = pages[pg, 0, kv, off].double().cpu()
+            vv = pages[pg, 1, kv, off].double().cpu()
+            want[h] = torch.softmax(kk @ qf[r, h] / math.sqrt(d), 0) @ vv
+        assert (outs[0][0][r].double().cpu().view(nq, d) - want).abs().max() <= 2e-2, r
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("d", [32, 128])
 def test_attention_finds_one_far_key(dtype, d):
