@@ -175,10 +175,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint64_t* q_full = bars;             // Q of an item landed
   uint64_t* k_full = bars + 1;         // [2] keys of a tile landed
   uint64_t* v_full = bars + 3;         // [2] values landed
-  uint64_t* k_free = bars + 5;         // [2] S = Q K^T has read the stage
-  uint64_t* v_free = bars + 7;         // [2] PV has read the stage
+  // (a key stage is free when the S product that read it is done, which is what s_full says; a
+  // value stage when its PV product is done: o_full.  The producers wait on those: a commit of
+  // its own for each cost the issuing warp ≈ 125 cycles a tile)
   uint64_t* s_full = bars + 9;         // [2] S of a tile is in tensor memory
-  uint64_t* s_free = bars + 11;        // [2] the softmax warps have read it
   uint64_t* q_free = bars + 13;        // the item's last S product has read Q
   uint64_t* o_full = bars + 14;        // [2] PV of a tile has been added to O (and its P may be overwritten)
   uint64_t* p_full = bars + 16;        // [2] P of a tile is in tensor memory
@@ -236,10 +236,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int s = 0; s < 2; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&v_full[s], 1);
-      mbar_init(&k_free[s], 1);
-      mbar_init(&v_free[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_free[s], 4 * GROUPS);
       mbar_init(&o_full[s], 1);
     }
     mbar_init(&p_full[0], 4 * GROUPS);
@@ -265,7 +262,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // ---- producers: warp 0 fetches Q and the key tiles, warp V_WARP the value tiles: a key stage
     // is free two tiles before the value stage of the same tile, and neither waits for the other's ----
     const bool keys = warp == 0;
-    uint64_t* free_bar = keys ? k_free : v_free;
+    uint64_t* free_bar = keys ? s_full : o_full;
     uint64_t* full_bar = keys ? k_full : v_full;
     const uint32_t dst_base = keys ? k_smem : v_smem;
     int gt = 0, j = 0;                  // tiles and items of this block so far
@@ -338,9 +335,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int g = gt + it;
         const int s = g & 1;
         const uint32_t phase = (uint32_t)(g >> 1) & 1u;
-        bool got = mbar_wait(&k_full[s], phase);
-        if (g >= 2) got = got && mbar_wait(&s_free[s], (uint32_t)((g >> 1) - 1) & 1u);
-        if (!__all_sync(0xffffffffu, got)) return false;
+        // (the S buffer is free: the softmax warps had read tile g - 2 before they announced its P,
+        // which this warp waited for before the PV product of that tile)
+        if (!__all_sync(0xffffffffu, mbar_wait(&k_full[s], phase))) return false;
         fence_after_sync();
         if (issuer) {
 #pragma unroll
@@ -350,7 +347,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                  desc_k_major(k_smem + s * KV_BYTES + koff), idesc_s, k != 0 ? 1u : 0u);
           }
           umma_commit(&s_full[s]);
-          umma_commit(&k_free[s]);
           if (it == I.n_tiles - 1) umma_commit(q_free);     // the item's last product with this Q
         }
         __syncwarp();
@@ -375,7 +371,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     (it | k) != 0 ? 1u : 0u);
           }
           umma_commit(&o_full[s]);
-          umma_commit(&v_free[s]);
         }
         __syncwarp();
       }
@@ -429,9 +424,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int q0 = 0; q0 < HC; q0 += 32) tmem_ld32(lane_base + S_COL + s * BLOCK_N + group * HC + q0, sc + q0);
         tmem_ld_wait();
-        fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s_free[s]);
         // every key of the tile is seen by every row: no masks (uniform over the block)
         const bool full_tile = (tile_first + it) * BLOCK_N + BLOCK_N - 1 <= pos0 && (tile_first + it) * BLOCK_N >= lo_last;
         float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
