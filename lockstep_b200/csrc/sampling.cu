@@ -209,6 +209,301 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ probs,
   if (threadIdx.x == 0) out[r] = token;
 }
 
+// --------------------------------------------------------------------------
+// The same sampling with a row spread over the eight blocks of a cluster: a thread keeps its
+// tokens' probabilities in registers (ids gthread * per .. + per - 1, contiguous, so that ties
+// are met in id order), every pass of the bisection is a compare-and-add over those registers,
+// a block sum and one exchange of the eight blocks' partials through distributed shared
+// memory, summed in rank order.  One block a row walked the row's 152 k probabilities from
+// memory 31 times a selection (≈ 1 ms a call, 1.8 ms with top-p, whatever the number of rows).
+// Sums are taken in an order fixed by the vocabulary size alone; all blocks of a cluster see the
+// same totals and take the same decisions.
+// --------------------------------------------------------------------------
+constexpr int SAMPLE_CLUSTER = 8;
+constexpr int SAMPLE_PER = 20;        // probabilities a thread keeps: vocabularies up to 8 x 1024 x 20 = 163,840
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t peer_addr(const void* mine, int rank) {
+  uint32_t a = (uint32_t)__cvta_generic_to_shared(mine), r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_peer_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_peer_s32(uint32_t addr) {
+  int v;
+  asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+// What the blocks of a cluster exchange: two sets of slots used in turn, so that a block may
+// write its next partial while a slow peer still reads the last one.
+struct ClusterShare {
+  float f[2][4];
+  int i[2][2];
+  float all_f[SAMPLE_CLUSTER][4];
+  int all_i[SAMPLE_CLUSTER][2];
+  float warp_f[3][32];
+  int warp_i[32];
+};
+
+// Every block gives (a, b); every thread gets the eight blocks' pairs in rank order in sh.all_f.
+// `turn` (every thread's own copy, the same in all) says which set of slots this exchange uses.
+__device__ void cluster_gather_f(ClusterShare& sh, int& turn, float a, float b = 0.f, float c = 0.f) {
+  const int t = turn;
+  turn ^= 1;
+  if (threadIdx.x == 0) { sh.f[t][0] = a; sh.f[t][1] = b; sh.f[t][2] = c; }
+  cluster_sync_all();
+  if (threadIdx.x < SAMPLE_CLUSTER * 4) {
+    const int rank = threadIdx.x >> 2, which = threadIdx.x & 3;
+    sh.all_f[rank][which] = ld_peer_f32(peer_addr(&sh.f[t][which], rank));
+  }
+  __syncthreads();
+}
+__device__ void cluster_gather_i(ClusterShare& sh, int& turn, int a, int b) {
+  const int t = turn;
+  turn ^= 1;
+  if (threadIdx.x == 0) { sh.i[t][0] = a; sh.i[t][1] = b; }
+  cluster_sync_all();
+  if (threadIdx.x < SAMPLE_CLUSTER * 2) {
+    const int rank = threadIdx.x >> 1, which = threadIdx.x & 1;
+    sh.all_i[rank][which] = ld_peer_s32(peer_addr(&sh.i[t][which], rank));
+  }
+  __syncthreads();
+}
+
+// sum over the cluster: a thread's value, lanes by xor tree, warps ascending, blocks in rank order
+__device__ float cluster_sum(ClusterShare& sh, int& turn, float v) {
+  const float block = ls_block_sum(v, sh.warp_f[0]);
+  cluster_gather_f(sh, turn, block);
+  float total = 0.f;
+#pragma unroll
+  for (int r = 0; r < SAMPLE_CLUSTER; ++r) total += sh.all_f[r][0];
+  __syncthreads();          // all have read before the next gather writes
+  return total;
+}
+
+// three sums over the cluster at once (each in the order of cluster_sum): one exchange for all
+__device__ void cluster_sum3(ClusterShare& sh, int& turn, float& a, float& b, float& c) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  a = ls_warp_sum(a);
+  b = ls_warp_sum(b);
+  c = ls_warp_sum(c);
+  __syncthreads();
+  if (lane == 0) { sh.warp_f[0][warp] = a; sh.warp_f[1][warp] = b; sh.warp_f[2][warp] = c; }
+  __syncthreads();
+  float ta = 0.f, tb = 0.f, tc = 0.f;
+  for (int w = 0; w < 32; ++w) { ta += sh.warp_f[0][w]; tb += sh.warp_f[1][w]; tc += sh.warp_f[2][w]; }
+  cluster_gather_f(sh, turn, ta, tb, tc);
+  a = b = c = 0.f;
+#pragma unroll
+  for (int r = 0; r < SAMPLE_CLUSTER; ++r) { a += sh.all_f[r][0]; b += sh.all_f[r][1]; c += sh.all_f[r][2]; }
+  __syncthreads();
+}
+
+// mass of this cluster's row with p >= the value whose bits are `bits`
+__device__ float mass_at_least_regs(ClusterShare& sh, int& turn, const float* p, int per, uint32_t bits) {
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < SAMPLE_PER; ++j)
+    if (j < per && __float_as_uint(p[j]) >= bits) s += p[j];
+  return cluster_sum(sh, turn, s);
+}
+
+// select_rank over the registers of a cluster: the token on which `target` falls in the
+// (-p, id) order, written to *token_out by the one thread that holds it; returns the mass up to
+// and including that token.
+__device__ float select_rank_regs(ClusterShare& sh, int& turn, const float* p, int per, int begin, float target,
+                                  int* token_out) {
+  target = fmaxf(target, 1e-37f);
+  // the largest bit pattern lo with mass(lo) >= target, the interval cut in four a pass (three
+  // thresholds' masses from one sweep over the registers and one exchange)
+  uint32_t lo = 0u, hi = 0x7f800000u;
+  for (int it = 0; it < 32 && lo < hi; ++it) {
+    const uint32_t span = hi - lo;
+    const uint32_t q1 = span >> 2, q2 = span >> 1, q3 = span - (span >> 2);
+    const uint32_t t1 = lo + (q1 ? q1 : 1u), t2 = lo + (q2 ? q2 : 1u), t3 = lo + (q3 ? q3 : 1u);
+    float m1 = 0.f, m2 = 0.f, m3 = 0.f;
+#pragma unroll
+    for (int j = 0; j < SAMPLE_PER; ++j) {
+      if (j < per) {
+        const uint32_t b = __float_as_uint(p[j]);
+        if (b >= t1) m1 += p[j];
+        if (b >= t2) m2 += p[j];
+        if (b >= t3) m3 += p[j];
+      }
+    }
+    cluster_sum3(sh, turn, m1, m2, m3);
+    if (m3 >= target) lo = t3;
+    else if (m2 >= target) { lo = t2; hi = t3 - 1u; }
+    else if (m1 >= target) { lo = t1; hi = t2 - 1u; }
+    else hi = t1 - 1u;
+  }
+  // snap lo to the smallest probability that occurs at or above it
+  float vmin = CUDART_INF_F;
+#pragma unroll
+  for (int j = 0; j < SAMPLE_PER; ++j)
+    if (j < per && __float_as_uint(p[j]) >= lo) vmin = fminf(vmin, p[j]);
+  vmin = -ls_warp_max(-vmin);
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) sh.warp_f[0][warp] = vmin;
+    __syncthreads();
+    vmin = sh.warp_f[0][0];
+    for (int w = 1; w < 32; ++w) vmin = fminf(vmin, sh.warp_f[0][w]);
+    __syncthreads();
+  }
+  cluster_gather_f(sh, turn, vmin);
+#pragma unroll
+  for (int r = 0; r < SAMPLE_CLUSTER; ++r) vmin = fminf(vmin, sh.all_f[r][0]);
+  __syncthreads();
+  const uint32_t vbits = __float_as_uint(vmin);
+  const float above = mass_at_least_regs(sh, turn, p, per, vbits + 1u);
+  int j = 0;
+  if (vmin > 0.f && vmin < CUDART_INF_F) {
+    j = (int)ceilf((target - above) / vmin) - 1;
+    if (j < 0) j = 0;
+  }
+  // ties of value vmin in ascending id: a thread's ids are contiguous and ascend with the thread
+  int count = 0;
+#pragma unroll
+  for (int q = 0; q < SAMPLE_PER; ++q) count += (q < per && __float_as_uint(p[q]) == vbits);
+  // exclusive prefix over the block: lanes by a scan, warps ascending
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = count;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  if (lane == 31) sh.warp_i[warp] = incl;
+  __syncthreads();
+  int before = incl - count, block_total = 0;
+  for (int w = 0; w < 32; ++w) {
+    if (w < warp) before += sh.warp_i[w];
+    block_total += sh.warp_i[w];
+  }
+  __syncthreads();
+  cluster_gather_i(sh, turn, block_total, 0);
+  const int rank = (int)cluster_rank();
+  int total = 0;
+#pragma unroll
+  for (int r = 0; r < SAMPLE_CLUSTER; ++r) {
+    if (r < rank) before += sh.all_i[r][0];
+    total += sh.all_i[r][0];
+  }
+  __syncthreads();
+  if (j >= total) j = total - 1;
+  if (j < 0) j = 0;
+  if (total <= 0 && rank == 0 && threadIdx.x == 0) *token_out = 0;      // nothing to choose from (a row of NaN)
+  if (j >= before && j < before + count) {
+    int k = before;
+#pragma unroll
+    for (int q = 0; q < SAMPLE_PER; ++q) {
+      if (q < per && __float_as_uint(p[q]) == vbits) {
+        if (k == j) *token_out = begin + q;
+        ++k;
+      }
+    }
+  }
+  return above + (float)(j + 1) * vmin;
+}
+
+__global__ void __cluster_dims__(SAMPLE_CLUSTER, 1, 1) __launch_bounds__(SAMPLE_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                      const float* __restrict__ top_p, const uint32_t* __restrict__ keys,
+                      const uint32_t* __restrict__ positions, int* __restrict__ out, int vocab) {
+  ls_dependency_sync();
+  __shared__ ClusterShare sh;
+  const int r = blockIdx.x / SAMPLE_CLUSTER;
+  const int rank = (int)cluster_rank();
+  const float* row = logits + (int64_t)r * vocab;
+  const int per = (vocab + SAMPLE_CLUSTER * SAMPLE_THREADS - 1) / (SAMPLE_CLUSTER * SAMPLE_THREADS);
+  const int begin = (rank * SAMPLE_THREADS + (int)threadIdx.x) * per;
+  int turn = 0;
+  // this thread's logits; the row's argmax (ties to the lowest id; NaN never wins)
+  float p[SAMPLE_PER];
+  ArgMax best{-CUDART_INF_F, 0x7fffffff};
+#pragma unroll
+  for (int j = 0; j < SAMPLE_PER; ++j) {
+    p[j] = -CUDART_INF_F;
+    if (j < per && begin + j < vocab) {
+      p[j] = row[begin + j];
+      if (p[j] > best.v || (p[j] == best.v && begin + j < best.i)) best = ArgMax{p[j], begin + j};
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sh.warp_f[0][warp] = best.v; sh.warp_i[warp] = best.i; }
+    __syncthreads();
+    best = ArgMax{sh.warp_f[0][0], sh.warp_i[0]};
+    for (int w = 1; w < 32; ++w) best = better(best, ArgMax{sh.warp_f[0][w], sh.warp_i[w]});
+    __syncthreads();
+  }
+  cluster_gather_f(sh, turn, best.v);
+  cluster_gather_i(sh, turn, best.i, 0);
+  ArgMax top{sh.all_f[0][0], sh.all_i[0][0]};
+#pragma unroll
+  for (int q = 1; q < SAMPLE_CLUSTER; ++q) top = better(top, ArgMax{sh.all_f[q][0], sh.all_i[q][0]});
+  __syncthreads();
+  if (top.i == 0x7fffffff) top.i = 0;
+  const float temp = temperature[r];
+  if (!(temp > 0.f)) {                       // the same branch in every block of the cluster
+    if (rank == 0 && threadIdx.x == 0) out[r] = top.i;
+    cluster_sync_all();                      // no block leaves while a peer may still read its shared memory
+    return;
+  }
+  // p = exp(l / T - max) / sum, as the one-block kernel takes it
+  const float vmax = __fdiv_rn(top.v, temp);
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < SAMPLE_PER; ++j) {
+    if (j < per && begin + j < vocab) {
+      p[j] = expf(__fdiv_rn(p[j], temp) - vmax);
+      s += p[j];
+    } else {
+      p[j] = 0.f;
+    }
+  }
+  const float z = cluster_sum(sh, turn, s);
+#pragma unroll
+  for (int j = 0; j < SAMPLE_PER; ++j) p[j] = __fdiv_rn(p[j], z);
+  // tokens past the vocabulary hold 0: they never count as ties of a positive value, and a
+  // selection never lands on them since `vmin` is taken over values at or above a mass that exists
+  const int live = begin < vocab ? (vocab - begin < per ? vocab - begin : per) : 0;
+
+  const float u = (float)((double)philox_word0(positions[2 * r], positions[2 * r + 1], keys[2 * r],
+                                               keys[2 * r + 1]) * 2.3283064365386963e-10);
+  const float tp = top_p[r];
+  int token = -1;
+  float head;
+  if (tp < 1.0f) {
+    int unused = -1;
+    head = select_rank_regs(sh, turn, p, live, begin, tp, &unused);
+  } else {
+    head = mass_at_least_regs(sh, turn, p, live, 0u);
+  }
+  select_rank_regs(sh, turn, p, live, begin, u * head, &token);
+  if (token >= 0) out[r] = token;            // exactly one thread of the cluster holds it
+  cluster_sync_all();                        // no block leaves while a peer may still read its shared memory
+}
+
 // argmax in two stages, so that a few rows of a wide vocabulary fill the device:
 // stage 1 reduces contiguous chunks of a row, stage 2 the chunks' winners.
 constexpr int ARGMAX_CHUNKS = 64;
@@ -270,11 +565,25 @@ LS_API int ls_argmax(const float* logits, int* out, void* scratch, int rows, int
   return ls_launch_status();
 }
 
-// probs: scratch [rows, vocab] float32.  keys, positions: [rows, 2] uint32 (low, high).
+// How many floats of scratch ls_sample needs for its probabilities: none where a row fits the
+// registers of a cluster (vocabularies up to 163,840), else rows x vocab.
+LS_API long long ls_sample_scratch_floats(int rows, int vocab) {
+  return vocab <= SAMPLE_CLUSTER * SAMPLE_THREADS * SAMPLE_PER ? 0LL : (long long)rows * vocab;
+}
+
+// probs: scratch of ls_sample_scratch_floats(rows, vocab) floats (may be null when that is 0).
+// keys, positions: [rows, 2] uint32 (low, high).
 LS_API int ls_sample(const float* logits, float* probs, const float* temperature,
                      const float* top_p, const uint32_t* keys, const uint32_t* positions, int* out,
                      int rows, int vocab, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  if (vocab <= SAMPLE_CLUSTER * SAMPLE_THREADS * SAMPLE_PER) {
+    // a row over the eight blocks of a cluster, its probabilities in registers
+    LS_COUNT(LS_K_SAMPLE), ls_launch(sample_cluster_kernel, rows * SAMPLE_CLUSTER, SAMPLE_THREADS, 0, stream, logits, temperature,
+                                     top_p, keys, positions, out, vocab);
+    return ls_launch_status();
+  }
+  if (probs == nullptr) return LS_E_SIZE;
   LS_COUNT(LS_K_SAMPLE), ls_launch(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, probs, temperature, top_p, keys,
                                                      positions, out, vocab);
   return ls_launch_status();
@@ -282,6 +591,7 @@ LS_API int ls_sample(const float* logits, float* probs, const float* temperature
 
 LS_API const char* ls_constants_sampling() {
   static char buf[256];
-  static const LsConstant c[] = {{"argmax.chunks", ARGMAX_CHUNKS}, {"sample.threads", SAMPLE_THREADS}};
+  static const LsConstant c[] = {{"argmax.chunks", ARGMAX_CHUNKS}, {"sample.threads", SAMPLE_THREADS},
+                                 {"sample.cluster_blocks", SAMPLE_CLUSTER}, {"sample.kept_per_thread", SAMPLE_PER}};
   return ls_format_constants(buf, sizeof buf, c, (int)(sizeof c / sizeof c[0]));
 }

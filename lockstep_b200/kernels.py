@@ -385,13 +385,23 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
                                _dev(scratch, "scratch"), rows, vocab, _stream()), "argmax")
 
 
+def sample_scratch_floats(rows: int, vocab: int) -> int:
+    """Floats of scratch ``sample`` needs for ``rows`` rows of ``vocab`` logits (0: none)."""
+    fn = library().ls_sample_scratch_floats
+    fn.argtypes, fn.restype = [c_int, c_int], ctypes.c_longlong
+    return int(fn(rows, vocab))
+
+
 def sample(logits, probs, temperature, top_p, keys, positions, out) -> None:
-    """keys, positions: [rows, 2] int32 holding the low and high 32 bits."""
+    """keys, positions: [rows, 2] int32 holding the low and high 32 bits.  ``probs``: float32
+    scratch of ``sample_scratch_floats(rows, vocab)`` elements, or None where that is 0."""
     rows, vocab = logits.shape
-    if probs.shape != logits.shape:
+    if probs is not None and probs.numel() < rows * vocab:
         raise KernelError("sample: probs scratch does not match the logits")
+    if probs is None and sample_scratch_floats(rows, vocab):
+        raise KernelError("sample: this vocabulary needs a scratch for the probabilities")
     _check(library().ls_sample(
-        _dev(logits, "logits", torch.float32), _dev(probs, "probs", torch.float32),
+        _dev(logits, "logits", torch.float32), _opt(probs, "probs", torch.float32),
         _dev(temperature, "temperature", torch.float32), _dev(top_p, "top_p", torch.float32),
         _dev(keys, "keys", torch.int32), _dev(positions, "positions", torch.int32),
         _dev(out, "out", torch.int32), rows, vocab, _stream()), "sample")

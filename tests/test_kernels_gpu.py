@@ -479,3 +479,51 @@ def test_sampling_matches_plain_on_clear_cases_and_in_distribution():
     # within rounding of a boundary may pick the neighbour
     assert got[0] == int(logits[0].argmax())
     assert agree >= rows - 2, f"only {agree} of {rows} draws agree with the plain sampler"
+
+
+def test_sampling_over_a_wide_vocabulary_with_ties():
+    """151,936 tokens (a row spread over the blocks of a cluster, probabilities in registers)
+    against the plain sampler; rows with many equal logits, where the rank among the ties
+    decides; a greedy row; a row whose mass sits on one token."""
+    k = K()
+    from lockstep_b200.sampling import philox
+
+    vocab = 151936
+    g = torch.Generator().manual_seed(9)
+    rows = 24
+    logits = torch.randn(rows, vocab, generator=g) * 4
+    logits[1] = torch.randint(0, 6, (vocab,), generator=g).float()          # six values: ties everywhere
+    logits[2] = 0.0                                                          # all equal: the draw picks an id
+    logits[3, 77777] = 60.0                                                  # one token has all the mass
+    temperature = torch.tensor([0.9 if i % 2 else 1.2 for i in range(rows)])
+    temperature[0] = 0.0
+    top_p = torch.tensor([1.0 if i % 3 else 0.7 for i in range(rows)])
+    top_p[1], top_p[2] = 0.5, 1.0
+    uids = [f"wide{i}" for i in range(rows)]
+    positions = [5 + 11 * i for i in range(rows)]
+    seed = 77
+    keys = torch.tensor([philox.key_words(seed, u) for u in uids], dtype=torch.int64)
+    pos = torch.tensor([[p & 0xFFFFFFFF, p >> 32] for p in positions], dtype=torch.int64)
+    as_i32 = lambda t: t.to(torch.int64).where(t < 2 ** 31, t - 2 ** 32).to(torch.int32)
+    out = torch.full((rows,), -7, dtype=torch.int32, device=dev())
+    probs = torch.empty(rows, vocab, dtype=torch.float32, device=dev())
+    k.sample(logits.to(dev()), probs, temperature.to(dev()), top_p.to(dev()), as_i32(keys).to(dev()),
+             as_i32(pos).to(dev()), out)
+    got = out.tolist()
+    assert all(0 <= t < vocab for t in got)
+    assert got[0] == int(logits[0].argmax()) and got[3] == 77777
+    agree, near = 0, 0
+    for i in range(rows):
+        want = plain.sample_top_p(logits[i], seed, uids[i], positions[i], p=float(top_p[i]),
+                                  temperature=float(temperature[i]))
+        agree += int(want == got[i])
+        # a draw within float32 rounding of a boundary may land on a neighbour in the ranking:
+        # a token of the same or the next probability
+        near += int(want == got[i] or abs(float(logits[i, want]) - float(logits[i, got[i]])) < 1e-3)
+    assert near == rows, f"{rows - near} draws are far from the plain sampler's"
+    assert agree >= rows - 4, f"only {agree} of {rows} draws agree with the plain sampler"
+    # the same call twice gives the same tokens
+    again = torch.empty_like(out)
+    k.sample(logits.to(dev()), probs, temperature.to(dev()), top_p.to(dev()), as_i32(keys).to(dev()),
+             as_i32(pos).to(dev()), again)
+    assert torch.equal(out, again)
