@@ -18,6 +18,11 @@ buffer that is refilled before each replay; work lists are padded to the
 capacity with null items, which the kernels skip.  Nothing about the
 arithmetic changes: the same kernels run on the same values.
 
+Steps that mix portions of prompts (a step that fills the token budget, say) are recorded too,
+keyed by their exact number of tokens and the rounded numbers of wanted rows and split items,
+when a step of the same shape comes for the third time: such steps launch some 300 kernels, and the
+host is slower at enqueueing them than the device at running them.
+
 A model whose parts are all ``graph_safe`` is one graph.  Where some are not (a mixer that
 reads the step's portions on the host), the runs of graph-safe steps between them are
 recorded, one graph each, and the other steps are called between the replays.
@@ -135,6 +140,101 @@ class StaticStepContext:
         self._pending = True
 
 
+MIXED_MIN_TOKENS = 256   # steps of fewer tokens are not worth a graph of their own
+MIXED_GRAPHS = 8         # recorded steps of mixed portions kept (least recently used goes first)
+MIXED_SPLIT_STEP = 64    # the split work list of such a step holds this many items, or a power of two times as many
+MIXED_PORTIONS = 4       # portions of two or more tokens such a step may hold
+MIXED_SIGHTINGS = 3      # a shape is recorded when it comes for this many times
+
+
+class StaticMixedContext:
+    """What parts see of a recorded step that mixes portions of prompts and decoded tokens: the
+    same fields as ``batch.StepContext``, as views into one device buffer that is refilled before
+    each replay.  The number of tokens is exact (it is part of the graph's key); the wanted rows
+    and the attention work lists are padded to capacities (with the first wanted row again, whose
+    logits are dropped, and with null items, which the kernels skip)."""
+
+    def __init__(self, tokens: int, wanted_cap: int, split_cap: int, max_entries: int,
+                 plan_keys: list[tuple[int, int]], device, err, split_size: int):
+        self.num_tokens, self.n_wanted = tokens, wanted_cap
+        self.split_cap, self.max_entries = split_cap, max_entries
+        self.plan_keys = sorted(plan_keys)
+        self.device, self.err, self.split_size = device, err, split_size
+        t = tokens
+        # (a few items more than the tokens make in one portion: a launcher that chooses a kernel
+        # by the number of items then sees about the real number)
+        self._tile_cap = {key: t // key[1] + MIXED_PORTIONS for key in self.plan_keys}
+        size = 3 * t + wanted_cap
+        self._off = {}
+        for key in self.plan_keys:
+            self._off[key] = size
+            size += 8 * self._tile_cap[key] + 8 * split_cap + 4 * max_entries
+        self.size = size
+        self.host = torch.zeros(size, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(size, dtype=torch.int32, device=device)
+        self.token_ids, self.positions = self.dev[0:t], self.dev[t:2 * t]
+        self.token_slot, self.wanted_rows = self.dev[2 * t:3 * t], self.dev[3 * t:3 * t + wanted_cap]
+        self._plans = {}
+        for key in self.plan_keys:
+            a = self._off[key]
+            b = a + 8 * self._tile_cap[key]
+            c = b + 8 * split_cap
+            self._plans[key] = AttentionPlan(
+                tile_work=self.dev[a:b].view(-1, 8), n_tile=self._tile_cap[key],
+                split_work=self.dev[b:c].view(-1, 8) if split_cap else None, n_split=split_cap,
+                combine_items=self.dev[c:c + 4 * max_entries].view(-1, 4) if split_cap else None,
+                n_combine=max_entries if split_cap else 0, n_slots=split_cap)
+        self.portions: list = []
+        self.entries: list = []
+        self.slots: list = []
+        self.copied = torch.cuda.Event()
+        self._pending = False
+        self.wanted = 0
+
+    def attention_plan(self, window: int, tile_tokens: int = 16) -> AttentionPlan:
+        try:
+            return self._plans[(window, tile_tokens)]
+        except KeyError:
+            raise KeyError(f"a part asked for the attention plan ({window}, {tile_tokens}), which the step "
+                           "that was recorded did not ask for") from None
+
+    def fill(self, entries, slots) -> None:
+        if self._pending:
+            self.copied.synchronize()
+        h, t = self.host_np, self.num_tokens
+        self.entries, self.slots = entries, slots
+        self.portions = []
+        wanted, off = [], 0
+        for e, slot in zip(entries, slots):
+            n = len(e.tokens)
+            h[off:off + n] = e.tokens
+            h[t + off:t + off + n] = np.arange(e.start, e.start + n)
+            h[2 * t + off:2 * t + off + n] = slot
+            wanted.extend(off + w for w in e.want)
+            self.portions.append((slot, off, e.start, n))
+            off += n
+        if off != t or len(wanted) > self.n_wanted:
+            raise ValueError("the step does not fit the recorded one")
+        self.wanted = len(wanted)
+        h[3 * t:3 * t + self.n_wanted] = wanted[0] if wanted else 0
+        h[3 * t:3 * t + len(wanted)] = wanted
+        for key in self.plan_keys:
+            tile, split, combine, n_slots = plan_attention(self.portions, key[0], self.split_size, key[1])
+            if len(tile) > self._tile_cap[key] or len(split) > self.split_cap or len(combine) > self.max_entries:
+                raise ValueError("the step's attention work outgrew the recorded capacities")
+            a = self._off[key]
+            b = a + 8 * self._tile_cap[key]
+            c = b + 8 * self.split_cap
+            h[a:c + 4 * self.max_entries] = 0
+            h[a:a + tile.size] = tile.reshape(-1)
+            h[b:b + split.size] = split.reshape(-1)
+            h[c:c + combine.size] = combine.reshape(-1)
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+        self._pending = True
+
+
 def split_items(entries, windows: list[int], split_size: int) -> int:
     """The longest attention work list of a decode step over ``entries``."""
     worst = 0
@@ -155,6 +255,10 @@ class DecodeGraphs:
         self.pool = None
         self.replays = 0
         self.dropped = 0
+        # steps that mix portions: recorded when a step of the same shape comes a second time
+        self.mixed: OrderedDict[tuple, tuple] = OrderedDict()
+        self.mixed_seen: OrderedDict[tuple, int] = OrderedDict()
+        self.mixed_replays = 0
 
     def capacity_for(self, entries) -> int:
         n = split_items(entries, self.windows, self.runner.split_size)
@@ -184,6 +288,15 @@ class DecodeGraphs:
         batch, capacity = key
         ctx = StaticStepContext(batch, capacity, self.windows, r.device, r.err, r.split_size,
                                 pad_slot=r.cache.pad_slot)
+        self.graphs[key] = self._record(ctx)
+        while len(self.graphs) > self.max_graphs:
+            # nothing of the dropped graph is in flight: _record() synchronised
+            self.graphs.popitem(last=False)
+            self.dropped += 1
+
+    def _record(self, ctx) -> tuple:
+        """(pieces, ctx, residual stream, logits or None, launches recorded) of the program on ``ctx``."""
+        r = self.runner
         if self.pool is None:
             self.pool = torch.cuda.graph_pool_handle()
         torch.cuda.synchronize()
@@ -218,11 +331,70 @@ class DecodeGraphs:
         # the last step's result is the logits: the graph's own buffer when that step is
         # recorded, else what the step returns at every replay
         logits = h if pieces[-1][0] is not None else None
-        self.graphs[key] = (pieces, ctx, stream, logits, recorded)
-        while len(self.graphs) > self.max_graphs:
-            # nothing of the dropped graph is in flight: record() synchronised above
-            self.graphs.popitem(last=False)
+        return pieces, ctx, stream, logits, recorded
+
+    # -- steps that mix portions of prompts and decoded tokens --------------
+    def mixed_key_for(self, entries) -> tuple | None:
+        """(tokens, wanted rows, split items) of the recorded step that would serve ``entries``, the
+        last two rounded up; None for steps too small to be worth recording, with more portions
+        than its tile work lists are made for, or with more wanted rows than requests can be live."""
+        tokens = sum(len(e.tokens) for e in entries)
+        if tokens < MIXED_MIN_TOKENS or len(entries) > self.runner.cache.max_live:
+            return None
+        wanted = sum(len(e.want) for e in entries)
+        singles = [e for e in entries if len(e.tokens) == 1]
+        splits = split_items(singles, self.windows, self.runner.split_size) if singles else 0
+        # the tile work lists hold what the tokens can make in up to MIXED_PORTIONS portions
+        if sum(len(e.tokens) > 1 for e in entries) > MIXED_PORTIONS:
+            return None
+        # few classes, so that a continuous batch whose decoded rows come and go records a
+        # handful of steps and not one per mix: wanted rows as many as requests may be live,
+        # split items the next power of two
+        split_cap = 0
+        if splits:
+            split_cap = MIXED_SPLIT_STEP
+            while split_cap < splits:
+                split_cap *= 2
+        if wanted > self.runner.cache.max_live:
+            return None
+        return tokens, self.runner.cache.max_live, split_cap
+
+    def mixed_ready(self, key) -> bool:
+        return key in self.mixed
+
+    def mixed_seen_again(self, key) -> bool:
+        """Counts a step of this shape that ran unrecorded; True from the MIXED_SIGHTINGS-th on."""
+        n = self.mixed_seen.pop(key, 0) + 1
+        self.mixed_seen[key] = n
+        while len(self.mixed_seen) > 64:
+            self.mixed_seen.popitem(last=False)
+        return n >= MIXED_SIGHTINGS
+
+    def record_mixed(self, key, plan_keys) -> None:
+        tokens, wanted_cap, split_cap = key
+        r = self.runner
+        ctx = StaticMixedContext(tokens, wanted_cap, split_cap, r.cache.max_live, list(plan_keys), r.device,
+                                 r.err, r.split_size)
+        self.mixed[key] = self._record(ctx)
+        while len(self.mixed) > MIXED_GRAPHS:
+            self.mixed.popitem(last=False)
             self.dropped += 1
+
+    def replay_mixed(self, key, entries, slots) -> torch.Tensor:
+        from .. import kernels as K
+
+        pieces, ctx, h, logits, recorded = self.mixed[key]
+        self.mixed.move_to_end(key)
+        ctx.fill(entries, slots)
+        for graph, fns in pieces:
+            if graph is not None:
+                graph.replay()
+            else:
+                for fn in fns:
+                    h = fn(h, ctx)
+        K.LAUNCHES[0] += recorded
+        self.mixed_replays += 1
+        return (h if logits is None else logits)[:ctx.wanted]
 
     def replay(self, key, entries, slots, tokens_device=None) -> torch.Tensor:
         """``tokens_device`` (int32, one per entry, on the device): the step's token ids, in

@@ -208,7 +208,17 @@ class ModelRunner:
         if logits is None:
             if tokens_device is not None:
                 raise ValueError("token ids on the device serve recorded steps only (see can_step_ahead)")
-            logits = self.forward(StepContext(entries, slots, self.device, self.err, self.split_size))
+            mixed = self.graphs.mixed_key_for(entries) if self.graphs is not None else None
+            if mixed is not None and self.graphs.mixed_ready(mixed):
+                logits = self.graphs.replay_mixed(mixed, entries, slots)
+                if not static_logits:
+                    logits = logits.clone()
+            else:
+                ctx = StepContext(entries, slots, self.device, self.err, self.split_size)
+                logits = self.forward(ctx)
+                # a step of this shape has come often enough: later ones replay a recorded one
+                if mixed is not None and self.graphs.mixed_seen_again(mixed):
+                    self.graphs.record_mixed(mixed, ctx._plans.keys())
         for e in entries:
             self.cache.advance(e.uid, e.start + len(e.tokens))
         self.steps_run += 1

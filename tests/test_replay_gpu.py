@@ -234,3 +234,47 @@ def test_bfloat16_rows_do_not_depend_on_the_neighbours(zoo, name):
     assert len(rows_alone) == sum(cuts)
     for key, row in rows_alone.items():
         assert torch.equal(row, rows_beside[key]), f"position {key[1]} of {uid} changes with its neighbours"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_steps_of_mixed_portions_are_recorded_when_their_shape_repeats(zoo, name, dtype):
+    """Steps of the same shape (a step that fills a token budget, say) come again and again: from
+    the second on they are recorded, later ones replay the recording.  Whole prompts of equal
+    length one after the other, then portions beside decoded tokens of three other requests: the
+    rows agree with the plain implementation and, bit for bit, with a runner that records nothing."""
+    from lockstep_b200.engine import ModelRunner
+
+    folder, _, _ = zoo(name, dtype)
+    config, page = H.CONFIGS[name]
+    vocab = config["vocab_size"]
+    n = 320
+    prompts = {u: H.random_tokens(n + 8, vocab, seed=900 + i) for i, u in enumerate("abcdefgh")}
+    plain = {u: H.plain_logits(folder, t).float() for u, t in prompts.items()}
+    plain["x"] = plain["y"] = plain["a"]
+    steps = []
+    for u in "abc":                                     # whole prompts, one a step: the same shape thrice
+        steps.append({"entries": [(u, prompts[u][:n], [n - 1])], "end": []})
+    for u in "xy":                                      # and twice more, by requests that end at once
+        steps.append({"entries": [(u, prompts["a"][:n], [0, n - 1])], "end": [u]})
+    at = {u: n for u in "abc"}
+    for k, u in enumerate("defgh"):                     # a portion of 317 beside three decoded tokens, five times
+        entries = [(v, prompts[v][at[v]:at[v] + 1], [0]) for v in "abc"]
+        for v in "abc":
+            at[v] += 1
+        entries.insert(1, (u, prompts[u][:n - 3], [n - 4]))
+        steps.append({"entries": entries, "end": [u]})
+    steps[-1]["end"] = ["h", "a", "b", "c"]
+    rows = {}
+    for graphs in (True, False):
+        runner = ModelRunner(folder, dtype=dtype, num_pages=4 * (-(-(n + 8) // page)) + 2, page_size=page,
+                             max_live=4, max_seq_len=1024, use_graphs=graphs)
+        rows[graphs] = H.run_plan(runner, steps)
+        if graphs:
+            assert runner.graphs.mixed_replays == 2 + 2, runner.graphs.mixed_replays
+            assert len(runner.graphs.mixed) == 2
+        runner.cache.audit()
+    H.assert_rows_close(rows[True], plain, dtype, f"{name}/{dtype}/recorded mixed steps", config=name)
+    assert rows[True].keys() == rows[False].keys()
+    for key in rows[True]:
+        assert torch.equal(rows[True][key], rows[False][key]), key
