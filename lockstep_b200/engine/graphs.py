@@ -145,6 +145,7 @@ MIXED_GRAPHS = 8         # recorded steps of mixed portions kept (least recently
 MIXED_SPLIT_STEP = 64    # the split work list of such a step holds this many items, or a power of two times as many
 MIXED_PORTIONS = 4       # portions of two or more tokens such a step may hold
 MIXED_SIGHTINGS = 3      # a shape is recorded when it comes for this many times
+MIXED_RECORDINGS = 48    # recordings of such steps in a runner's life: a workload of ever new shapes stops recording
 
 
 class StaticMixedContext:
@@ -259,6 +260,7 @@ class DecodeGraphs:
         self.mixed: OrderedDict[tuple, tuple] = OrderedDict()
         self.mixed_seen: OrderedDict[tuple, int] = OrderedDict()
         self.mixed_replays = 0
+        self.mixed_recordings = 0
 
     def capacity_for(self, entries) -> int:
         n = split_items(entries, self.windows, self.runner.split_size)
@@ -364,6 +366,8 @@ class DecodeGraphs:
 
     def mixed_seen_again(self, key) -> bool:
         """Counts a step of this shape that ran unrecorded; True from the MIXED_SIGHTINGS-th on."""
+        if self.mixed_recordings >= MIXED_RECORDINGS:
+            return False
         n = self.mixed_seen.pop(key, 0) + 1
         self.mixed_seen[key] = n
         while len(self.mixed_seen) > 64:
@@ -376,8 +380,10 @@ class DecodeGraphs:
         ctx = StaticMixedContext(tokens, wanted_cap, split_cap, r.cache.max_live, list(plan_keys), r.device,
                                  r.err, r.split_size)
         self.mixed[key] = self._record(ctx)
+        self.mixed_recordings += 1
         while len(self.mixed) > MIXED_GRAPHS:
-            self.mixed.popitem(last=False)
+            dropped, _ = self.mixed.popitem(last=False)
+            self.mixed_seen.pop(dropped, None)        # it has to come three times again
             self.dropped += 1
 
     def replay_mixed(self, key, entries, slots) -> torch.Tensor:
