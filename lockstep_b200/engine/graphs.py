@@ -350,7 +350,7 @@ class DecodeGraphs:
         if sum(len(e.tokens) > 1 for e in entries) > MIXED_PORTIONS:
             return None
         # few classes, so that a continuous batch whose decoded rows come and go records a
-        # handful of steps and not one per mix: wanted rows as many as requests may be live,
+        # handful of steps and not one per mix: wanted rows in sixty-fours (at most as many as requests may be live),
         # split items the next power of two
         split_cap = 0
         if splits:
@@ -359,7 +359,7 @@ class DecodeGraphs:
                 split_cap *= 2
         if wanted > self.runner.cache.max_live:
             return None
-        return tokens, self.runner.cache.max_live, split_cap
+        return tokens, min(self.runner.cache.max_live, -(-max(wanted, 1) // 64) * 64), split_cap
 
     def mixed_ready(self, key) -> bool:
         return key in self.mixed
