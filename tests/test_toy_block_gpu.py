@@ -1,9 +1,10 @@
-"""A block arrangement and an embedding defined here, not in the framework.
+"""A block arrangement, an embedding and a norm defined here, not in the framework.
 
 The block is a "sandwich": a norm before and a norm after the mixer, and after the
 feed-forward, whose output is the sum of two branches (the layer's own feed-forward and a
 second, shared one).  Its further parts come from ``LayerSpec.extra`` under names of the
-block's own choosing.  The embedding adds a learned table of absolute positions to the token
+block's own choosing; the norm after the mixer is a toy norm of its own kind
+(centred, with a bias).  The embedding adds a learned table of absolute positions to the token
 embedding, and the mixers rotate nothing: the position encoding lives outside the mixer.  A
 toy architecture uses both, is replayed whole, in portions and mixed (decode steps recorded as
 graphs), and compared with the same model written out plainly in float64."""
@@ -23,7 +24,27 @@ pytestmark = pytest.mark.gpu
 def register_toys():
     from lockstep_b200 import kernels as K
     from lockstep_b200.config import LayerRun, LayerSpec, ModelSpec, PartSpec, register_architecture
-    from lockstep_b200.parts import Block, Part, WeightSpec, build_part, register_part
+    from lockstep_b200.parts import Block, Norm, Part, WeightSpec, build_part, register_part
+
+    class CentredNorm(Norm):
+        """y = (x - mean(x)) * rsqrt(var(x) + eps) * gain + bias, in float32, out in the engine's type."""
+
+        graph_safe = True
+
+        def __init__(self, width, eps, runtime):
+            self.width, self.eps, self.rt = width, eps, runtime
+
+        def weight_specs(self):
+            return {"weight": WeightSpec((self.width,), "gain"), "bias": WeightSpec((self.width,))}
+
+        def bind(self, tensors):
+            self.gain, self.bias = tensors["weight"].float(), tensors["bias"].float()
+
+        def forward(self, h, row_index=None):
+            x = h if row_index is None else h[row_index.long()]
+            x = x - x.mean(dim=-1, keepdim=True)
+            y = x * torch.rsqrt(x.square().mean(dim=-1, keepdim=True) + self.eps) * self.gain + self.bias
+            return y.to(self.rt.dtype)
 
     class Sandwich(Block):
         """h += post_a(mixer(pre_a(h)));  h += post_b(ffn(pre_b(h)) + shared(pre_b(h)))."""
@@ -97,6 +118,10 @@ def register_toys():
     def build_block(spec, runtime, layer_spec=None, **_):
         return Sandwich(layer_spec, runtime)
 
+    @register_part("norm", "toy_centred_norm")
+    def build_norm(spec, runtime, **_):
+        return CentredNorm(spec["width"], spec["eps"], runtime)
+
     @register_part("embedding", "toy_learned_positions")
     def build_embedding(spec, runtime, **_):
         return LearnedPositions(spec["vocab_size"], spec["width"], spec["places"], runtime)
@@ -117,12 +142,13 @@ def register_toys():
             r = self.raw
             width, d = r["width"], r["head_dim"]
             norm = PartSpec("rmsnorm", {"width": width, "eps": r["eps"]})
+            centred = PartSpec("toy_centred_norm", {"width": width, "eps": r["eps"]})
             attn = PartSpec("gqa_attention", {"hidden_size": width, "num_heads": r["heads"], "num_kv_heads": r["kv_heads"],
                                               "head_dim": d, "qk_norm_eps": None, "window": 0, "scale": d ** -0.5})
             layers = [LayerSpec(prefix=f"blocks.{i}", block=PartSpec("toy_sandwich"), mixer=attn,
                                 feed_forward=PartSpec("swiglu", {"hidden_size": width, "intermediate_size": r["ffn"]}),
                                 mixer_norm=norm, feed_forward_norm=norm, position=PartSpec("none"),
-                                extra={"post_mixer_norm": norm, "post_feed_forward_norm": norm,
+                                extra={"post_mixer_norm": centred, "post_feed_forward_norm": norm,
                                        "shared_feed_forward": PartSpec("swiglu", {"hidden_size": width,
                                                                                   "intermediate_size": r["shared"]})})
                       for i in range(r["layers"])]
@@ -143,6 +169,7 @@ def unregister_toys():
     unregister_architecture("ToySandwichForCausalLM")
     unregister_part("block", "toy_sandwich")
     unregister_part("embedding", "toy_learned_positions")
+    unregister_part("norm", "toy_centred_norm")
 
 
 def plain_toy(folder, tokens):
@@ -154,6 +181,11 @@ def plain_toy(folder, tokens):
     n, d, nq, nkv = len(tokens), r["head_dim"], r["heads"], r["kv_heads"]
     h = w["embed.tokens.weight"][torch.tensor(tokens)] + w["embed.places.weight"][:n]
     norm = lambda x, name: plain.rms_norm(x, w[name], r["eps"])
+
+    def centred(x, name):
+        x = x - x.mean(dim=-1, keepdim=True)
+        return x * torch.rsqrt(x.square().mean(dim=-1, keepdim=True) + r["eps"]) * w[f"{name}.weight"] + w[f"{name}.bias"]
+
     for i in range(r["layers"]):
         p = f"blocks.{i}"
         y = norm(h, f"{p}.pre_a.weight")
@@ -161,7 +193,7 @@ def plain_toy(folder, tokens):
         k = (y @ w[f"{p}.mixer.k_proj.weight"].T).view(n, nkv, d)
         v = (y @ w[f"{p}.mixer.v_proj.weight"].T).view(n, nkv, d)
         a = plain.causal_attention(q, k, v, d ** -0.5).reshape(n, nq * d) @ w[f"{p}.mixer.o_proj.weight"].T
-        h = h + norm(a, f"{p}.post_a.weight")
+        h = h + centred(a, f"{p}.post_a")
         y = norm(h, f"{p}.pre_b.weight")
         both = sum(plain.swiglu_mlp(y, w[f"{p}.{b}.gate_proj.weight"], w[f"{p}.{b}.up_proj.weight"],
                                     w[f"{p}.{b}.down_proj.weight"]) for b in ("ffn", "shared"))
