@@ -278,6 +278,29 @@ def time_prefill(runner, tokens, repeats=REPEATS):
     return times
 
 
+def time_generate(engine, batch, options, prompt=512, new=256, repeats=3):
+    """Tokens a second of `batch` requests with prompts of `prompt` tokens generating `new` tokens
+    each through ``Engine.generate`` (host tokens in and out, the prefill included); the median of
+    `repeats` runs after one untimed run."""
+    import time
+
+    import torch
+
+    from lockstep_b200 import Request
+
+    rates = []
+    for r in range(repeats + 1):
+        requests = [Request(uid=f"g{r}_{i}", prompt=[(11 * i + 7 * j + r) % 1000 for j in range(prompt)],
+                            max_new_tokens=new, **options) for i in range(batch)]
+        torch.cuda.synchronize()
+        start = time.perf_counter()
+        out = engine.generate(requests)
+        torch.cuda.synchronize()
+        if r:
+            rates.append(sum(len(v) for v in out.values()) / (time.perf_counter() - start))
+    return statistics.median(rates)
+
+
 def steps_for(ms_guess: float, least: int = 8, most: int = 400, region_ms: float = 220.0) -> int:
     """Steps that make a region last about `region_ms`."""
     return max(least, min(most, int(region_ms / max(ms_guess, 1e-3))))
@@ -383,6 +406,11 @@ def run_ours(args):
     e2e_all, h2d, d2h = time_e2e(engine, args.batch, CONTEXT, args.steps, args.warmup)
     pre_all = time_prefill(runner, PREFILL_TOKENS)
     pre_ms = statistics.median(pre_all)
+    if not args.quick:
+        # whole generations through the entry point (their prefill included), greedy and sampled
+        for name, options in (("greedy", {}), ("temperature", {"temperature": 0.8, "seed": 3}),
+                              ("top_p", {"temperature": 0.8, "top_p": 0.9, "seed": 3})):
+            points[f"generate_b{args.batch}_p512_n256_{name}"] = round(time_generate(engine, args.batch, options), 1)
     flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
     bytes_step = step_bytes(cfg, layers, args.batch, CONTEXT - args.steps / 2)
     achieved = bytes_step / (ms * 1e-3) / 1e9
